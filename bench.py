@@ -1,0 +1,387 @@
+#!/usr/bin/env python
+"""Benchmark of the KSMM hot path.
+
+One *step* is one pass of the single-factor sweep: every benchmark pattern at
+batch 25088 in fp32 and fp16, batch-last and batch-first (one kernel launch per
+case).  Inputs are synthetic (x ~ N(0,1), W ~ U(+-1/sqrt(c)), seeded), resident
+in device memory for `value`, and in pinned host memory for `e2e`, which goes
+through the C ABI's host-buffer entry point (host->device copy, kernel,
+device->host copy inside the timed call).
+
+    python bench.py --gpus N --steps K --warmup W          # this library
+    python bench.py --impl reference ...                   # the reference's CPU algorithm
+
+With N > 1 (launched by torch.distributed.run) every rank runs the same sweep
+on its own batch shard of 25088 columns: weak scaling, no collective on the
+data path; the time is the maximum over ranks.
+
+Prints one JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+BATCH = 25088
+# the patterns the benchmark specification names (README layer, KS-ViT-B MLP, 3-factor chain)
+PATTERNS = [(6, 64, 64, 1), (1, 768, 192, 2), (4, 192, 192, 1), (1, 768, 192, 4),
+            (1, 192, 768, 4), (1, 64, 64, 16), (4, 64, 64, 4), (16, 64, 64, 1)]
+DTYPES = ["fp32", "fp16"]
+TORCH_DT = {"fp32": torch.float32, "fp16": torch.float16}
+ESIZE = {"fp32": 4, "fp16": 2}
+
+
+def flops_of(p, batch):
+    a, b, c, d = p
+    return 2.0 * a * b * c * d * batch
+
+
+def min_bytes_of(p, batch, es):
+    a, b, c, d = p
+    return float(es) * (a * c * d * batch + a * b * d * batch + a * b * c * d)
+
+
+def cases():
+    out = []
+    for dt in DTYPES:
+        for bs_last in (True, False):
+            for p in PATTERNS:
+                out.append({"pattern": p, "dtype": dt, "bs_last": bs_last})
+    return out
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            pk = json.load(f)
+        return {"hbm_gbs": float(pk["hbm_gbs"]), "bf16_tflops": float(pk["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+# ---------------------------------------------------------------------------
+# clocks: sampled through NVML while the timed region runs (read-only)
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+               0x4: "sw_power_cap", 0x80: "hw_power_brake", 0x2: "applications_clocks_setting"}
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def start(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+        med = statistics.median(self.samples) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+# ---------------------------------------------------------------------------
+# the reference's CPU algorithm (torch einsum, all host threads), bounded sample
+# ---------------------------------------------------------------------------
+def cpu_reference_pass(sample_cols, seed=0):
+    """One pass of the fp32 half of the sweep on the host at `sample_cols` batch
+    columns with the reference's einsum algorithm; returns (flops, seconds)."""
+    from oracle import reference_port as rp
+    g = torch.Generator().manual_seed(seed)
+    total_fl, total_s = 0.0, 0.0
+    for bs_last in (True, False):
+        for p in PATTERNS:
+            a, b, c, d = p
+            w = (torch.rand((a, b, c, d), generator=g) * 2 - 1) / (c ** 0.5)
+            shape = (a * c * d, sample_cols) if bs_last else (sample_cols, a * c * d)
+            x = torch.randn(shape, generator=g)
+            chain = rp.ChainCPU([p], [w], "einsum", bs_last)
+            t0 = time.perf_counter()
+            chain(x)
+            total_s += time.perf_counter() - t0
+            total_fl += flops_of(p, sample_cols)
+    return total_fl, total_s
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    cols = 3136
+    for _ in range(args.warmup):
+        cpu_reference_pass(cols)
+    fl, secs = 0.0, 0.0
+    for _ in range(args.steps):
+        f, s = cpu_reference_pass(cols)
+        fl += f
+        secs += s
+    val = fl / secs / 1e12
+    line = {
+        "impl": "reference", "metric": "ksmm_sweep_throughput", "value": val, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * secs / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(),
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+                         "kind": "port",
+                         "sample": f"fp32 half of the sweep (16 cases), first {cols} of {BATCH} batch "
+                                   "columns, reference algo=einsum restated on torch CPU"},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config():
+    return {"workload": "single-factor sweep (configs[1] restricted to the 8 benchmark patterns): "
+                        "fp32+fp16 x batch-last+batch-first, B=25088 per GPU, 32 launches per step",
+            "patterns": [list(p) for p in PATTERNS], "batch_per_gpu": BATCH,
+            "l2": "a step touches ~5.4 GB of distinct buffers (> 126 MB L2) before any buffer repeats"}
+
+
+# ---------------------------------------------------------------------------
+# this library
+# ---------------------------------------------------------------------------
+def run_ours(args, rank, world, local_rank):
+    import ksmm_b200 as kb
+    from ksmm_b200 import _lib
+
+    lib = _lib.load()
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    peaks = load_peaks()
+    cs = cases()
+    g = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    for c in cs:
+        a, b, cc, d = c["pattern"]
+        dt = TORCH_DT[c["dtype"]]
+        shape = (a * cc * d, BATCH) if c["bs_last"] else (BATCH, a * cc * d)
+        c["x"] = torch.randn(shape, generator=g).to(dt).to(dev)
+        w = (torch.rand((a, b, cc, d), generator=g) * 2 - 1) / (cc ** 0.5)
+        c["w"] = kb.generate_factor(a, b, cc, d, "kernel", w, dt, dev)
+        oshape = (a * b * d, BATCH) if c["bs_last"] else (BATCH, a * b * d)
+        c["y"] = torch.empty(oshape, dtype=dt, device=dev)
+        c["flops"] = flops_of(c["pattern"], BATCH)
+        c["bytes"] = min_bytes_of(c["pattern"], BATCH, ESIZE[c["dtype"]])
+    step_flops = sum(c["flops"] for c in cs)
+
+    def one_step(events=None):
+        for idx, c in enumerate(cs):
+            a, b, cc, d = c["pattern"]
+            if events is not None:
+                events[idx][0].record()
+            kb.forward_ex(c["x"], c["w"], c["bs_last"], a, b, cc, d, out=c["y"])
+            if events is not None:
+                events[idx][1].record()
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+
+    for _ in range(max(args.warmup, 3)):
+        one_step()
+    torch.cuda.synchronize()
+    kb.check_device()
+
+    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+           for _ in cs] for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local_rank)
+    launches0 = kb.launch_count()
+    barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    e0.record()
+    for s in range(args.steps):
+        one_step(ev[s])
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    clocks = sampler.stop()
+    launches = kb.launch_count() - launches0
+    elapsed_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device=dev)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    kb.check_device()
+    value = world * step_flops * args.steps / (elapsed_ms * 1e-3) / 1e12
+
+    # per-case launch durations (CUDA events around each launch, inside the timed region)
+    ffma = ctypes.c_float(0.0)
+    _lib.check(lib.ksmm_cu_measure_ffma_peak(ctypes.byref(ffma), None))
+    ffma_peak = float(ffma.value)
+    per = []
+    for idx, c in enumerate(cs):
+        ms = statistics.mean(ev[s][idx][0].elapsed_time(ev[s][idx][1]) for s in range(args.steps))
+        t_hbm = c["bytes"] / (peaks["hbm_gbs"] * 1e9)
+        pk = ffma_peak if c["dtype"] == "fp32" else peaks["bf16_tflops"]
+        t_fl = c["flops"] / (pk * 1e12)
+        t_roof = max(t_hbm, t_fl)
+        per.append({"pattern": list(c["pattern"]), "dtype": c["dtype"],
+                    "layout": "bs_last" if c["bs_last"] else "bs_first", "ms": round(ms, 5),
+                    "gbs": round(c["bytes"] / (ms * 1e-3) / 1e9, 1),
+                    "tflops": round(c["flops"] / (ms * 1e-3) / 1e12, 2),
+                    "bound": "hbm" if t_hbm >= t_fl else ("ffma" if c["dtype"] == "fp32" else "tensor"),
+                    "roofline_frac": round(t_roof / (ms * 1e-3), 4)})
+
+    def roofline_of(entry, c):
+        ms = entry["ms"]
+        if entry["bound"] == "hbm":
+            ach, pk, unit = c["bytes"] / (ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s"
+        else:
+            ach = c["flops"] / (ms * 1e-3) / 1e12
+            pk = ffma_peak if entry["bound"] == "ffma" else peaks["bf16_tflops"]
+            unit = "TFLOP/s"
+        return {"bound": entry["bound"], "achieved": round(ach, 2), "peak": round(pk, 2), "unit": unit,
+                "frac": round(ach / pk, 4), "traffic": None,
+                "kernel": f"{entry['dtype']} {entry['layout']} {tuple(entry['pattern'])}",
+                "peak_source": ("ksmm_cu_measure_ffma_peak (live FFMA probe; no fp32 figure in "
+                                "MEASURED_PEAKS.json)" if entry["bound"] == "ffma"
+                                else f"MEASURED_PEAKS.json ({peaks['source']})"),
+                "share_of_step": round(ms / (elapsed_ms / args.steps), 4)}
+
+    dom = max(range(len(cs)), key=lambda q: per[q]["ms"])
+    hbm_idx = [q for q in range(len(cs)) if per[q]["bound"] == "hbm"]
+    dom_hbm = max(hbm_idx, key=lambda q: per[q]["ms"]) if hbm_idx else None
+
+    # ---- end to end through the C ABI with pinned HOST buffers ------------------------------
+    e2e = None
+    if not args.no_e2e:
+        host = []
+        for c in cs:
+            a, b, cc, d = c["pattern"]
+            hx = torch.empty(c["x"].shape, dtype=c["x"].dtype, pin_memory=True).copy_(c["x"])
+            hw = torch.empty(c["w"].shape, dtype=c["w"].dtype, pin_memory=True).copy_(c["w"])
+            hy = torch.empty(c["y"].shape, dtype=c["y"].dtype, pin_memory=True)
+            host.append((hx, hw, hy, _lib.int32_array([a, b, cc, d]),
+                         (ctypes.c_void_p * 1)(hw.data_ptr())))
+        torch.cuda.synchronize()
+        h2d = sum(hx.numel() * hx.element_size() + hw.numel() * hw.element_size()
+                  for hx, hw, _, _, _ in host)
+        d2h = sum(hy.numel() * hy.element_size() for _, _, hy, _, _ in host)
+
+        def e2e_step():
+            for c, (hx, hw, hy, pat, vals) in zip(cs, host):
+                code = _lib.KSMM_F32 if c["dtype"] == "fp32" else _lib.KSMM_F16
+                _lib.check(lib.ksmm_cu_chain_forward_host(
+                    hx.data_ptr(), vals, hy.data_ptr(), None, BATCH, 1, pat, code,
+                    int(c["bs_last"]), local_rank))
+
+        e2e_step()  # warm-up: the library allocates its staging buffers here
+        e2e_steps = max(1, min(args.steps, 3))
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e2e_s = time.perf_counter() - t0
+        barrier()
+        if world > 1:
+            t = torch.tensor([e2e_s], device=dev)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            e2e_s = float(t.item())
+        # the result really came back: compare one case with the device-resident run
+        chk = cs[0]
+        kb.forward_ex(chk["x"], chk["w"], chk["bs_last"], *chk["pattern"], out=chk["y"])
+        torch.cuda.synchronize()
+        assert torch.equal(host[0][2], chk["y"].cpu()), "host-path result differs from device path"
+        e2e = {"value": world * step_flops * e2e_steps / e2e_s / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": e2e_steps,
+               "api": "ksmm_cu_chain_forward_host (C ABI, pinned host buffers, wall clock)"}
+
+    if rank != 0:
+        return
+
+    # ---- CPU baseline: bounded sample on the host cores (rank 0, N = 1 only) -----------------
+    cpu = None
+    if world == 1 and not args.no_cpu:
+        cols = 3136
+        cpu_reference_pass(cols)
+        fl, secs, passes = 0.0, 0.0, 0
+        while secs < 10.0 and passes < 40:
+            f, s = cpu_reference_pass(cols)
+            fl, secs, passes = fl + f, secs + s, passes + 1
+        cpu = {"value": fl / secs / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+               "kind": "port",
+               "sample": f"{passes} passes of the fp32 half of the sweep (16 cases) on the first {cols} "
+                         f"of {BATCH} batch columns, reference algo=einsum restated on torch CPU"}
+
+    line = {
+        "metric": "ksmm_sweep_throughput", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32+f16 (fp32 accumulate)", "data": "synthetic",
+        "config": workload_config(), "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
+        "roofline": roofline_of(per[dom], cs[dom]),
+        "roofline_hbm": roofline_of(per[dom_hbm], cs[dom_hbm]) if dom_hbm is not None else None,
+        "ffma_peak_tflops": round(ffma_peak, 2),
+        "cpu_baseline": cpu, "per_pattern": per,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world > 1:
+        torch.cuda.set_device(local_rank)
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,194 @@
+/*
+ * ksmm_cu.h -- C ABI of the B200-native Kronecker-sparse matrix multiplication
+ * (KSMM) library, libksmm_cu.so.
+ *
+ * The reference project has no C ABI.  Each entry point below names the
+ * reference interface it stands in for (paths relative to the reference
+ * checkout).  All pointers are plain device pointers unless the name says
+ * "host"; no torch type appears anywhere in this file.
+ *
+ * Conventions shared by every call
+ *   - one factor has a pattern (a, b, c, d); weights ("values") are in the
+ *     reference's kernel format: a row-major (a*d*c, b) matrix whose element
+ *     [((i_a*d + i_d)*c + k), j] is W[i_a, j, k, i_d]
+ *     (src/ksmm_py/layer/kronecker_sparse/interface.py:65-69,
+ *      src/ksmm_cu/src/template_sparse_mm.cu:362-394);
+ *   - batch-last (bs_last = 1): input is (a*c*d, batch) row-major, output is
+ *     (a*b*d, batch); batch-first (bs_last = 0): input is (batch, a*c*d),
+ *     output is (batch, a*b*d);
+ *   - inputs are borrowed, outputs are caller-owned and fully overwritten;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default
+ *     stream); every call is asynchronous with respect to the host and
+ *     ordered on that stream, except the *_host calls, which return after the
+ *     result is in host memory;
+ *   - the return value is a ksmm_status_t; on failure ksmm_cu_last_error()
+ *     gives a message for the calling thread.  The library never aborts the
+ *     process (the reference asserts: kernel_bs_first_float.cuh:18,
+ *     kernel.cu:123-125).
+ */
+#ifndef KSMM_CU_H_
+#define KSMM_CU_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define KSMM_API __attribute__((visibility("default")))
+#else
+#define KSMM_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  KSMM_OK = 0,
+  KSMM_ERR_BAD_ARGUMENT = 1,   /* null pointer, non-positive size, bad enum   */
+  KSMM_ERR_UNSUPPORTED = 2,    /* dtype / layout combination not implemented  */
+  KSMM_ERR_CUDA = 3,           /* a CUDA runtime or driver call failed        */
+  KSMM_ERR_WORKSPACE = 4,      /* workspace missing or too small              */
+  KSMM_ERR_DEVICE_TIMEOUT = 5, /* a bounded device-side wait gave up          */
+  KSMM_ERR_NO_DEVICE = 6       /* no sm_100 device is visible                 */
+} ksmm_status_t;
+
+/* Element types.  The strings the reference passes through pybind
+ * ("torch.float32", "torch.float16", "torch.float8_e4m3fn"; kernel.cu:66,83,103)
+ * map onto these in the Python layer. */
+typedef enum {
+  KSMM_F32 = 0,
+  KSMM_F16 = 1,
+  KSMM_BF16 = 2,
+  KSMM_F8E4M3 = 3
+} ksmm_dtype_t;
+
+/* Kernel families (for ksmm_forward_desc_t.algo and the tuner). */
+typedef enum {
+  KSMM_ALGO_AUTO = 0,   /* cached tuner choice, else heuristic                */
+  KSMM_ALGO_SIMT = 1,   /* FFMA register-tiled kernel, any shape/alignment     */
+  KSMM_ALGO_TC = 2      /* tcgen05 + TMEM + TMA kernel (16-bit and fp8 types)  */
+} ksmm_algo_t;
+
+/* Full description of one factor multiplication. */
+typedef struct {
+  const void* input;
+  const void* values;     /* kernel-format weights, (a*d*c, b) row-major       */
+  void* output;
+  const void* bias;       /* optional, a*b*d elements of out_dtype, or NULL    */
+  int64_t batch;
+  int32_t a, b, c, d;
+  int32_t in_dtype;       /* ksmm_dtype_t of input and values                  */
+  int32_t out_dtype;      /* ksmm_dtype_t of output (F8 not allowed)           */
+  int32_t bs_last;        /* 1 = batch-last, 0 = batch-first                   */
+  int32_t algo;           /* ksmm_algo_t                                       */
+  int32_t config;         /* tile configuration index inside the family, -1 = auto */
+  float alpha;            /* output = alpha * (K x) + bias; fp8: s_x * s_w     */
+} ksmm_forward_desc_t;
+
+/* Library version: major*10000 + minor*100 + patch. */
+KSMM_API int ksmm_cu_version(void);
+
+/* Message for the last failure on the calling thread ("" if none). */
+KSMM_API const char* ksmm_cu_last_error(void);
+KSMM_API const char* ksmm_cu_status_string(int status);
+
+/*
+ * One factor, output dtype = input dtype, alpha = 1, no bias.
+ * Replaces the C++-linkage launchers
+ *   void best_kernel_bs_{first,last}_{float,half}(T* input, T* values, T* output,
+ *        int batch_size, int a, int b, int c, int d, dim3&, dim3&)
+ * (src/ksmm_py/layer/kronecker_sparse/kernel_bs_first_float.cuh:8-21,
+ *  kernel_bs_last_half.cuh:8-21) and the dtype/layout switch around them
+ * (kernel.cu:40-127).  Argument order follows those launchers: input, values,
+ * output, batch, a, b, c, d.
+ */
+KSMM_API int ksmm_cu_forward(const void* input, const void* values, void* output,
+                    int64_t batch, int a, int b, int c, int d,
+                    int dtype, int bs_last, void* stream);
+
+/*
+ * One factor with every option (mixed output type, scale, bias, forced kernel
+ * family / tile configuration).  Same reference counterpart as
+ * ksmm_cu_forward; the fp8 path is what the reference's empty branch
+ * (kernel.cu:66-82) and its standalone fp8 kernels
+ * (src/ksmm_cu/src/template_kernels_fp8.cuh:22-370) were meant to provide,
+ * with per-tensor scales folded into alpha and fp32 accumulation.
+ */
+KSMM_API int ksmm_cu_forward_ex(const ksmm_forward_desc_t* desc, void* stream);
+
+/*
+ * A chain of factors: patterns[4*f .. 4*f+3] = (a,b,c,d) of factor f, applied
+ * f = 0 first, as KSLinear.forward_bs_{first,last} loops over its factors
+ * (interface.py:193-211, 269-291) and post_process adds the bias once
+ * (interface.py:451-467).  `workspace` holds the intermediate activations;
+ * its size comes from ksmm_cu_chain_workspace_bytes (0 for a single factor).
+ */
+KSMM_API size_t ksmm_cu_chain_workspace_bytes(int nfactors, const int32_t* patterns,
+                                     int64_t batch, int dtype);
+KSMM_API int ksmm_cu_chain_forward(const void* input, const void* const* values, void* output,
+                          const void* bias, void* workspace, size_t workspace_bytes,
+                          int64_t batch, int nfactors, const int32_t* patterns,
+                          int dtype, int bs_last, void* stream);
+
+/*
+ * Host-memory variant of ksmm_cu_chain_forward: input, values and output are
+ * HOST buffers; the call stages them through device memory that the library
+ * owns (grown on demand, reused across calls), runs the chain and returns
+ * after the output has been copied back.  This is the call a C user without
+ * its own device buffers makes; it stands in for the standalone driver's
+ * cudaMalloc / cudaMemcpy / launch / cudaMemcpy sequence
+ * (src/ksmm_cu/src/template_sparse_mm.cu:443-457, 545-784, 800-803).
+ * `device` is the CUDA device ordinal.
+ */
+KSMM_API int ksmm_cu_chain_forward_host(const void* host_input, const void* const* host_values,
+                               void* host_output, const void* host_bias,
+                               int64_t batch, int nfactors, const int32_t* patterns,
+                               int dtype, int bs_last, int device);
+
+/*
+ * Tile-configuration introspection and tuning.  Replaces the offline
+ * exhaustive search of src/ksmm_cu/long_run.sh:178-229 and the generated
+ * .best tables (kernel_bs_last_float.best etc.): candidates are compiled in,
+ * timed in-process with CUDA events and cached per
+ * (dtype, layout, a, b, c, d, batch).
+ *
+ * ksmm_cu_num_configs: number of tile configurations of a kernel family.
+ * ksmm_cu_config_supported: 1 if (algo, config) can run this problem.
+ * ksmm_cu_tune: times every supported candidate on the given buffers (which
+ *   must be valid for the problem; output is overwritten), stores the winner
+ *   in the in-process cache, and reports it.  best_ms may be NULL.
+ * ksmm_cu_set_choice / ksmm_cu_get_choice: write / read the cache directly,
+ *   so that a saved table can be re-loaded without re-timing.
+ */
+KSMM_API int ksmm_cu_num_configs(int algo);
+KSMM_API int ksmm_cu_config_supported(int algo, int config, int64_t batch, int a, int b, int c, int d,
+                             int in_dtype, int out_dtype, int bs_last);
+KSMM_API int ksmm_cu_tune(const ksmm_forward_desc_t* desc, int nrepeats, void* stream,
+                 int* best_algo, int* best_config, float* best_ms);
+KSMM_API int ksmm_cu_set_choice(int64_t batch, int a, int b, int c, int d, int in_dtype, int out_dtype,
+                       int bs_last, int algo, int config);
+KSMM_API int ksmm_cu_get_choice(int64_t batch, int a, int b, int c, int d, int in_dtype, int out_dtype,
+                       int bs_last, int* algo, int* config);
+
+/*
+ * Synchronises `stream` and returns KSMM_ERR_DEVICE_TIMEOUT if a kernel
+ * launched earlier on the current device gave up one of its bounded waits
+ * (the flag is then cleared), KSMM_OK otherwise.  The reference has no
+ * counterpart: its launchers never check a CUDA or device status
+ * (kernel.cu:40-127).
+ */
+KSMM_API int ksmm_cu_check_device(void* stream);
+
+/* Number of kernel launches issued by this library in the calling process
+ * since load (all threads); used by the benchmark to report its launch count. */
+KSMM_API uint64_t ksmm_cu_launch_count(void);
+
+/* FP32 FFMA throughput probe: runs a register-resident FMA loop on every SM
+ * and returns the measured TFLOP/s in *tflops (the fp32 roofline denominator,
+ * which no vendor library reports). */
+KSMM_API int ksmm_cu_measure_ffma_peak(float* tflops, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KSMM_CU_H_ */

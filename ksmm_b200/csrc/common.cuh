@@ -1,0 +1,144 @@
+// Shared host/device helpers of libksmm_cu: element-type traits, vector
+// load/store helpers, status plumbing.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ksmm_cu.h"
+
+namespace ksmm {
+
+// ---------------------------------------------------------------------------
+// element types
+// ---------------------------------------------------------------------------
+struct f8e4m3 {
+  uint8_t bits;
+};
+
+template <typename T>
+struct ElemTraits;
+
+template <>
+struct ElemTraits<float> {
+  static constexpr int kDtype = KSMM_F32;
+  __device__ static float to_float(float v) { return v; }
+  __device__ static float from_float(float v) { return v; }
+};
+template <>
+struct ElemTraits<__half> {
+  static constexpr int kDtype = KSMM_F16;
+  __device__ static float to_float(__half v) { return __half2float(v); }
+  __device__ static __half from_float(float v) { return __float2half_rn(v); }
+};
+template <>
+struct ElemTraits<__nv_bfloat16> {
+  static constexpr int kDtype = KSMM_BF16;
+  __device__ static float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+  __device__ static __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }
+};
+template <>
+struct ElemTraits<f8e4m3> {
+  static constexpr int kDtype = KSMM_F8E4M3;
+  __device__ static float to_float(f8e4m3 v) {
+    __half_raw h = __nv_cvt_fp8_to_halfraw(v.bits, __NV_E4M3);
+    return __half2float(__half(h));
+  }
+};
+
+__host__ __device__ inline int dtype_size(int dt) {
+  return dt == KSMM_F32 ? 4 : (dt == KSMM_F8E4M3 ? 1 : 2);
+}
+
+// ---------------------------------------------------------------------------
+// N-wide (N = 1, 2, 4) global loads / stores with conversion to / from float.
+// The caller guarantees N * sizeof(T) alignment when N > 1.
+// ---------------------------------------------------------------------------
+template <typename T, int N>
+__device__ __forceinline__ void load_vec(const T* __restrict__ p, float (&out)[N]) {
+  if constexpr (N == 1) {
+    out[0] = ElemTraits<T>::to_float(*p);
+  } else if constexpr (sizeof(T) == 4) {
+    if constexpr (N == 4) {
+      float4 v = __ldg(reinterpret_cast<const float4*>(p));
+      out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+    } else {
+      float2 v = __ldg(reinterpret_cast<const float2*>(p));
+      out[0] = v.x; out[1] = v.y;
+    }
+  } else if constexpr (sizeof(T) == 2) {
+    if constexpr (N == 4) {
+      uint2 raw = __ldg(reinterpret_cast<const uint2*>(p));
+      T tmp[4];
+      *reinterpret_cast<uint2*>(tmp) = raw;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) out[e] = ElemTraits<T>::to_float(tmp[e]);
+    } else {
+      uint32_t raw = __ldg(reinterpret_cast<const uint32_t*>(p));
+      T tmp[2];
+      *reinterpret_cast<uint32_t*>(tmp) = raw;
+      out[0] = ElemTraits<T>::to_float(tmp[0]);
+      out[1] = ElemTraits<T>::to_float(tmp[1]);
+    }
+  } else {
+    if constexpr (N == 4) {
+      uint32_t raw = __ldg(reinterpret_cast<const uint32_t*>(p));
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        T t; t.bits = (raw >> (8 * e)) & 0xffu;
+        out[e] = ElemTraits<T>::to_float(t);
+      }
+    } else {
+      uint16_t raw = __ldg(reinterpret_cast<const uint16_t*>(p));
+      T t0, t1; t0.bits = raw & 0xffu; t1.bits = raw >> 8;
+      out[0] = ElemTraits<T>::to_float(t0);
+      out[1] = ElemTraits<T>::to_float(t1);
+    }
+  }
+}
+
+template <typename T, int N>
+__device__ __forceinline__ void store_vec(T* __restrict__ p, const float (&v)[N]) {
+  if constexpr (N == 1) {
+    *p = ElemTraits<T>::from_float(v[0]);
+  } else if constexpr (sizeof(T) == 4) {
+    if constexpr (N == 4) {
+      *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+      *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]);
+    }
+  } else {
+    T tmp[N];
+#pragma unroll
+    for (int e = 0; e < N; ++e) tmp[e] = ElemTraits<T>::from_float(v[e]);
+    if constexpr (N == 4) {
+      *reinterpret_cast<uint2*>(p) = *reinterpret_cast<uint2*>(tmp);
+    } else {
+      *reinterpret_cast<uint32_t*>(p) = *reinterpret_cast<uint32_t*>(tmp);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// problem description handed to every kernel family
+// ---------------------------------------------------------------------------
+struct Problem {
+  const void* in;
+  const void* w;
+  void* out;
+  const void* bias;
+  int64_t batch;
+  int a, b, c, d;
+  int in_dtype, out_dtype;
+  int bs_last;
+  float alpha;
+};
+
+// host-side error plumbing (defined in ksmm_cu.cu)
+int set_error(int status, const char* fmt, ...);
+void count_launch();
+
+}  // namespace ksmm

@@ -1,0 +1,495 @@
+// C ABI of libksmm_cu.so: argument checking, kernel-family dispatch, the
+// in-process tuner cache, chained factors, and the host-buffer variant.
+// Declarations and the reference interfaces they stand in for: include/ksmm_cu.h.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <tuple>
+#include <vector>
+
+#include "common.cuh"
+#include "tc_kernel.h"
+
+namespace ksmm {
+
+// ---------------------------------------------------------------------------
+// error plumbing
+// ---------------------------------------------------------------------------
+static thread_local char g_last_error[512] = "";
+static std::atomic<uint64_t> g_launches{0};
+
+int set_error(int status, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+  return status;
+}
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+#define KSMM_CUDA_OK(expr)                                                              \
+  do {                                                                                  \
+    cudaError_t e__ = (expr);                                                           \
+    if (e__ != cudaSuccess)                                                             \
+      return set_error(KSMM_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__)); \
+  } while (0)
+
+// per-dtype instantiations live in their own translation units
+int simt_launch_f32(const Problem& p, int config, cudaStream_t stream);
+int simt_launch_f16(const Problem& p, int config, cudaStream_t stream);
+int simt_launch_bf16(const Problem& p, int config, cudaStream_t stream);
+int simt_launch_f8(const Problem& p, int config, cudaStream_t stream);
+int simt_default_config_for(const Problem& p);
+int simt_num_configs();
+
+static int simt_launch(const Problem& p, int config, cudaStream_t stream) {
+  if (config < 0) config = simt_default_config_for(p);
+  switch (p.in_dtype) {
+    case KSMM_F32:
+      if (p.out_dtype != KSMM_F32)
+        return set_error(KSMM_ERR_UNSUPPORTED, "fp32 input needs an fp32 output");
+      return simt_launch_f32(p, config, stream);
+    case KSMM_F16:
+      if (p.out_dtype != KSMM_F16)
+        return set_error(KSMM_ERR_UNSUPPORTED, "fp16 input needs an fp16 output");
+      return simt_launch_f16(p, config, stream);
+    case KSMM_BF16:
+      if (p.out_dtype != KSMM_BF16)
+        return set_error(KSMM_ERR_UNSUPPORTED, "bf16 input needs a bf16 output");
+      return simt_launch_bf16(p, config, stream);
+    case KSMM_F8E4M3:
+      return simt_launch_f8(p, config, stream);
+    default:
+      return set_error(KSMM_ERR_BAD_ARGUMENT, "unknown input dtype %d", p.in_dtype);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// tuner cache: (batch, a, b, c, d, in_dtype, out_dtype, bs_last) -> (algo, config)
+// ---------------------------------------------------------------------------
+using ChoiceKey = std::tuple<int64_t, int, int, int, int, int, int, int>;
+struct Choice {
+  int algo, config;
+};
+static std::mutex g_choice_mu;
+static std::map<ChoiceKey, Choice> g_choices;
+
+static ChoiceKey key_of(const Problem& p) {
+  return ChoiceKey(p.batch, p.a, p.b, p.c, p.d, p.in_dtype, p.out_dtype, p.bs_last);
+}
+
+static bool lookup_choice(const Problem& p, Choice* out) {
+  std::lock_guard<std::mutex> g(g_choice_mu);
+  auto it = g_choices.find(key_of(p));
+  if (it == g_choices.end()) return false;
+  *out = it->second;
+  return true;
+}
+
+static int check_problem(const Problem& p) {
+  if (!p.in || !p.w || !p.out)
+    return set_error(KSMM_ERR_BAD_ARGUMENT, "null pointer (input=%p values=%p output=%p)", p.in,
+                     p.w, p.out);
+  if (p.a <= 0 || p.b <= 0 || p.c <= 0 || p.d <= 0)
+    return set_error(KSMM_ERR_BAD_ARGUMENT, "pattern (%d,%d,%d,%d) must be positive", p.a, p.b,
+                     p.c, p.d);
+  if (p.batch < 0) return set_error(KSMM_ERR_BAD_ARGUMENT, "negative batch");
+  if (p.in_dtype < KSMM_F32 || p.in_dtype > KSMM_F8E4M3)
+    return set_error(KSMM_ERR_BAD_ARGUMENT, "unknown input dtype %d", p.in_dtype);
+  if (p.out_dtype < KSMM_F32 || p.out_dtype > KSMM_BF16)
+    return set_error(KSMM_ERR_BAD_ARGUMENT, "unsupported output dtype %d", p.out_dtype);
+  if (p.bs_last != 0 && p.bs_last != 1)
+    return set_error(KSMM_ERR_BAD_ARGUMENT, "bs_last must be 0 or 1");
+  return KSMM_OK;
+}
+
+static int run_family(const Problem& p, int algo, int config, cudaStream_t stream) {
+  if (algo == KSMM_ALGO_SIMT) return simt_launch(p, config, stream);
+  if (algo == KSMM_ALGO_TC) return tc_launch(p, config, stream);
+  return set_error(KSMM_ERR_BAD_ARGUMENT, "unknown kernel family %d", algo);
+}
+
+static int dispatch(const Problem& p, int algo, int config, cudaStream_t stream) {
+  int st = check_problem(p);
+  if (st != KSMM_OK) return st;
+  if (p.batch == 0) return KSMM_OK;  // empty batch: nothing to write
+  if (algo == KSMM_ALGO_AUTO) {
+    Choice ch;
+    if (lookup_choice(p, &ch)) return run_family(p, ch.algo, ch.config, stream);
+    const int tc_cfg = tc_default_config(p);
+    if (tc_cfg >= 0) return tc_launch(p, tc_cfg, stream);
+    return simt_launch(p, -1, stream);
+  }
+  return run_family(p, algo, config, stream);
+}
+
+static Problem problem_of(const ksmm_forward_desc_t& dsc) {
+  Problem p;
+  p.in = dsc.input;
+  p.w = dsc.values;
+  p.out = dsc.output;
+  p.bias = dsc.bias;
+  p.batch = dsc.batch;
+  p.a = dsc.a; p.b = dsc.b; p.c = dsc.c; p.d = dsc.d;
+  p.in_dtype = dsc.in_dtype;
+  p.out_dtype = dsc.out_dtype;
+  p.bs_last = dsc.bs_last;
+  p.alpha = dsc.alpha;
+  return p;
+}
+
+// ---------------------------------------------------------------------------
+// FFMA peak probe
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) ffma_probe_kernel(float* sink, int iters, float seed) {
+  float r[16];
+#pragma unroll
+  for (int q = 0; q < 16; ++q) r[q] = seed + threadIdx.x * 1e-3f + q;
+  const float m = 1.0000001f, add = 1e-7f;
+  for (int it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+#pragma unroll
+      for (int q = 0; q < 16; ++q) r[q] = fmaf(r[q], m, add);
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int q = 0; q < 16; ++q) s += r[q];
+  if (s == 123.456f) sink[0] = s;  // never true; keeps the loop alive
+}
+
+// ---------------------------------------------------------------------------
+// device buffers owned by the host-memory entry point
+// ---------------------------------------------------------------------------
+struct HostPathState {
+  std::mutex mu;
+  int device = -1;
+  cudaStream_t stream = nullptr;
+  void* buf[4] = {nullptr, nullptr, nullptr, nullptr};  // input, output, weights, workspace
+  size_t cap[4] = {0, 0, 0, 0};
+};
+static HostPathState g_host;
+
+static int host_reserve(int which, size_t bytes) {
+  if (bytes <= g_host.cap[which]) return KSMM_OK;
+  if (g_host.buf[which]) {
+    KSMM_CUDA_OK(cudaFree(g_host.buf[which]));
+    g_host.buf[which] = nullptr;
+    g_host.cap[which] = 0;
+  }
+  size_t want = bytes + bytes / 8 + 256;
+  KSMM_CUDA_OK(cudaMalloc(&g_host.buf[which], want));
+  g_host.cap[which] = want;
+  return KSMM_OK;
+}
+
+static size_t align_up(size_t v, size_t al) { return (v + al - 1) / al * al; }
+
+}  // namespace ksmm
+
+using namespace ksmm;
+
+extern "C" {
+
+int ksmm_cu_version(void) { return 100; }
+
+const char* ksmm_cu_last_error(void) { return g_last_error; }
+
+const char* ksmm_cu_status_string(int status) {
+  switch (status) {
+    case KSMM_OK: return "ok";
+    case KSMM_ERR_BAD_ARGUMENT: return "bad argument";
+    case KSMM_ERR_UNSUPPORTED: return "unsupported";
+    case KSMM_ERR_CUDA: return "CUDA error";
+    case KSMM_ERR_WORKSPACE: return "workspace missing or too small";
+    case KSMM_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";
+    case KSMM_ERR_NO_DEVICE: return "no sm_100 device";
+    default: return "unknown status";
+  }
+}
+
+int ksmm_cu_check_device(void* stream) {
+  return tc_check_device(static_cast<cudaStream_t>(stream));
+}
+
+uint64_t ksmm_cu_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int ksmm_cu_forward(const void* input, const void* values, void* output, int64_t batch, int a,
+                    int b, int c, int d, int dtype, int bs_last, void* stream) {
+  Problem p;
+  p.in = input; p.w = values; p.out = output; p.bias = nullptr;
+  p.batch = batch; p.a = a; p.b = b; p.c = c; p.d = d;
+  p.in_dtype = dtype;
+  p.out_dtype = dtype;
+  p.bs_last = bs_last;
+  p.alpha = 1.f;
+  if (dtype == KSMM_F8E4M3)
+    return set_error(KSMM_ERR_UNSUPPORTED,
+                     "fp8 needs an explicit output type and scale: use ksmm_cu_forward_ex");
+  return dispatch(p, KSMM_ALGO_AUTO, -1, static_cast<cudaStream_t>(stream));
+}
+
+int ksmm_cu_forward_ex(const ksmm_forward_desc_t* desc, void* stream) {
+  if (!desc) return set_error(KSMM_ERR_BAD_ARGUMENT, "null descriptor");
+  return dispatch(problem_of(*desc), desc->algo, desc->config, static_cast<cudaStream_t>(stream));
+}
+
+size_t ksmm_cu_chain_workspace_bytes(int nfactors, const int32_t* patterns, int64_t batch,
+                                     int dtype) {
+  if (nfactors <= 1 || !patterns || batch <= 0) return 0;
+  size_t mx = 0;
+  for (int f = 0; f + 1 < nfactors; ++f) {
+    const int32_t* q = patterns + 4 * f;
+    size_t bytes = static_cast<size_t>(q[0]) * q[1] * q[3] * batch * dtype_size(dtype);
+    if (bytes > mx) mx = bytes;
+  }
+  mx = align_up(mx, 256);
+  return nfactors == 2 ? mx : 2 * mx;
+}
+
+int ksmm_cu_chain_forward(const void* input, const void* const* values, void* output,
+                          const void* bias, void* workspace, size_t workspace_bytes,
+                          int64_t batch, int nfactors, const int32_t* patterns, int dtype,
+                          int bs_last, void* stream) {
+  if (nfactors <= 0 || !patterns || !values)
+    return set_error(KSMM_ERR_BAD_ARGUMENT, "chain needs at least one factor");
+  if (dtype == KSMM_F8E4M3)
+    return set_error(KSMM_ERR_UNSUPPORTED, "chains run in fp32, fp16 or bf16");
+  for (int f = 0; f + 1 < nfactors; ++f) {
+    const int32_t* q = patterns + 4 * f;
+    const int32_t* r = patterns + 4 * (f + 1);
+    if (static_cast<int64_t>(q[0]) * q[1] * q[3] != static_cast<int64_t>(r[0]) * r[2] * r[3])
+      return set_error(KSMM_ERR_BAD_ARGUMENT,
+                       "factor %d produces %lld features but factor %d expects %lld", f,
+                       static_cast<long long>(q[0]) * q[1] * q[3], f + 1,
+                       static_cast<long long>(r[0]) * r[2] * r[3]);
+  }
+  const size_t need = ksmm_cu_chain_workspace_bytes(nfactors, patterns, batch, dtype);
+  if (need > 0 && (!workspace || workspace_bytes < need))
+    return set_error(KSMM_ERR_WORKSPACE, "chain workspace: need %zu bytes, got %zu", need,
+                     workspace_bytes);
+  const size_t half = nfactors == 2 ? need : need / 2;
+  const void* cur = input;
+  for (int f = 0; f < nfactors; ++f) {
+    const int32_t* q = patterns + 4 * f;
+    const bool last = (f + 1 == nfactors);
+    void* dst = last ? output : static_cast<char*>(workspace) + (f & 1) * half;
+    Problem p;
+    p.in = cur; p.w = values[f]; p.out = dst; p.bias = last ? bias : nullptr;
+    p.batch = batch; p.a = q[0]; p.b = q[1]; p.c = q[2]; p.d = q[3];
+    p.in_dtype = dtype; p.out_dtype = dtype; p.bs_last = bs_last; p.alpha = 1.f;
+    int st = dispatch(p, KSMM_ALGO_AUTO, -1, static_cast<cudaStream_t>(stream));
+    if (st != KSMM_OK) return st;
+    cur = dst;
+  }
+  return KSMM_OK;
+}
+
+int ksmm_cu_chain_forward_host(const void* host_input, const void* const* host_values,
+                               void* host_output, const void* host_bias, int64_t batch,
+                               int nfactors, const int32_t* patterns, int dtype, int bs_last,
+                               int device) {
+  if (nfactors <= 0 || !patterns || !host_values || !host_input || !host_output)
+    return set_error(KSMM_ERR_BAD_ARGUMENT, "null argument to the host-memory chain call");
+  if (batch <= 0) return batch == 0 ? KSMM_OK : set_error(KSMM_ERR_BAD_ARGUMENT, "negative batch");
+  std::lock_guard<std::mutex> g(g_host.mu);
+  KSMM_CUDA_OK(cudaSetDevice(device));
+  if (g_host.device != device) {
+    // buffers belong to one device at a time; moving devices drops them
+    for (int q = 0; q < 4; ++q) {
+      if (g_host.buf[q]) cudaFree(g_host.buf[q]);
+      g_host.buf[q] = nullptr;
+      g_host.cap[q] = 0;
+    }
+    if (g_host.stream) cudaStreamDestroy(g_host.stream);
+    g_host.stream = nullptr;
+    KSMM_CUDA_OK(cudaStreamCreateWithFlags(&g_host.stream, cudaStreamNonBlocking));
+    g_host.device = device;
+  }
+  const size_t es = dtype_size(dtype);
+  const int32_t* p0 = patterns;
+  const int32_t* pl = patterns + 4 * (nfactors - 1);
+  const size_t in_bytes = static_cast<size_t>(p0[0]) * p0[2] * p0[3] * batch * es;
+  const size_t out_feats = static_cast<size_t>(pl[0]) * pl[1] * pl[3];
+  const size_t out_bytes = out_feats * batch * es;
+  std::vector<size_t> woff(nfactors + 1, 0);
+  for (int f = 0; f < nfactors; ++f) {
+    const int32_t* q = patterns + 4 * f;
+    woff[f + 1] = woff[f] + align_up(static_cast<size_t>(q[0]) * q[1] * q[2] * q[3] * es, 256);
+  }
+  const size_t bias_off = woff[nfactors];
+  const size_t w_bytes = bias_off + (host_bias ? align_up(out_feats * es, 256) : 0);
+  const size_t ws_bytes = ksmm_cu_chain_workspace_bytes(nfactors, patterns, batch, dtype);
+  int st;
+  if ((st = host_reserve(0, in_bytes)) != KSMM_OK) return st;
+  if ((st = host_reserve(1, out_bytes)) != KSMM_OK) return st;
+  if ((st = host_reserve(2, w_bytes)) != KSMM_OK) return st;
+  if ((st = host_reserve(3, ws_bytes)) != KSMM_OK) return st;
+  cudaStream_t s = g_host.stream;
+  KSMM_CUDA_OK(cudaMemcpyAsync(g_host.buf[0], host_input, in_bytes, cudaMemcpyHostToDevice, s));
+  std::vector<const void*> dvals(nfactors);
+  for (int f = 0; f < nfactors; ++f) {
+    const int32_t* q = patterns + 4 * f;
+    char* dst = static_cast<char*>(g_host.buf[2]) + woff[f];
+    KSMM_CUDA_OK(cudaMemcpyAsync(dst, host_values[f],
+                                 static_cast<size_t>(q[0]) * q[1] * q[2] * q[3] * es,
+                                 cudaMemcpyHostToDevice, s));
+    dvals[f] = dst;
+  }
+  const void* dbias = nullptr;
+  if (host_bias) {
+    char* dst = static_cast<char*>(g_host.buf[2]) + bias_off;
+    KSMM_CUDA_OK(cudaMemcpyAsync(dst, host_bias, out_feats * es, cudaMemcpyHostToDevice, s));
+    dbias = dst;
+  }
+  st = ksmm_cu_chain_forward(g_host.buf[0], dvals.data(), g_host.buf[1], dbias, g_host.buf[3],
+                             g_host.cap[3], batch, nfactors, patterns, dtype, bs_last, s);
+  if (st != KSMM_OK) return st;
+  KSMM_CUDA_OK(cudaMemcpyAsync(host_output, g_host.buf[1], out_bytes, cudaMemcpyDeviceToHost, s));
+  KSMM_CUDA_OK(cudaStreamSynchronize(s));
+  return KSMM_OK;
+}
+
+int ksmm_cu_num_configs(int algo) {
+  if (algo == KSMM_ALGO_SIMT) return simt_num_configs();
+  if (algo == KSMM_ALGO_TC) return tc_num_configs();
+  return 0;
+}
+
+int ksmm_cu_config_supported(int algo, int config, int64_t batch, int a, int b, int c, int d,
+                             int in_dtype, int out_dtype, int bs_last) {
+  Problem p;
+  p.in = p.w = nullptr; p.out = nullptr; p.bias = nullptr;
+  p.batch = batch; p.a = a; p.b = b; p.c = c; p.d = d;
+  p.in_dtype = in_dtype; p.out_dtype = out_dtype; p.bs_last = bs_last; p.alpha = 1.f;
+  if (a <= 0 || b <= 0 || c <= 0 || d <= 0 || batch <= 0) return 0;
+  if (algo == KSMM_ALGO_SIMT) {
+    if (config < 0 || config >= simt_num_configs()) return 0;
+    if (in_dtype == KSMM_F8E4M3) return out_dtype != KSMM_F8E4M3;
+    return in_dtype == out_dtype;
+  }
+  if (algo == KSMM_ALGO_TC) return tc_config_supported(p, config, /*check_pointers=*/false);
+  return 0;
+}
+
+int ksmm_cu_tune(const ksmm_forward_desc_t* desc, int nrepeats, void* stream, int* best_algo,
+                 int* best_config, float* best_ms) {
+  if (!desc) return set_error(KSMM_ERR_BAD_ARGUMENT, "null descriptor");
+  Problem p = problem_of(*desc);
+  int st = check_problem(p);
+  if (st != KSMM_OK) return st;
+  if (p.batch == 0) return set_error(KSMM_ERR_BAD_ARGUMENT, "cannot tune an empty batch");
+  if (nrepeats < 1) nrepeats = 1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaEvent_t e0, e1;
+  KSMM_CUDA_OK(cudaEventCreate(&e0));
+  KSMM_CUDA_OK(cudaEventCreate(&e1));
+  float best = -1.f;
+  Choice win{KSMM_ALGO_SIMT, simt_default_config_for(p)};
+  const int families[2] = {KSMM_ALGO_TC, KSMM_ALGO_SIMT};
+  for (int fam : families) {
+    const int ncfg = ksmm_cu_num_configs(fam);
+    for (int cfg = 0; cfg < ncfg; ++cfg) {
+      if (fam == KSMM_ALGO_TC) {
+        if (!tc_config_supported(p, cfg, true)) continue;
+      } else if (!ksmm_cu_config_supported(fam, cfg, p.batch, p.a, p.b, p.c, p.d, p.in_dtype,
+                                           p.out_dtype, p.bs_last)) {
+        continue;
+      }
+      // warm-up (also surfaces launch errors)
+      if (run_family(p, fam, cfg, s) != KSMM_OK) continue;
+      if (cudaStreamSynchronize(s) != cudaSuccess) {
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+        return set_error(KSMM_ERR_CUDA, "tuning candidate (%d,%d) failed on the device", fam, cfg);
+      }
+      cudaEventRecord(e0, s);
+      for (int r = 0; r < nrepeats; ++r) run_family(p, fam, cfg, s);
+      cudaEventRecord(e1, s);
+      if (cudaEventSynchronize(e1) != cudaSuccess) {
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+        return set_error(KSMM_ERR_CUDA, "tuning candidate (%d,%d) failed on the device", fam, cfg);
+      }
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, e0, e1);
+      ms /= nrepeats;
+      if (best < 0.f || ms < best) {
+        best = ms;
+        win = Choice{fam, cfg};
+      }
+    }
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  if (best < 0.f) return set_error(KSMM_ERR_UNSUPPORTED, "no kernel candidate ran");
+  {
+    std::lock_guard<std::mutex> g(g_choice_mu);
+    g_choices[key_of(p)] = win;
+  }
+  if (best_algo) *best_algo = win.algo;
+  if (best_config) *best_config = win.config;
+  if (best_ms) *best_ms = best;
+  return KSMM_OK;
+}
+
+int ksmm_cu_set_choice(int64_t batch, int a, int b, int c, int d, int in_dtype, int out_dtype,
+                       int bs_last, int algo, int config) {
+  if (algo != KSMM_ALGO_SIMT && algo != KSMM_ALGO_TC)
+    return set_error(KSMM_ERR_BAD_ARGUMENT, "unknown kernel family %d", algo);
+  if (!ksmm_cu_config_supported(algo, config, batch, a, b, c, d, in_dtype, out_dtype, bs_last))
+    return set_error(KSMM_ERR_UNSUPPORTED, "configuration (%d,%d) cannot run this problem", algo,
+                     config);
+  std::lock_guard<std::mutex> g(g_choice_mu);
+  g_choices[ChoiceKey(batch, a, b, c, d, in_dtype, out_dtype, bs_last)] = Choice{algo, config};
+  return KSMM_OK;
+}
+
+int ksmm_cu_get_choice(int64_t batch, int a, int b, int c, int d, int in_dtype, int out_dtype,
+                       int bs_last, int* algo, int* config) {
+  std::lock_guard<std::mutex> g(g_choice_mu);
+  auto it = g_choices.find(ChoiceKey(batch, a, b, c, d, in_dtype, out_dtype, bs_last));
+  if (it == g_choices.end()) return set_error(KSMM_ERR_BAD_ARGUMENT, "no cached choice");
+  if (algo) *algo = it->second.algo;
+  if (config) *config = it->second.config;
+  return KSMM_OK;
+}
+
+int ksmm_cu_measure_ffma_peak(float* tflops, void* stream) {
+  if (!tflops) return set_error(KSMM_ERR_BAD_ARGUMENT, "null result pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int dev = 0, sms = 0;
+  KSMM_CUDA_OK(cudaGetDevice(&dev));
+  KSMM_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  float* sink = nullptr;
+  KSMM_CUDA_OK(cudaMalloc(&sink, sizeof(float)));
+  const int iters = 4096, blocks = sms * 8;
+  cudaEvent_t e0, e1;
+  cudaEventCreate(&e0);
+  cudaEventCreate(&e1);
+  ffma_probe_kernel<<<blocks, 256, 0, s>>>(sink, iters, 1.f);  // warm-up
+  float best = 1e30f;
+  for (int rep = 0; rep < 5; ++rep) {
+    cudaEventRecord(e0, s);
+    ffma_probe_kernel<<<blocks, 256, 0, s>>>(sink, iters, 1.f);
+    cudaEventRecord(e1, s);
+    cudaEventSynchronize(e1);
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    if (ms < best) best = ms;
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaError_t err = cudaGetLastError();
+  cudaFree(sink);
+  if (err != cudaSuccess)
+    return set_error(KSMM_ERR_CUDA, "ffma probe failed: %s", cudaGetErrorString(err));
+  const double fl = 2.0 * 16 * 8 * static_cast<double>(iters) * 256.0 * blocks;
+  *tflops = static_cast<float>(fl / (best * 1e-3) / 1e12);
+  return KSMM_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,20 @@
+// Host interface of the tcgen05 / TMEM / TMA kernel family (KSMM_ALGO_TC).
+#pragma once
+
+#include "common.cuh"
+
+namespace ksmm {
+
+int tc_num_configs();
+// true if configuration `config` of the family can run problem `p`
+// (element types, layout, TMA alignment rules).  With check_pointers the
+// base addresses are checked as well.
+bool tc_config_supported(const Problem& p, int config, bool check_pointers);
+// heuristic default configuration, or -1 if the family cannot run `p`
+int tc_default_config(const Problem& p);
+int tc_launch(const Problem& p, int config, cudaStream_t stream);
+// Synchronises `stream` and reports a device-side timeout recorded by any
+// earlier launch of this family on the current device (then clears it).
+int tc_check_device(cudaStream_t stream);
+
+}  // namespace ksmm

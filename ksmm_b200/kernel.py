@@ -1,0 +1,190 @@
+"""Per-factor and chained operators on top of the C ABI.
+
+Mirrors ``Kernel.forward(input, factor, bs_last, a, b, c, d, dtype, vsize)`` of
+the reference (src/ksmm_py/layer/kronecker_sparse/kernel.py:63-73) and the
+pybind signature below it (kernel.cpp:25-50): same argument order and meaning,
+same ownership (inputs borrowed, output freshly allocated on the input's
+device, kernel.cu:50-52).  Differences, all on purpose:
+
+* nothing is generated or compiled at call time (the reference rewrites its
+  own .cuh/.cpp files and runs nvcc per new pattern, kernel.py:92-298);
+* launches go to torch's *current* stream, not the legacy default stream;
+* failures raise (the reference asserts or silently returns garbage for fp8,
+  kernel.cu:66-82, 123-125);
+* ``vsize`` is accepted and ignored: vector widths are chosen by the library.
+
+torch is used for device memory and streams only.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import ForwardDesc, KsmmError  # noqa: F401
+
+_DTYPE_CODE = {
+    torch.float32: _lib.KSMM_F32,
+    torch.float16: _lib.KSMM_F16,
+    torch.bfloat16: _lib.KSMM_BF16,
+    torch.float8_e4m3fn: _lib.KSMM_F8E4M3,
+}
+# dtype strings that the reference's extension receives (kernel.cu:66,83-84,103-104)
+_DTYPE_FROM_STR = {
+    "torch.float32": torch.float32, "torch.float": torch.float32,
+    "torch.float16": torch.float16, "torch.half": torch.float16,
+    "torch.bfloat16": torch.bfloat16,
+    "torch.float8_e4m3fn": torch.float8_e4m3fn,
+}
+
+
+def dtype_code(dtype):
+    if isinstance(dtype, str):
+        dtype = _DTYPE_FROM_STR.get(dtype)
+    if dtype not in _DTYPE_CODE:
+        raise TypeError(f"unsupported dtype {dtype}: expected float32, float16, bfloat16 or float8_e4m3fn")
+    return _DTYPE_CODE[dtype]
+
+
+def _stream_ptr(device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _check_inputs(input, factor, bs_last, a, b, c, d):
+    if not input.is_cuda:
+        raise ValueError("input must be a CUDA tensor")
+    if not factor.is_cuda:
+        raise ValueError("factor must be a CUDA tensor")
+    if not input.is_contiguous():
+        raise ValueError("input must be contiguous")
+    if not factor.is_contiguous():
+        raise ValueError("factor must be contiguous")
+    if input.dim() != 2:
+        raise ValueError(f"input must be 2-D, got shape {tuple(input.shape)}")
+    feat = input.shape[0] if bs_last else input.shape[1]
+    if feat != a * c * d:
+        raise ValueError(f"input has {feat} features, pattern ({a},{b},{c},{d}) expects {a * c * d}")
+    if tuple(factor.shape) != (a * d * c, b):
+        raise ValueError(f"factor must have shape ({a * d * c}, {b}) = (a*d*c, b), got {tuple(factor.shape)}")
+    if factor.dtype != input.dtype:
+        raise TypeError(f"factor dtype {factor.dtype} differs from input dtype {input.dtype}")
+    if factor.device != input.device:
+        raise ValueError("input and factor live on different devices")
+
+
+def forward_ex(input, factor, bs_last, a, b, c, d, *, out_dtype=None, alpha=1.0, bias=None,
+               algo=_lib.KSMM_ALGO_AUTO, config=-1, out=None):
+    """One factor with every option of ``ksmm_cu_forward_ex``."""
+    lib = _lib.load()
+    bs_last = int(bool(bs_last))
+    _check_inputs(input, factor, bs_last, a, b, c, d)
+    out_dtype = input.dtype if out_dtype is None else out_dtype
+    if input.dtype == torch.float8_e4m3fn and out_dtype == torch.float8_e4m3fn:
+        raise TypeError("fp8 inputs need a bfloat16, float16 or float32 output")
+    batch = input.shape[1] if bs_last else input.shape[0]
+    shape = (a * b * d, batch) if bs_last else (batch, a * b * d)
+    if out is None:
+        out = torch.empty(shape, dtype=out_dtype, device=input.device)
+    elif tuple(out.shape) != shape or out.dtype != out_dtype or not out.is_contiguous():
+        raise ValueError("out has the wrong shape, dtype or strides")
+    if bias is not None:
+        if bias.numel() != a * b * d or bias.dtype != out_dtype or not bias.is_contiguous():
+            raise ValueError("bias must hold a*b*d contiguous elements of the output dtype")
+    desc = ForwardDesc(
+        input=input.data_ptr(), values=factor.data_ptr(), output=out.data_ptr(),
+        bias=bias.data_ptr() if bias is not None else None, batch=batch, a=a, b=b, c=c, d=d,
+        in_dtype=dtype_code(input.dtype), out_dtype=dtype_code(out_dtype), bs_last=bs_last,
+        algo=algo, config=config, alpha=float(alpha))
+    with torch.cuda.device(input.device):
+        _lib.check(lib.ksmm_cu_forward_ex(ctypes.byref(desc), _stream_ptr(input.device)))
+    return out
+
+
+class Kernel:
+    """Drop-in for the reference's ``Kernel`` (kernel.py:62-329).  Inference
+    only, like the reference (its ``backward`` is a stub, kernel.py:323-329)."""
+
+    @staticmethod
+    def forward(input, factor, bs_last, a, b, c, d, dtype=None, vsize=4):
+        if dtype is not None:
+            code = dtype_code(dtype)
+            if code != dtype_code(input.dtype):
+                raise TypeError(f"dtype argument {dtype} does not match the input's {input.dtype}")
+        return forward_ex(input, factor, bs_last, a, b, c, d)
+
+
+def forward(input, factor, bs_last, a, b, c, d, dtype, vsize=4):
+    """Same signature as the reference extension's ``forward`` (kernel.cpp:25-45)."""
+    return Kernel.forward(input, factor, bool(bs_last), a, b, c, d, dtype, vsize)
+
+
+def chain_forward(input, factors, patterns, bs_last, bias=None, workspace=None, out=None):
+    """All factors of one KSLinear in one library call (``ksmm_cu_chain_forward``).
+
+    ``factors[f]`` is the kernel-format (a*d*c, b) weight of ``patterns[f]``;
+    ``patterns[0]`` is applied first.  ``bias`` (out features, output dtype)
+    is fused into the last factor.
+    """
+    lib = _lib.load()
+    bs_last = int(bool(bs_last))
+    nf = len(patterns)
+    if nf == 0 or len(factors) != nf:
+        raise ValueError("need one factor per pattern")
+    for f, (p, w) in enumerate(zip(patterns, factors)):
+        a, b, c, d = p
+        if f == 0:
+            _check_inputs(input, w, bs_last, a, b, c, d)
+        elif tuple(w.shape) != (a * d * c, b) or w.dtype != input.dtype or not w.is_contiguous() \
+                or w.device != input.device:
+            raise ValueError(f"factor {f} must be a contiguous ({a * d * c}, {b}) tensor of {input.dtype}")
+    batch = input.shape[1] if bs_last else input.shape[0]
+    la, lb, lc, ld = patterns[-1]
+    n_out = la * lb * ld
+    shape = (n_out, batch) if bs_last else (batch, n_out)
+    if out is None:
+        out = torch.empty(shape, dtype=input.dtype, device=input.device)
+    flat = [int(v) for p in patterns for v in p]
+    pat = _lib.int32_array(flat)
+    code = dtype_code(input.dtype)
+    need = lib.ksmm_cu_chain_workspace_bytes(nf, pat, batch, code)
+    if need > 0 and (workspace is None or workspace.numel() * workspace.element_size() < need):
+        workspace = torch.empty(need, dtype=torch.uint8, device=input.device)
+    if bias is not None and (bias.numel() != n_out or bias.dtype != input.dtype):
+        raise ValueError("bias must hold out_size elements of the input dtype")
+    vals = (ctypes.c_void_p * nf)(*[w.data_ptr() for w in factors])
+    with torch.cuda.device(input.device):
+        _lib.check(lib.ksmm_cu_chain_forward(
+            input.data_ptr(), vals, out.data_ptr(), bias.data_ptr() if bias is not None else None,
+            workspace.data_ptr() if workspace is not None else None,
+            workspace.numel() * workspace.element_size() if workspace is not None else 0,
+            batch, nf, pat, code, bs_last, _stream_ptr(input.device)))
+    return out
+
+
+def quantize_e4m3(t):
+    """Per-tensor e4m3 quantisation: returns (t / s cast to float8_e4m3fn, s) with
+    s = amax(|t|) / 448 (the largest finite e4m3 value)."""
+    amax = t.detach().abs().amax().float()
+    scale = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+    q = (t.float() / scale).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+    return q, float(scale)
+
+
+def forward_fp8(input_q, factor_q, bs_last, a, b, c, d, scale_x, scale_w,
+                out_dtype=torch.bfloat16, **kw):
+    """fp8-e4m3 factor: y = scale_x * scale_w * (W_q x_q), fp32 accumulation."""
+    return forward_ex(input_q, factor_q, bs_last, a, b, c, d, out_dtype=out_dtype,
+                      alpha=float(scale_x) * float(scale_w), **kw)
+
+
+def check_device(device=None):
+    """Synchronise the current stream and raise if a kernel recorded a device-side timeout."""
+    lib = _lib.load()
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        _lib.check(lib.ksmm_cu_check_device(_stream_ptr(dev)))
+
+
+def launch_count():
+    return int(_lib.load().ksmm_cu_launch_count())

@@ -1,0 +1,111 @@
+"""The C-ABI library loads and exports everything include/ksmm_cu.h declares;
+argument validation runs without a GPU (no compute call is made here)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from ksmm_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "ksmm_cu.h")
+
+
+def declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ksmm_cu_\w+)\s*\(", text)))
+
+
+def test_header_and_binding_list_agree():
+    assert declared_symbols() == sorted(_lib.EXPORTS)
+
+
+def test_library_exports_every_declared_symbol():
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    for name in declared_symbols():
+        assert hasattr(lib, name), name
+
+
+def test_version_and_status_strings():
+    lib = _lib.load()
+    assert lib.ksmm_cu_version() >= 100
+    assert lib.ksmm_cu_status_string(0) == b"ok"
+    assert b"timed out" in lib.ksmm_cu_status_string(_lib.KSMM_ERR_DEVICE_TIMEOUT)
+    assert lib.ksmm_cu_status_string(12345) == b"unknown status"
+
+
+def test_null_pointers_are_rejected_not_dereferenced():
+    lib = _lib.load()
+    st = lib.ksmm_cu_forward(None, None, None, 8, 1, 2, 3, 4, _lib.KSMM_F32, 1, None)
+    assert st == _lib.KSMM_ERR_BAD_ARGUMENT
+    assert b"null pointer" in lib.ksmm_cu_last_error()
+    with pytest.raises(_lib.KsmmError):
+        _lib.check(st)
+
+
+def test_bad_pattern_dtype_layout():
+    lib = _lib.load()
+    buf = ctypes.create_string_buffer(64)
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    assert lib.ksmm_cu_forward(p, p, p, 8, 0, 2, 3, 4, _lib.KSMM_F32, 1, None) == _lib.KSMM_ERR_BAD_ARGUMENT
+    assert lib.ksmm_cu_forward(p, p, p, -1, 1, 2, 3, 4, _lib.KSMM_F32, 1, None) == _lib.KSMM_ERR_BAD_ARGUMENT
+    assert lib.ksmm_cu_forward(p, p, p, 8, 1, 2, 3, 4, 9, 1, None) == _lib.KSMM_ERR_BAD_ARGUMENT
+    assert lib.ksmm_cu_forward(p, p, p, 8, 1, 2, 3, 4, _lib.KSMM_F32, 2, None) == _lib.KSMM_ERR_BAD_ARGUMENT
+    # fp8 through the plain call has no output type / scale: explicit refusal
+    assert lib.ksmm_cu_forward(p, p, p, 8, 1, 2, 3, 4, _lib.KSMM_F8E4M3, 1, None) == _lib.KSMM_ERR_UNSUPPORTED
+    # empty batch is legal and launches nothing
+    before = lib.ksmm_cu_launch_count()
+    assert lib.ksmm_cu_forward(p, p, p, 0, 1, 2, 3, 4, _lib.KSMM_F32, 1, None) == _lib.KSMM_OK
+    assert lib.ksmm_cu_launch_count() == before
+
+
+def test_chain_validation_and_workspace():
+    lib = _lib.load()
+    pats = _lib.int32_array([6, 64, 64, 1, 1, 768, 192, 2])
+    # intermediate is 6*64*1 = 384 features of fp32
+    assert lib.ksmm_cu_chain_workspace_bytes(2, pats, 25088, _lib.KSMM_F32) == 384 * 25088 * 4
+    assert lib.ksmm_cu_chain_workspace_bytes(1, pats, 25088, _lib.KSMM_F32) == 0
+    three = _lib.int32_array([1, 64, 64, 16, 4, 64, 64, 4, 16, 64, 64, 1])
+    assert lib.ksmm_cu_chain_workspace_bytes(3, three, 128, _lib.KSMM_F16) == 2 * 1024 * 128 * 2
+    buf = ctypes.create_string_buffer(64)
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    vals = (ctypes.c_void_p * 2)(p, p)
+    # mismatched chain
+    bad = _lib.int32_array([6, 64, 64, 1, 1, 768, 100, 2])
+    st = lib.ksmm_cu_chain_forward(p, vals, p, None, None, 0, 16, 2, bad, _lib.KSMM_F32, 1, None)
+    assert st == _lib.KSMM_ERR_BAD_ARGUMENT and b"expects" in lib.ksmm_cu_last_error()
+    # missing workspace
+    st = lib.ksmm_cu_chain_forward(p, vals, p, None, None, 0, 16, 2, pats, _lib.KSMM_F32, 1, None)
+    assert st == _lib.KSMM_ERR_WORKSPACE
+
+
+def test_config_tables():
+    lib = _lib.load()
+    assert lib.ksmm_cu_num_configs(_lib.KSMM_ALGO_SIMT) >= 4
+    assert lib.ksmm_cu_num_configs(_lib.KSMM_ALGO_TC) >= 2
+    assert lib.ksmm_cu_num_configs(99) == 0
+    sup = lib.ksmm_cu_config_supported
+    F16, F32, F8, BF16 = _lib.KSMM_F16, _lib.KSMM_F32, _lib.KSMM_F8E4M3, _lib.KSMM_BF16
+    # the fp32 FFMA family takes anything
+    assert sup(_lib.KSMM_ALGO_SIMT, 0, 25088, 1, 449, 514, 3, F32, F32, 0) == 1
+    # tensor-core family: 16-bit and fp8 only, TMA stride rules
+    assert sup(_lib.KSMM_ALGO_TC, 0, 25088, 1, 768, 192, 4, F16, F16, 1) == 1
+    assert sup(_lib.KSMM_ALGO_TC, 0, 25088, 1, 768, 192, 4, F32, F32, 1) == 0
+    assert sup(_lib.KSMM_ALGO_TC, 0, 25087, 1, 768, 192, 4, F16, F16, 1) == 0   # batch*2 % 16 != 0
+    assert sup(_lib.KSMM_ALGO_TC, 0, 25088, 1, 449, 192, 4, F16, F16, 1) == 0   # b*2 % 16 != 0
+    assert sup(_lib.KSMM_ALGO_TC, 0, 25088, 4, 192, 192, 1, BF16, BF16, 0) == 1
+    assert sup(_lib.KSMM_ALGO_TC, 0, 25088, 1, 768, 192, 4, F8, BF16, 1) == 1
+    assert sup(_lib.KSMM_ALGO_TC, 4, 25088, 1, 768, 192, 4, F8, BF16, 1) == 0   # N tile 64 < one fp8 box row
+
+
+def test_choice_cache_round_trip():
+    lib = _lib.load()
+    algo, cfg = ctypes.c_int(-1), ctypes.c_int(-1)
+    assert lib.ksmm_cu_get_choice(77, 1, 64, 64, 1, 0, 0, 1, ctypes.byref(algo), ctypes.byref(cfg)) != 0
+    assert lib.ksmm_cu_set_choice(77, 1, 64, 64, 1, 0, 0, 1, _lib.KSMM_ALGO_SIMT, 1) == 0
+    assert lib.ksmm_cu_get_choice(77, 1, 64, 64, 1, 0, 0, 1, ctypes.byref(algo), ctypes.byref(cfg)) == 0
+    assert (algo.value, cfg.value) == (_lib.KSMM_ALGO_SIMT, 1)
+    # a configuration that cannot run the problem is refused
+    assert lib.ksmm_cu_set_choice(77, 1, 64, 64, 1, 0, 0, 1, _lib.KSMM_ALGO_TC, 0) == _lib.KSMM_ERR_UNSUPPORTED

@@ -1,0 +1,387 @@
+"""Parity of the CUDA library (through its C ABI) with the CPU oracle and with
+the reference's own outputs.  Tolerances are the relative Frobenius errors of
+the benchmark specification: 1e-5 fp32, 1e-2 fp16/bf16, 5e-2 fp8."""
+import ctypes
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import ksmm_b200 as kb
+from golden_cases import CASES, make_inputs, make_weights
+from ksmm_b200 import _lib
+from oracle import ksmm_oracle as ko
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = np.load(os.path.join(os.path.dirname(__file__), "golden", "ksmm_golden.npz"))
+TOL = {torch.float32: 1e-5, torch.float16: 1e-2, torch.bfloat16: 1e-2}
+TDT = {"float32": torch.float32, "float16": torch.float16}
+DEV = "cuda:0"
+
+
+def _inputs(pattern, batch, dtype, bs_last, seed):
+    rng = np.random.RandomState(seed)
+    a, b, c, d = pattern
+    shape = (a * c * d, batch) if bs_last else (batch, a * c * d)
+    x = torch.from_numpy(rng.standard_normal(shape).astype(np.float32)).to(dtype)
+    w = torch.from_numpy(make_weights([pattern], rng)[0]).to(dtype)
+    return x, w
+
+
+def _oracle(x, w, bs_last):
+    """fp64 oracle on the values the GPU actually sees (already rounded to dtype)."""
+    return ko.factor_apply(x.float().numpy(), w.float().numpy(), bs_last)
+
+
+def _run(x, w, pattern, bs_last, algo=_lib.KSMM_ALGO_AUTO, config=-1, poison=True, **kw):
+    wk = kb.generate_factor(*pattern, "kernel", w, x.dtype, DEV)
+    xg = x.to(DEV)
+    a, b, c, d = pattern
+    batch = x.shape[1] if bs_last else x.shape[0]
+    shape = (a * b * d, batch) if bs_last else (batch, a * b * d)
+    out = None
+    if poison:
+        out = torch.full(shape, float("nan"), dtype=kw.get("out_dtype", x.dtype), device=DEV)
+    y = kb.forward_ex(xg, wk, bs_last, a, b, c, d, algo=algo, config=config, out=out, **kw)
+    return y.float().cpu().numpy()
+
+
+# ---------------------------------------------------------------------------
+# 1. the reference's own outputs, through KSLinear
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("case", CASES, ids=[c["name"] for c in CASES])
+def test_kslinear_matches_reference_golden(case):
+    x, ws, bias = make_inputs(case)
+    dt = TDT[case["dtype"]]
+    layer = kb.KSLinear(case["patterns"], weights=[torch.from_numpy(w) for w in ws],
+                        bias=bias is not None, algo="kernel", dtype=dt, bs_last=case["bs_last"],
+                        device=DEV)
+    if bias is not None:
+        layer.bias.data.copy_(torch.from_numpy(bias).to(dt).reshape(layer.bias.shape))
+    y = layer(torch.from_numpy(x).to(DEV))
+    ref = GOLDEN[case["name"] + "/y"]
+    assert tuple(y.shape) == ref.shape
+    err = ko.rel_fro_error(y.float().cpu().numpy(), ref)
+    assert err < TOL[dt], (case["name"], err)
+    # per-factor execution gives the same answer as the single chain call
+    layer.fuse_chain = False
+    y2 = layer(torch.from_numpy(x).to(DEV))
+    assert ko.rel_fro_error(y2.float().cpu().numpy(), ref) < TOL[dt]
+
+
+def test_state_dict_layout_is_the_reference_kernel_format():
+    case = next(c for c in CASES if c["name"] == "f_2_3_5_4_last")
+    _, ws, _ = make_inputs(case)
+    layer = kb.KSLinear(case["patterns"], weights=[torch.from_numpy(w) for w in ws], bias=True,
+                        algo="kernel", dtype=torch.float32, bs_last=True, device=DEV)
+    sd = layer.state_dict()
+    assert set(sd) == {"factors.0", "bias"}
+    assert np.array_equal(sd["factors.0"].cpu().numpy(), GOLDEN["f_2_3_5_4_last/kernel_format0"])
+    assert tuple(sd["bias"].shape) == (layer.out_size, 1)
+    dense = layer.get_dense_product().cpu().numpy()
+    assert np.array_equal(dense, GOLDEN["f_2_3_5_4_last/dense_from_kernel0"])
+
+
+# ---------------------------------------------------------------------------
+# 2. FFMA family: every tile configuration, ragged shapes, every element type
+# ---------------------------------------------------------------------------
+SIMT_PATTERNS = [(2, 3, 5, 4), (1, 16, 16, 1), (3, 7, 9, 2), (1, 48, 24, 3), (2, 130, 20, 1),
+                 (1, 64, 64, 2), (1, 1, 1, 8), (4, 8, 8, 1)]
+
+
+@pytest.mark.parametrize("config", range(6))
+@pytest.mark.parametrize("bs_last", [True, False])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_simt_family_every_config(config, bs_last, dtype):
+    for pi, pattern in enumerate(SIMT_PATTERNS):
+        for batch in (33, 256):
+            x, w = _inputs(pattern, batch, dtype, bs_last, seed=100 + pi)
+            y = _run(x, w, pattern, bs_last, algo=_lib.KSMM_ALGO_SIMT, config=config)
+            assert not np.isnan(y).any(), (pattern, batch)
+            err = ko.rel_fro_error(y, _oracle(x, w, bs_last))
+            assert err < TOL[dtype], (pattern, batch, err)
+
+
+@pytest.mark.parametrize("bs_last", [True, False])
+def test_simt_unaligned_pointers_take_the_scalar_path(bs_last):
+    pattern, batch = (2, 12, 8, 1), 36
+    x, w = _inputs(pattern, batch, torch.float32, bs_last, seed=5)
+    a, b, c, d = pattern
+    # views that start 4 bytes into an allocation: 16-byte vector accesses are illegal
+    xs = torch.empty(x.numel() + 1, device=DEV)[1:].view(x.shape).copy_(x)
+    wk = kb.generate_factor(*pattern, "kernel", w, torch.float32, DEV)
+    ws = torch.empty(wk.numel() + 1, device=DEV)[1:].view(wk.shape).copy_(wk)
+    out = torch.empty((a * b * d) * batch + 1, device=DEV)[1:].view(
+        (a * b * d, batch) if bs_last else (batch, a * b * d))
+    y = kb.forward_ex(xs, ws, bs_last, a, b, c, d, out=out)
+    assert ko.rel_fro_error(y.cpu().numpy(), _oracle(x, w, bs_last)) < 1e-5
+
+
+# ---------------------------------------------------------------------------
+# 3. tensor-core family
+# ---------------------------------------------------------------------------
+TC_PATTERNS_LAST = [(1, 64, 64, 1), (2, 128, 32, 2), (1, 192, 192, 1), (4, 64, 64, 4),
+                    (1, 768, 192, 2), (1, 192, 768, 4), (3, 48, 80, 2), (1, 136, 72, 3)]
+TC_PATTERNS_FIRST = [(1, 64, 64, 1), (2, 128, 32, 1), (4, 192, 192, 1), (16, 64, 64, 1),
+                     (1, 768, 192, 1), (3, 48, 80, 1), (1, 136, 72, 1)]
+
+
+@pytest.mark.parametrize("config", range(5))
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_tc_family_batch_last(config, dtype):
+    for pi, pattern in enumerate(TC_PATTERNS_LAST):
+        for batch in (8, 136, 520):
+            x, w = _inputs(pattern, batch, dtype, True, seed=200 + pi)
+            y = _run(x, w, pattern, True, algo=_lib.KSMM_ALGO_TC, config=config)
+            assert not np.isnan(y).any(), (pattern, batch)
+            err = ko.rel_fro_error(y, _oracle(x, w, True))
+            assert err < TOL[dtype], (pattern, batch, config, err)
+    kb.check_device()
+
+
+@pytest.mark.parametrize("config", range(5))
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_tc_family_batch_first(config, dtype):
+    for pi, pattern in enumerate(TC_PATTERNS_FIRST):
+        for batch in (8, 136, 520):
+            x, w = _inputs(pattern, batch, dtype, False, seed=300 + pi)
+            y = _run(x, w, pattern, False, algo=_lib.KSMM_ALGO_TC, config=config)
+            assert not np.isnan(y).any(), (pattern, batch)
+            err = ko.rel_fro_error(y, _oracle(x, w, False))
+            assert err < TOL[dtype], (pattern, batch, config, err)
+    kb.check_device()
+
+
+def test_tc_refuses_what_it_cannot_run():
+    x, w = _inputs((1, 64, 64, 2), 16, torch.float16, False, seed=1)  # batch-first with d > 1
+    with pytest.raises(kb.KsmmError) as ei:
+        _run(x, w, (1, 64, 64, 2), False, algo=_lib.KSMM_ALGO_TC, config=0)
+    assert ei.value.status == _lib.KSMM_ERR_UNSUPPORTED
+    x, w = _inputs((1, 64, 64, 1), 16, torch.float32, True, seed=1)
+    with pytest.raises(kb.KsmmError):
+        _run(x, w, (1, 64, 64, 1), True, algo=_lib.KSMM_ALGO_TC, config=0)
+
+
+@pytest.mark.parametrize("bs_last", [True, False])
+def test_bias_and_alpha_epilogue(bs_last):
+    for dtype, algo in ((torch.float32, _lib.KSMM_ALGO_SIMT), (torch.float16, _lib.KSMM_ALGO_SIMT),
+                        (torch.float16, _lib.KSMM_ALGO_TC), (torch.bfloat16, _lib.KSMM_ALGO_TC)):
+        pattern, batch = (2, 72, 48, 1), 72
+        x, w = _inputs(pattern, batch, dtype, bs_last, seed=9)
+        rng = np.random.RandomState(10)
+        bias = torch.from_numpy(rng.standard_normal(2 * 72).astype(np.float32)).to(dtype)
+        y = _run(x, w, pattern, bs_last, algo=algo, bias=bias.to(DEV), alpha=0.5)
+        ref = 0.5 * _oracle(x, w, bs_last)
+        bf = bias.float().numpy()
+        ref = ref + (bf[:, None] if bs_last else bf[None, :])
+        assert ko.rel_fro_error(y, ref) < TOL[dtype], (dtype, algo)
+
+
+# ---------------------------------------------------------------------------
+# 4. fp8-e4m3 with per-tensor scales and fp32 accumulation
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("pattern", [(4, 192, 192, 1), (1, 768, 192, 4), (1, 192, 768, 4)])
+@pytest.mark.parametrize("algo", [_lib.KSMM_ALGO_TC, _lib.KSMM_ALGO_SIMT])
+def test_fp8_factor(pattern, algo):
+    batch, bs_last = 512, True
+    x, w = _inputs(pattern, batch, torch.float32, bs_last, seed=40)
+    a, b, c, d = pattern
+    wk = kb.generate_factor(a, b, c, d, "kernel", w, torch.float32, DEV)
+    xq, sx = kb.quantize_e4m3(x.to(DEV))
+    wq, sw = kb.quantize_e4m3(wk)
+    ref_full = _oracle(x, w, bs_last)                       # unquantised fp32 dense result
+    xq_f = xq.float().cpu().numpy()
+    wq_abcd = ko.kernel_format_to_abcd(wq.float().cpu().numpy(), pattern)
+    ref_q = sx * sw * ko.factor_apply(xq_f, wq_abcd, bs_last)  # exact result on the quantised values
+    for out_dtype, tol_q in ((torch.bfloat16, 1e-2), (torch.float32, 1e-5)):
+        y = kb.forward_fp8(xq, wq, bs_last, a, b, c, d, sx, sw, out_dtype=out_dtype, algo=algo)
+        y = y.float().cpu().numpy()
+        assert ko.rel_fro_error(y, ref_q) < tol_q, (pattern, out_dtype)
+        assert ko.rel_fro_error(y, ref_full) < 5e-2, (pattern, out_dtype)
+    kb.check_device()
+
+
+def test_fp8_kslinear_chain():
+    pats = [(4, 192, 192, 1), (1, 768, 192, 4)]
+    rng = np.random.RandomState(41)
+    ws = make_weights(pats, rng)
+    x = rng.standard_normal((768, 256)).astype(np.float32)
+    layer = kb.KSLinear(pats, weights=[torch.from_numpy(w) for w in ws], bias=False, algo="kernel",
+                        dtype=torch.float8_e4m3fn, bs_last=True, device=DEV)
+    y = layer(torch.from_numpy(x).to(DEV).to(torch.bfloat16))
+    ref = ko.chain_apply(x, ws, True)
+    assert ko.rel_fro_error(y.float().cpu().numpy(), ref) < 5e-2 * math.sqrt(2)
+
+
+# ---------------------------------------------------------------------------
+# 5. full benchmark batch (25088): size-independent properties
+# ---------------------------------------------------------------------------
+FULL_B = 25088
+FULL_PATTERNS = [(6, 64, 64, 1), (1, 768, 192, 2), (4, 192, 192, 1), (1, 768, 192, 4),
+                 (1, 192, 768, 4), (1, 64, 64, 16), (4, 64, 64, 4), (16, 64, 64, 1)]
+
+
+@pytest.mark.parametrize("bs_last", [True, False])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_full_batch_sampled_columns_against_oracle(dtype, bs_last):
+    g = torch.Generator(device="cpu").manual_seed(77)
+    cols = np.unique(np.concatenate([np.arange(0, 8), np.arange(FULL_B - 8, FULL_B),
+                                     np.random.RandomState(1).randint(0, FULL_B, 48)]))
+    for pattern in FULL_PATTERNS:
+        a, b, c, d = pattern
+        shape = (a * c * d, FULL_B) if bs_last else (FULL_B, a * c * d)
+        x = torch.randn(shape, generator=g).to(dtype)
+        w = torch.from_numpy(make_weights([pattern], np.random.RandomState(3))[0]).to(dtype)
+        wk = kb.generate_factor(a, b, c, d, "kernel", w, dtype, DEV)
+        y = kb.Kernel.forward(x.to(DEV), wk, bs_last, a, b, c, d, dtype)
+        ys = (y[:, cols] if bs_last else y[cols]).float().cpu().numpy()
+        xs = (x[:, cols] if bs_last else x[cols]).float().numpy()
+        err = ko.rel_fro_error(ys, ko.factor_apply(xs, w.float().numpy(), bs_last))
+        assert err < TOL[dtype], (pattern, err)
+    kb.check_device()
+
+
+def test_full_batch_linearity_and_determinism_fp32():
+    pattern = (1, 768, 192, 2)
+    a, b, c, d = pattern
+    g = torch.Generator(device="cpu").manual_seed(5)
+    x1 = torch.randn((a * c * d, FULL_B), generator=g).to(DEV)
+    x2 = torch.randn((a * c * d, FULL_B), generator=g).to(DEV)
+    w = torch.from_numpy(make_weights([pattern], np.random.RandomState(4))[0])
+    wk = kb.generate_factor(a, b, c, d, "kernel", w, torch.float32, DEV)
+    f = lambda t: kb.Kernel.forward(t, wk, True, a, b, c, d, torch.float32)  # noqa: E731
+    y1, y2, y12 = f(x1), f(x2), f(x1 + x2)
+    rel = (torch.linalg.norm(y12 - (y1 + y2)) / torch.linalg.norm(y12)).item()
+    assert rel < 1e-5
+    assert torch.equal(f(x1), y1)  # bitwise repeatable
+
+
+def test_full_batch_families_agree_fp16():
+    g = torch.Generator(device="cpu").manual_seed(6)
+    for pattern in [(1, 768, 192, 4), (4, 64, 64, 4)]:
+        a, b, c, d = pattern
+        x = torch.randn((a * c * d, FULL_B), generator=g).half().to(DEV)
+        w = torch.from_numpy(make_weights([pattern], np.random.RandomState(4))[0]).half()
+        wk = kb.generate_factor(a, b, c, d, "kernel", w, torch.float16, DEV)
+        y_tc = kb.forward_ex(x, wk, True, a, b, c, d, algo=_lib.KSMM_ALGO_TC)
+        y_ffma = kb.forward_ex(x, wk, True, a, b, c, d, algo=_lib.KSMM_ALGO_SIMT)
+        rel = (torch.linalg.norm(y_tc.float() - y_ffma.float()) / torch.linalg.norm(y_ffma.float())).item()
+        assert rel < 2e-3, (pattern, rel)   # both round one fp32 sum to fp16
+    kb.check_device()
+
+
+def test_readme_chain_full_batch_fp32():
+    pats = [(6, 64, 64, 1), (1, 768, 192, 2)]
+    rng = np.random.RandomState(8)
+    ws = make_weights(pats, rng)
+    g = torch.Generator(device="cpu").manual_seed(9)
+    x = torch.randn((384, FULL_B), generator=g)
+    layer = kb.KSLinear(pats, weights=[torch.from_numpy(w) for w in ws], bias=False, algo="kernel",
+                        dtype=torch.float32, bs_last=True, device=DEV)
+    y = layer(x.to(DEV))
+    assert tuple(y.shape) == (1536, FULL_B)
+    cols = np.random.RandomState(2).randint(0, FULL_B, 64)
+    ref = ko.chain_apply(x[:, cols].numpy(), ws, True)
+    assert ko.rel_fro_error(y[:, cols].cpu().numpy(), ref) < 1e-5
+
+
+@pytest.mark.parametrize("bs_last", [True, False])
+def test_vit_mlp_chains_full_batch_fp16(bs_last):
+    rng = np.random.RandomState(12)
+    g = torch.Generator(device="cpu").manual_seed(13)
+    for pats in ([(4, 192, 192, 1), (1, 768, 192, 4)], [(1, 192, 768, 4), (4, 192, 192, 1)],
+                 [(1, 64, 64, 16), (4, 64, 64, 4), (16, 64, 64, 1)]):
+        ws = [w.astype(np.float16) for w in make_weights(pats, rng)]
+        n_in = pats[0][0] * pats[0][2] * pats[0][3]
+        x = torch.randn((n_in, FULL_B) if bs_last else (FULL_B, n_in), generator=g).half()
+        layer = kb.KSLinear(pats, weights=[torch.from_numpy(w) for w in ws], bias=True,
+                            algo="kernel", dtype=torch.float16, bs_last=bs_last, device=DEV)
+        y = layer(x.to(DEV))
+        cols = np.random.RandomState(2).randint(0, FULL_B, 32)
+        xs = (x[:, cols] if bs_last else x[cols]).float().numpy()
+        ref = ko.chain_apply(xs, [w.astype(np.float64) for w in ws], bs_last,
+                             bias=layer.bias.float().cpu().numpy(), round_to=np.float16)
+        ys = (y[:, cols] if bs_last else y[cols]).float().cpu().numpy()
+        assert ko.rel_fro_error(ys, ref) < 1e-2, pats
+    kb.check_device()
+
+
+# ---------------------------------------------------------------------------
+# 6. C ABI called directly: host-buffer entry point, tuner, edge cases
+# ---------------------------------------------------------------------------
+def test_chain_forward_host_buffers():
+    lib = _lib.load()
+    pats = [(2, 8, 4, 2), (4, 6, 4, 2)]
+    rng = np.random.RandomState(21)
+    ws = make_weights(pats, rng)
+    for bs_last in (1, 0):
+        batch = 50
+        x = rng.standard_normal((16, batch) if bs_last else (batch, 16)).astype(np.float32)
+        bias = rng.standard_normal(48).astype(np.float32)
+        wk = [ko.abcd_to_kernel_format(w) for w in ws]
+        y = np.full((48, batch) if bs_last else (batch, 48), np.nan, dtype=np.float32)
+        vals = (ctypes.c_void_p * 2)(*[w.ctypes.data for w in wk])
+        flat = _lib.int32_array([v for p in pats for v in p])
+        for _ in range(2):  # second call reuses the library's device buffers
+            st = lib.ksmm_cu_chain_forward_host(x.ctypes.data, vals, y.ctypes.data, bias.ctypes.data,
+                                                batch, 2, flat, _lib.KSMM_F32, bs_last, 0)
+            _lib.check(st)
+            ref = ko.chain_apply(x, ws, bool(bs_last), bias=bias)
+            assert ko.rel_fro_error(y, ref) < 1e-5
+
+
+def test_tuner_picks_a_working_candidate():
+    lib = _lib.load()
+    pattern, batch = (2, 128, 64, 2), 2048
+    a, b, c, d = pattern
+    for dtype in (torch.float32, torch.float16):
+        x, w = _inputs(pattern, batch, dtype, True, seed=31)
+        xg = x.to(DEV)
+        wk = kb.generate_factor(a, b, c, d, "kernel", w, dtype, DEV)
+        out = torch.empty((a * b * d, batch), dtype=dtype, device=DEV)
+        code = kb.kernel.dtype_code(dtype)
+        desc = _lib.ForwardDesc(input=xg.data_ptr(), values=wk.data_ptr(), output=out.data_ptr(),
+                                bias=None, batch=batch, a=a, b=b, c=c, d=d, in_dtype=code,
+                                out_dtype=code, bs_last=1, algo=0, config=-1, alpha=1.0)
+        algo, cfg, ms = ctypes.c_int(), ctypes.c_int(), ctypes.c_float()
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        _lib.check(lib.ksmm_cu_tune(ctypes.byref(desc), 5, stream, ctypes.byref(algo),
+                                    ctypes.byref(cfg), ctypes.byref(ms)))
+        assert algo.value in (_lib.KSMM_ALGO_SIMT, _lib.KSMM_ALGO_TC) and ms.value > 0
+        ga, gc = ctypes.c_int(), ctypes.c_int()
+        assert lib.ksmm_cu_get_choice(batch, a, b, c, d, code, code, 1, ctypes.byref(ga),
+                                      ctypes.byref(gc)) == 0
+        assert (ga.value, gc.value) == (algo.value, cfg.value)
+        y = kb.Kernel.forward(xg, wk, True, a, b, c, d, dtype)  # now served by the cached choice
+        assert ko.rel_fro_error(y.float().cpu().numpy(), _oracle(x, w, True)) < TOL[dtype]
+
+
+def test_edge_batches():
+    for dtype in (torch.float32, torch.float16):
+        for bs_last in (True, False):
+            pattern = (2, 16, 8, 1)
+            a, b, c, d = pattern
+            _, w = _inputs(pattern, 4, dtype, bs_last, seed=1)
+            wk = kb.generate_factor(a, b, c, d, "kernel", w, dtype, DEV)
+            for batch in (0, 1, 2):
+                shape = (a * c * d, batch) if bs_last else (batch, a * c * d)
+                x = torch.randn(shape).to(dtype)
+                y = kb.Kernel.forward(x.to(DEV), wk, bs_last, a, b, c, d, dtype)
+                assert tuple(y.shape) == ((a * b * d, batch) if bs_last else (batch, a * b * d))
+                if batch:
+                    assert ko.rel_fro_error(y.float().cpu().numpy(), _oracle(x, w, bs_last)) < TOL[dtype]
+
+
+def test_ffma_peak_probe_and_launch_counter():
+    lib = _lib.load()
+    before = kb.launch_count()
+    x, w = _inputs((1, 16, 16, 1), 32, torch.float32, True, seed=2)
+    _run(x, w, (1, 16, 16, 1), True)
+    assert kb.launch_count() == before + 1
+    tf = ctypes.c_float()
+    _lib.check(lib.ksmm_cu_measure_ffma_peak(ctypes.byref(tf), None))
+    assert 20.0 < tf.value < 120.0   # B200: 148 SMs x 128 lanes x 2 flop x ~1.9 GHz ~ 72
+    kb.check_device()

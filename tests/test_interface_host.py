@@ -1,0 +1,73 @@
+"""Host-side logic of the Python layer that needs no GPU."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from golden_cases import CASES, make_inputs
+from ksmm_b200 import interface as itf
+from ksmm_b200 import kernel as kmod
+from oracle import ksmm_oracle as ko
+
+GOLDEN = np.load(os.path.join(os.path.dirname(__file__), "golden", "ksmm_golden.npz"))
+
+
+def test_kernel_algo_refuses_cpu_like_the_reference():
+    # interface.py:163-164 of the reference raises Exception("kernel expects device='cuda'.")
+    with pytest.raises(Exception, match="kernel expects device='cuda'"):
+        itf.KSLinear([(1, 4, 4, 1)], algo="kernel", device="cpu")
+
+
+def test_other_algorithms_are_not_silently_emulated():
+    with pytest.raises(NotImplementedError):
+        itf.KSLinear([(1, 4, 4, 1)], algo="dense", device="cuda")
+
+
+def test_mismatched_chain_is_rejected():
+    with pytest.raises(ValueError):
+        itf.KSLinear([(6, 64, 64, 1), (1, 768, 100, 2)], algo="kernel", device="cuda")
+
+
+@pytest.mark.parametrize("name", ["f_1_16_16_1_last", "f_2_3_5_4_last"])
+def test_generate_factor_layout_matches_reference(name):
+    case = next(c for c in CASES if c["name"] == name)
+    _, ws, _ = make_inputs(case)
+    p = case["patterns"][0]
+    wk = itf.generate_factor(*p, "kernel", torch.from_numpy(ws[0]), torch.float32, "cpu")
+    assert np.array_equal(wk.numpy(), GOLDEN[name + "/kernel_format0"])
+    dense = itf.from_kernel_format_to_dense(wk, p)
+    assert np.array_equal(dense.numpy(), GOLDEN[name + "/dense_from_kernel0"])
+    assert np.array_equal(itf.from_kernel_format_to_abcd(wk, p).numpy(), ws[0])
+
+
+def test_default_init_range():
+    wk = itf.generate_factor(2, 8, 16, 3, "kernel", None, torch.float32, "cpu")
+    assert tuple(wk.shape) == (2 * 3 * 16, 8)
+    assert float(wk.abs().max()) <= 0.25 + 1e-6
+
+
+def test_dtype_codes_and_strings():
+    assert kmod.dtype_code(torch.float32) == 0 and kmod.dtype_code("torch.float") == 0
+    assert kmod.dtype_code(torch.float16) == 1 and kmod.dtype_code("torch.half") == 1
+    assert kmod.dtype_code(torch.bfloat16) == 2
+    assert kmod.dtype_code("torch.float8_e4m3fn") == 3
+    with pytest.raises(TypeError):
+        kmod.dtype_code(torch.float64)
+
+
+def test_operator_rejects_cpu_tensors_and_bad_shapes():
+    x = torch.zeros(8, 4)
+    w = torch.zeros(8, 2)
+    with pytest.raises(ValueError, match="CUDA"):
+        kmod.Kernel.forward(x, w, True, 1, 2, 8, 1, torch.float32)
+
+
+def test_quantize_e4m3_matches_oracle():
+    rng = np.random.RandomState(2)
+    x = rng.standard_normal((64, 32)).astype(np.float32)
+    q, s = kmod.quantize_e4m3(torch.from_numpy(x))
+    s_ref = ko.e4m3_scale(x)
+    assert abs(s - s_ref) < 1e-7 * s_ref + 1e-12
+    ref = ko.quantize_e4m3(x.astype(np.float32) / np.float32(s))
+    assert np.array_equal(q.float().numpy(), ref.astype(np.float32))
