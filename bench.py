@@ -54,12 +54,25 @@ def min_bytes_of(p, batch, es):
     return float(es) * (a * c * d * batch + a * b * d * batch + a * b * c * d)
 
 
-def cases():
+def cases(only=None):
+    """Every (dtype, layout, pattern) of the sweep; `only` = "fp16:bs_last:1,768,192,4"
+    (any field may be empty) restricts it, e.g. for a profiler capture of one kernel."""
     out = []
     for dt in DTYPES:
         for bs_last in (True, False):
             for p in PATTERNS:
                 out.append({"pattern": p, "dtype": dt, "bs_last": bs_last})
+    if only:
+        f = (only.split(":") + ["", "", ""])[:3]
+        pat = tuple(int(v) for v in f[2].split(",")) if f[2] else None
+        out = [c for c in out
+               if (not f[0] or c["dtype"] == f[0])
+               and (not f[1] or ("bs_last" if c["bs_last"] else "bs_first") == f[1])
+               and (pat is None or c["pattern"] == pat)]
+        if pat is not None and not out:
+            for dt in ([f[0]] if f[0] else DTYPES):
+                for bl in ([f[1] == "bs_last"] if f[1] else [True, False]):
+                    out.append({"pattern": pat, "dtype": dt, "bs_last": bl})
     return out
 
 
@@ -188,7 +201,7 @@ def run_ours(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     peaks = load_peaks()
-    cs = cases()
+    cs = cases(args.only)
     g = torch.Generator(device="cpu").manual_seed(1234 + rank)
     for c in cs:
         a, b, cc, d = c["pattern"]
@@ -361,11 +374,13 @@ def run_ours(args, rank, world, local_rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--only", default=None,
+                    help='restrict the sweep: "dtype:layout:a,b,c,d", e.g. "fp16:bs_last:1,768,192,4"')
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

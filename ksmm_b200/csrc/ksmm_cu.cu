@@ -90,7 +90,8 @@ static bool lookup_choice(const Problem& p, Choice* out) {
 }
 
 static int check_problem(const Problem& p) {
-  if (!p.in || !p.w || !p.out)
+  // an empty batch has empty (possibly null) input and output buffers
+  if (p.batch != 0 && (!p.in || !p.w || !p.out))
     return set_error(KSMM_ERR_BAD_ARGUMENT, "null pointer (input=%p values=%p output=%p)", p.in,
                      p.w, p.out);
   if (p.a <= 0 || p.b <= 0 || p.c <= 0 || p.d <= 0)
