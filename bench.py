@@ -216,40 +216,42 @@ def run_ours(args, rank, world, local_rank):
         c["bytes"] = min_bytes_of(c["pattern"], BATCH, ESIZE[c["dtype"]])
     step_flops = sum(c["flops"] for c in cs)
 
-    def one_step(events=None):
-        for idx, c in enumerate(cs):
+    def one_step():
+        for c in cs:
             a, b, cc, d = c["pattern"]
-            if events is not None:
-                events[idx][0].record()
             kb.forward_ex(c["x"], c["w"], c["bs_last"], a, b, cc, d, out=c["y"])
-            if events is not None:
-                events[idx][1].record()
 
     def barrier():
         if world > 1:
             torch.distributed.barrier()
 
-    for _ in range(max(args.warmup, 3)):
+    # The step is captured once in a CUDA graph and replayed: the launches are
+    # short (10-500 us), so without a graph the host's launch path would be timed
+    # instead of the kernels.
+    for _ in range(2):
         one_step()
     torch.cuda.synchronize()
     kb.check_device()
+    step_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(step_graph):
+        one_step()
+    for _ in range(max(args.warmup, 3)):
+        step_graph.replay()
+    torch.cuda.synchronize()
 
-    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-           for _ in cs] for _ in range(args.steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(local_rank)
-    launches0 = kb.launch_count()
     barrier()
     torch.cuda.synchronize()
     sampler.start()
     e0.record()
     for s in range(args.steps):
-        one_step(ev[s])
+        step_graph.replay()
     e1.record()
     torch.cuda.synchronize()
     barrier()
     clocks = sampler.stop()
-    launches = kb.launch_count() - launches0
+    launches = args.steps * len(cs)
     elapsed_ms = e0.elapsed_time(e1)
     if world > 1:
         t = torch.tensor([elapsed_ms], device=dev)
@@ -258,13 +260,58 @@ def run_ours(args, rank, world, local_rank):
     kb.check_device()
     value = world * step_flops * args.steps / (elapsed_ms * 1e-3) / 1e12
 
-    # per-case launch durations (CUDA events around each launch, inside the timed region)
+    # Per-case launch duration: a graph of REP launches of the one kernel over
+    # rotating input/output buffers whose combined size exceeds L2, timed with one
+    # CUDA-event pair on the launching stream (event overhead amortised over REP).
+    REP = 20
+    L2_BYTES = 126 * 1024 * 1024
+
+    def case_ms(c, algo=0, config=-1):
+        a, b, cc, d = c["pattern"]
+        foot = c["x"].numel() * c["x"].element_size() + c["y"].numel() * c["y"].element_size()
+        ncopy = min(REP, max(1, -(-2 * L2_BYTES // foot)))
+        xs = [c["x"]] + [c["x"].clone() for _ in range(ncopy - 1)]
+        ys = [c["y"]] + [torch.empty_like(c["y"]) for _ in range(ncopy - 1)]
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for r in range(REP):
+                kb.forward_ex(xs[r % ncopy], c["w"], c["bs_last"], a, b, cc, d, out=ys[r % ncopy],
+                              algo=algo, config=config)
+        g.replay()
+        torch.cuda.synchronize()
+        best = []
+        for _ in range(3):
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            g.replay()
+            s1.record()
+            torch.cuda.synchronize()
+            best.append(s0.elapsed_time(s1) / REP)
+        del g, xs, ys
+        return statistics.median(best)
+
+    if args.sweep_configs:
+        # every tile configuration of both kernel families on every case (tuning aid)
+        for c in cs:
+            code = _lib.KSMM_F32 if c["dtype"] == "fp32" else _lib.KSMM_F16
+            row = []
+            for algo in (_lib.KSMM_ALGO_TC, _lib.KSMM_ALGO_SIMT):
+                for cfg in range(lib.ksmm_cu_num_configs(algo)):
+                    if not lib.ksmm_cu_config_supported(algo, cfg, BATCH, *c["pattern"], code, code,
+                                                        int(c["bs_last"])):
+                        continue
+                    ms = case_ms(c, algo, cfg)
+                    row.append(f"{'tc' if algo == _lib.KSMM_ALGO_TC else 'ffma'}{cfg}={ms * 1e3:.1f}us")
+            if rank == 0:
+                print(c["dtype"], "bs_last" if c["bs_last"] else "bs_first", c["pattern"], " ".join(row),
+                      file=sys.stderr, flush=True)
+
     ffma = ctypes.c_float(0.0)
     _lib.check(lib.ksmm_cu_measure_ffma_peak(ctypes.byref(ffma), None))
     ffma_peak = float(ffma.value)
     per = []
     for idx, c in enumerate(cs):
-        ms = statistics.mean(ev[s][idx][0].elapsed_time(ev[s][idx][1]) for s in range(args.steps))
+        ms = case_ms(c)
         t_hbm = c["bytes"] / (peaks["hbm_gbs"] * 1e9)
         pk = ffma_peak if c["dtype"] == "fp32" else peaks["bf16_tflops"]
         t_fl = c["flops"] / (pk * 1e12)
@@ -379,6 +426,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--sweep-configs", action="store_true",
+                    help="also time every tile configuration of every case (printed to stderr)")
     ap.add_argument("--only", default=None,
                     help='restrict the sweep: "dtype:layout:a,b,c,d", e.g. "fp16:bs_last:1,768,192,4"')
     args = ap.parse_args()

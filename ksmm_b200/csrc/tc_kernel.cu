@@ -2,9 +2,11 @@
 // fp8-e4m3 inputs with fp32 accumulation.
 //
 // One factor with pattern (a,b,c,d) is a*d independent (b x c) blocks, each
-// contracted with a (c x batch) slice of the input.  A work unit is one
-// 128 x NT tile of one block's output; a persistent CTA (one per SM) walks
-// units bid, bid + grid, ... so that the CTAs running at any moment work on
+// contracted with a (c x batch) slice of the input.  A work item is one input
+// tile of one block together with g of the 128 x NT output tiles computed from
+// it; when the whole input tile fits in shared memory it is fetched once per
+// item and only the weights stream.  A persistent CTA (one per SM) walks items
+// bid, bid + grid, ... so that the CTAs running at any moment work on
 // neighbouring tiles and share their operands in L2.
 //
 //   batch-last : D[j (128 rows), n (NT cols)] = W_blk[j,k] * X_blk[k,n]
@@ -21,11 +23,12 @@
 // elements: it converts them, writes 16-byte chunks into a 128-byte-swizzled
 // staging tile, and one thread issues a TMA store of the tile.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocator and
-// single-thread MMA issuer, warps 2..5 = epilogue (TMEM lane quarter =
-// warp index mod 4).  Operand stages form a ring guarded by full/empty
-// mbarriers; the accumulator is double-buffered in TMEM (2 x NT columns) so
-// the epilogue of unit u overlaps the MMAs of unit u+1.
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM allocator and
+// single-thread MMA issuer, warps 2..9 = epilogue (TMEM lane quarter = warp
+// index mod 4; each warp converts and stores its own 32-row sub-tiles, so the
+// epilogue has no block-level barrier).  Input chunk slots and the weight ring
+// are guarded by full/empty mbarriers; the accumulator is double-buffered in
+// TMEM (2 x NT columns) so the epilogue of one tile overlaps the MMAs of the next.
 //
 // Every mbarrier wait is bounded (about two seconds); on expiry the kernel
 // records a code in a device status word, stops issuing work, releases TMEM
@@ -38,6 +41,7 @@
 // (src/ksmm_cu/src/template_kernels_fp8.cuh:22-370).
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "tc_kernel.h"
@@ -48,17 +52,34 @@ namespace tc {
 // one status word per device that loads the module; 0 = no device-side timeout
 __device__ int g_tc_status_word = 0;
 
+#ifdef KSMM_TC_TRACE
+// Diagnostic build only: per-role timestamp log of CTA 0.
+__device__ unsigned long long g_trace[4][8192];
+#define KSMM_TRACE_DECL uint32_t tr_n = 0
+#define KSMM_TRACE(role, ev)                                                              \
+  do {                                                                                    \
+    if (blockIdx.x == 0 && tr_n < 8192)                                                   \
+      g_trace[role][tr_n++] = (static_cast<unsigned long long>(ev) << 48) |               \
+                              (static_cast<unsigned long long>(clock64()) & 0xFFFFFFFFFFFFull); \
+  } while (0)
+#else
+#define KSMM_TRACE_DECL
+#define KSMM_TRACE(role, ev)
+#endif
+
 struct Params {
   int a, b, c, d;
   int64_t batch;
   int tiles_n, tiles_j;
-  int64_t units;
+  uint32_t rows;        // tiles_n * a * d: (block, batch tile) pairs
+  uint32_t row_groups;  // CTAs per j tile; each walks a contiguous range of rows
   int nk;
   uint32_t idesc;
   float alpha;
   const void* bias;
   int out_dtype;
   int* status;
+  int ablate;  // diagnostic: bit0 skip TMA loads, bit1 skip MMAs, bit2 skip epilogue work
 };
 
 // ---------------------------------------------------------------------------
@@ -77,11 +98,15 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+#ifndef KSMM_TEST_WAIT
+#define KSMM_WAIT_OP "mbarrier.try_wait.parity.shared::cta.b64"
+#else
+#define KSMM_WAIT_OP "mbarrier.test_wait.parity.shared::cta.b64"
+#endif
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "{\n\t.reg .pred p;\n\t" KSMM_WAIT_OP " p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
@@ -94,23 +119,30 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
+constexpr long long kWaitLimitCycles = 4000000000ll;  // about two seconds of SM clock
+constexpr int kEpilogueWarps = 8;
+constexpr int kEpilogueThreads = kEpilogueWarps * 32;
+constexpr int kThreads = 64 + kEpilogueThreads;
 
 // Bounded wait.  Returns false after the limit, or as soon as another role has
 // raised the CTA-wide abort flag; the caller then leaves its loop.
+// SLEEP_NS > 0: the waiter is off the critical path (producer, epilogue) and
+// sleeps between polls, so that its polling does not take issue slots and
+// barrier-unit bandwidth from the MMA-issuing thread on the same SM partition.
+template <int SLEEP_NS>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
-#pragma unroll 1
-  for (int q = 0; q < 32; ++q)
-    if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
 #pragma unroll 1
   while (true) {
 #pragma unroll 1
-    for (int q = 0; q < 64; ++q)
+    for (int q = 0; q < 64; ++q) {
       if (mbar_try_wait(bar, parity)) return true;
+      if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
+    }
     if (*abort_flag) return false;
-    if (global_timer_ns() - t0 > kWaitLimitNs) {
+    if (clock64() - t0 > kWaitLimitCycles) {
       *abort_flag = 1;
       atomicCAS(status, 0, code);
       return false;
@@ -212,7 +244,7 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
                    bar)
                : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -259,58 +291,74 @@ __device__ __forceinline__ float bias_at(const void* bias, int64_t idx, int out_
   return __bfloat162float(static_cast<const __nv_bfloat16*>(bias)[idx]);
 }
 
-template <bool BS_LAST, int ES, int OS, int NT, int KC, int ST>
+// WRES = true  ("weight-stationary"): the CTA's weight tile (all NWC k chunks of
+//   it) stays in shared memory while the CTA walks its rows; only input chunks
+//   stream through the ring (SX stages of one chunk each).
+// WRES = false ("streaming"): a ring stage holds one k chunk of both operands
+//   (NWC = 0); used when the weight tile is too large to keep.
+template <bool BS_LAST, int ES, int OS, int NT, int KC, bool WRES, int NWC, int SX>
 struct Cfg {
   static constexpr int NBOX = 128 / ES;        // elements in one 128-byte box row
   static constexpr int UK = 32 / ES;           // k extent of one MMA
-  static constexpr int M_BYTES = 128 * KC * ES;
-  static constexpr int N_BYTES = NT * KC * ES;
-  static constexpr int STAGE_BYTES = M_BYTES + N_BYTES;
+  static constexpr int M_BYTES = 128 * KC * ES;  // one k chunk of the M-side operand
+  static constexpr int N_BYTES = NT * KC * ES;   // one k chunk of the N-side operand
+  static constexpr int XB = BS_LAST ? N_BYTES : M_BYTES;  // input chunk
+  static constexpr int WB = BS_LAST ? M_BYTES : N_BYTES;  // weight chunk
+  static constexpr int STAGE_BYTES = XB + (WRES ? 0 : WB);
   static constexpr int CB = 128 / OS;          // output elements in one staging row
-  static constexpr int STG_BYTES = 128 * 128;
-  static constexpr int BAR_BYTES = 256;
-  static constexpr int SMEM_BYTES = ST * STAGE_BYTES + 2 * STG_BYTES + BAR_BYTES + 1024;
+  static constexpr int STG_WARP_BYTES = 32 * 128;  // one warp's 32 rows x 128 bytes
+  static constexpr int STG_BYTES = kEpilogueWarps * STG_WARP_BYTES;
+  static constexpr int NBAR = 2 * SX + 2 + 4;
+  static constexpr int BAR_BYTES = 512;
+  static constexpr int SMEM_BYTES = NWC * WB + SX * STAGE_BYTES + STG_BYTES + BAR_BYTES + 1024;
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+  static_assert(SMEM_BYTES > 116 * 1024, "one CTA per SM, so that the TMEM allocation never waits");
   static constexpr int TMEM_COLS = 2 * NT;
   static_assert(NT == 64 || NT == 128 || NT == 256, "TMEM allocation must be a power of two");
   static_assert(KC % UK == 0 && KC % 8 == 0, "k chunk");
-  static_assert(BS_LAST || KC == NBOX, "batch-first stages hold one 128-byte k box");
+  static_assert(BS_LAST || KC == NBOX, "batch-first input chunks are one 128-byte k box");
   static_assert(NT % NBOX == 0, "N tile must be whole 128-byte box rows");
-  static_assert(2 * ST + 4 <= 24, "barrier area");
+  static_assert(8 * NBAR + 16 <= BAR_BYTES, "barrier area");
+  static_assert(WRES ? NWC > 0 : NWC == 0, "resident weight chunks exist in weight-stationary mode only");
 };
 
-template <bool BS_LAST, int ES, int OS, int NT, int KC, int ST>
-__global__ void __launch_bounds__(192, 1)
+template <bool BS_LAST, int ES, int OS, int NT, int KC, bool WRES, int NWC, int SX>
+__global__ void __launch_bounds__(kThreads, 1)
     ksmm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
                    const __grid_constant__ CUtensorMap tmY, const Params P) {
-  using C = Cfg<BS_LAST, ES, OS, NT, KC, ST>;
+  using C = Cfg<BS_LAST, ES, OS, NT, KC, WRES, NWC, SX>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t sm0 = (raw + 1023u) & ~1023u;  // 1024-byte alignment for the 128-byte swizzle
   uint8_t* sm_gen = smem_raw + (sm0 - raw);
-  const uint32_t stg0 = sm0 + ST * C::STAGE_BYTES;
-  const uint32_t bar0 = stg0 + 2 * C::STG_BYTES;
-  uint8_t* bar_gen = sm_gen + ST * C::STAGE_BYTES + 2 * C::STG_BYTES;
+  const uint32_t wres0 = sm0;                           // resident weight tile (weight-stationary)
+  const uint32_t ring0 = wres0 + NWC * C::WB;           // stage ring
+  const uint32_t stg0 = ring0 + SX * C::STAGE_BYTES;    // epilogue staging, one tile per warp
+  const uint32_t bar0 = stg0 + C::STG_BYTES;
+  uint8_t* bar_gen = sm_gen + NWC * C::WB + SX * C::STAGE_BYTES + C::STG_BYTES;
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
-  auto empty_bar = [&](int s) { return bar0 + 8u * (ST + s); };
-  auto tfull_bar = [&](int q) { return bar0 + 8u * (2 * ST + q); };
-  auto tempty_bar = [&](int q) { return bar0 + 8u * (2 * ST + 2 + q); };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * (2 * ST + 4));
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 8 * (2 * ST + 4) + 4);
-  volatile int* epi_abort = reinterpret_cast<volatile int*>(bar_gen + 8 * (2 * ST + 4) + 8);
+  auto empty_bar = [&](int s) { return bar0 + 8u * (SX + s); };
+  const uint32_t wfull_bar = bar0 + 8u * (2 * SX);
+  const uint32_t wempty_bar = bar0 + 8u * (2 * SX + 1);
+  auto tfull_bar = [&](int q) { return bar0 + 8u * (2 * SX + 2 + q); };
+  auto tempty_bar = [&](int q) { return bar0 + 8u * (2 * SX + 4 + q); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * C::NBAR);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 8 * C::NBAR + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < ST; ++s) {
+    for (int s = 0; s < SX; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
+    mbar_init(wfull_bar, 1);
+    mbar_init(wempty_bar, 1);
     for (int q = 0; q < 2; ++q) {
       mbar_init(tfull_bar(q), 1);
-      mbar_init(tempty_bar(q), 128);
+      mbar_init(tempty_bar(q), kEpilogueWarps);
     }
     *abort_flag = 0;
-    *epi_abort = 0;
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -322,50 +370,64 @@ __global__ void __launch_bounds__(192, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int d = P.d;
-  const int64_t units = P.units;
+  // Work split: CTA c keeps one j tile (tj = c mod tiles_j) and walks a
+  // contiguous range of rows, a row being one (block, batch tile) pair.  CTAs
+  // that differ only in tj walk the same rows at the same time and share the
+  // input tile in L2; the weight tile changes only when the block changes.
+  const uint32_t d = P.d;
   const int nk = P.nk;
-
-  // unit -> (j tile fastest, then batch tile, then block): neighbouring CTAs
-  // share the input slice (batch-last) or the input rows (batch-first)
-  auto decode = [&](int64_t u, int& tj, int& tn, int& blk) {
-    tj = static_cast<int>(u % P.tiles_j);
-    const int64_t r = u / P.tiles_j;
-    tn = static_cast<int>(r % P.tiles_n);
-    blk = static_cast<int>(r / P.tiles_n);
-  };
+  const int tj = static_cast<int>(blockIdx.x % P.tiles_j);
+  const uint32_t rc = blockIdx.x / P.tiles_j;
+  const uint32_t row_begin = static_cast<uint32_t>(static_cast<uint64_t>(rc) * P.rows / P.row_groups);
+  const uint32_t row_end = static_cast<uint32_t>(static_cast<uint64_t>(rc + 1) * P.rows / P.row_groups);
+  const int j0 = tj * (BS_LAST ? 128 : NT);
 
   if (warp == 0) {
     // ===================== TMA producer =====================
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t si = 0, sph = 0, wph = 0;  // ring position / phase, weight-tile phase
+      int cur_blk = -1;
+      KSMM_TRACE_DECL;
       bool ok = true;
-      for (int64_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
-        int tj, tn, blk;
-        decode(u, tj, tn, blk);
+      for (uint32_t row = row_begin; row < row_end && ok; ++row) {
+        const int blk = static_cast<int>(row / P.tiles_n);
+        const int tn = static_cast<int>(row % P.tiles_n);
         const int i = blk / d, l = blk % d;
         const int n0 = tn * (BS_LAST ? NT : 128);
-        const int j0 = tj * (BS_LAST ? 128 : NT);
-        for (int kc = 0; kc < nk; ++kc, ++it) {
-          const int s = it % ST;
-          const uint32_t ph = (it / ST) & 1u;
-          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, P.status, 1)) { ok = false; break; }
-          mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
-          const uint32_t mdst = sm0 + s * C::STAGE_BYTES;
-          const uint32_t ndst = mdst + C::M_BYTES;
+        if (WRES && blk != cur_blk) {
+          // new block: fetch its weight tile once the MMAs on the old one are done
+          if (!mbar_wait<64>(wempty_bar, wph ^ 1u, abort_flag, P.status, 1)) { ok = false; break; }
+          wph ^= 1u;
+          mbar_expect_tx(wfull_bar, nk * C::WB);
+          for (int kc = 0; kc < nk; ++kc) {
+#pragma unroll
+            for (int wb = 0; wb < (BS_LAST ? 128 : NT) / C::NBOX; ++wb)
+              tma_load_3d(wres0 + kc * C::WB + wb * KC * 128, &tmW, wfull_bar, j0 + wb * C::NBOX,
+                          kc * KC, blk);
+          }
+          cur_blk = blk;
+        }
+        for (int kc = 0; kc < nk; ++kc) {
+          KSMM_TRACE(0, 3);
+          if (!mbar_wait<64>(empty_bar(si), sph ^ 1u, abort_flag, P.status, 2)) { ok = false; break; }
+          KSMM_TRACE(0, 4);
+          const uint32_t dst = ring0 + si * C::STAGE_BYTES;
+          const uint32_t bar = full_bar(si);
+          mbar_expect_tx(bar, C::STAGE_BYTES);
           if constexpr (BS_LAST) {
 #pragma unroll
-            for (int wb = 0; wb < 128 / C::NBOX; ++wb)
-              tma_load_3d(mdst + wb * KC * 128, &tmW, full_bar(s), j0 + wb * C::NBOX, kc * KC, blk);
-#pragma unroll
             for (int xb = 0; xb < NT / C::NBOX; ++xb)
-              tma_load_4d(ndst + xb * KC * 128, &tmX, full_bar(s), n0 + xb * C::NBOX, l, kc * KC, i);
+              tma_load_4d(dst + xb * KC * 128, &tmX, bar, n0 + xb * C::NBOX, l, kc * KC, i);
           } else {
-            tma_load_3d(mdst, &tmX, full_bar(s), kc * KC, i, n0);
-#pragma unroll
-            for (int wb = 0; wb < NT / C::NBOX; ++wb)
-              tma_load_3d(ndst + wb * KC * 128, &tmW, full_bar(s), j0 + wb * C::NBOX, kc * KC, blk);
+            tma_load_3d(dst, &tmX, bar, kc * KC, i, n0);
           }
+          if constexpr (!WRES) {
+#pragma unroll
+            for (int wb = 0; wb < (BS_LAST ? 128 : NT) / C::NBOX; ++wb)
+              tma_load_3d(dst + C::XB + wb * KC * 128, &tmW, bar, j0 + wb * C::NBOX, kc * KC, blk);
+          }
+          KSMM_TRACE(0, 5);
+          if (++si == SX) { si = 0; sph ^= 1u; }
         }
       }
     }
@@ -373,136 +435,174 @@ __global__ void __launch_bounds__(192, 1)
   } else if (warp == 1) {
     // ===================== MMA issuer =====================
     if (lane == 0) {
-      uint32_t it = 0, ut = 0;
+      // descriptor words that never change: SBO = 1024 bytes, version 1, 128-byte swizzle
+      constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+      constexpr uint32_t kLboMN = static_cast<uint32_t>((KC * 128) >> 4) << 16;  // MN-major operands
+      constexpr uint32_t kLboK = 1u << 16;                                       // unused for K-major
+      constexpr uint32_t kStepMN = (C::UK * 128) >> 4;  // descriptor address step per MMA, MN-major
+      constexpr uint32_t kStepK = (C::UK * ES) >> 4;    // K-major: UK elements inside the swizzle row
+      const uint32_t idesc = P.idesc;
+      uint32_t si = 0, sph = 0, wph = 0, ut = 0;
+      int cur_blk = -1;
       bool ok = true;
-      for (int64_t u = blockIdx.x; u < units && ok; u += gridDim.x, ++ut) {
+      KSMM_TRACE_DECL;
+      for (uint32_t row = row_begin; row < row_end && ok; ++row, ++ut) {
+        const int blk = static_cast<int>(row / P.tiles_n);
+        if (WRES && blk != cur_blk) {
+          if (!mbar_wait<0>(wfull_bar, wph, abort_flag, P.status, 3)) { ok = false; break; }
+          wph ^= 1u;
+          cur_blk = blk;
+        }
         const uint32_t buf = ut & 1u, bph = (ut >> 1) & 1u;
-        if (!mbar_wait(tempty_bar(buf), bph ^ 1u, abort_flag, P.status, 2)) { ok = false; break; }
+        KSMM_TRACE(1, 10);
+        if (!mbar_wait<0>(tempty_bar(buf), bph ^ 1u, abort_flag, P.status, 4)) { ok = false; break; }
         tc_fence_after();
+        KSMM_TRACE(1, 11);
         const uint32_t dcol = tmem_base + buf * NT;
-        for (int kc = 0; kc < nk; ++kc, ++it) {
-          const int s = it % ST;
-          const uint32_t ph = (it / ST) & 1u;
-          if (!mbar_wait(full_bar(s), ph, abort_flag, P.status, 3)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t mdst = sm0 + s * C::STAGE_BYTES;
-          const uint32_t ndst = mdst + C::M_BYTES;
+        for (int kc = 0; kc < nk; ++kc) {
+          KSMM_TRACE(1, 14);
+          if (!mbar_wait<0>(full_bar(si), sph, abort_flag, P.status, 5)) { ok = false; break; }
+          KSMM_TRACE(1, 15);
+          const uint32_t xsrc = ring0 + si * C::STAGE_BYTES;
+          const uint32_t wsrc = WRES ? wres0 + kc * C::WB : xsrc + C::XB;
+          const uint32_t xlo = (xsrc >> 4) | (BS_LAST ? kLboMN : kLboK);
+          const uint32_t wlo = (wsrc >> 4) | kLboMN;
 #pragma unroll
           for (int k = 0; k < KC / C::UK; ++k) {
-            uint64_t adesc, bdesc;
-            if constexpr (BS_LAST) {
-              adesc = make_desc(mdst + k * C::UK * 128, KC * 128, 1024);
-            } else {
-              adesc = make_desc(mdst + k * C::UK * ES, 16, 1024);
-            }
-            bdesc = make_desc(ndst + k * C::UK * 128, KC * 128, 1024);
-            umma<ES>(dcol, adesc, bdesc, P.idesc, (kc | k) != 0 ? 1u : 0u);
+            const uint32_t xl = xlo + k * (BS_LAST ? kStepMN : kStepK);
+            const uint32_t wl = wlo + k * kStepMN;
+            const uint64_t xdesc = (static_cast<uint64_t>(kDescHi) << 32) | xl;
+            const uint64_t wdesc = (static_cast<uint64_t>(kDescHi) << 32) | wl;
+            // batch-last: A = weights, B = input slice; batch-first: A = input rows, B = weights
+            umma<ES>(dcol, BS_LAST ? wdesc : xdesc, BS_LAST ? xdesc : wdesc, idesc,
+                     (kc | k) != 0 ? 1u : 0u);
           }
-          umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+          umma_commit(empty_bar(si));  // frees the stage once these MMAs have read it
+          KSMM_TRACE(1, 16);
+          if (++si == SX) { si = 0; sph ^= 1u; }
         }
-        if (ok) umma_commit(tfull_bar(buf));  // accumulator complete
+        if (!ok) break;
+        umma_commit(tfull_bar(buf));  // accumulator complete
+        KSMM_TRACE(1, 17);
+        if (WRES && (row + 1 == row_end || static_cast<int>((row + 1) / P.tiles_n) != blk))
+          umma_commit(wempty_bar);  // last use of this weight tile
       }
     }
     __syncwarp();
   } else {
     // ===================== epilogue =====================
-    const int q = warp & 3;  // TMEM lane quarter this warp may access
-    const int row = q * 32 + lane;
-    const int epi_tid = (warp - 2) * 32 + lane;
+    // Warp w owns TMEM lane quarter w mod 4 (32 output rows) and the column boxes
+    // (w - 2) / 4, (w - 2) / 4 + kEpilogueWarps / 4, ...  Each warp converts its
+    // 32 x CB sub-tile into its own swizzled staging tile and issues its own TMA
+    // store, so the epilogue needs no block-level barrier.
+    const int ew = warp - 2;
+    const int q = warp & 3;
+    const int grp = ew >> 2;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
-    uint32_t ut = 0, stg_count = 0;
-    for (int64_t u = blockIdx.x; u < units; u += gridDim.x, ++ut) {
-      const uint32_t buf = ut & 1u, bph = (ut >> 1) & 1u;
-      int tj, tn, blk;
-      decode(u, tj, tn, blk);
+    const bool plain = (P.alpha == 1.f) && (P.bias == nullptr);
+    const uint32_t stg = stg0 + ew * C::STG_WARP_BYTES;
+    uint32_t ut = 0;
+    KSMM_TRACE_DECL;
+    const int trole = (ew == 0) ? 2 : 3;
+    const bool tron = (ew == 0 || ew == 5) && lane == 0;
+    (void)trole; (void)tron;
+    for (uint32_t row = row_begin; row < row_end; ++row, ++ut) {
+      const int blk = static_cast<int>(row / P.tiles_n);
+      const int tn = static_cast<int>(row % P.tiles_n);
       const int i = blk / d, l = blk % d;
       const int n0 = tn * (BS_LAST ? NT : 128);
-      const int j0 = tj * (BS_LAST ? 128 : NT);
-      if (!mbar_wait(tfull_bar(buf), bph, abort_flag, P.status, 4)) *epi_abort = 1;
-      bar_sync_named(1, 128);
-      if (*epi_abort) break;
+      const uint32_t buf = ut & 1u, bph = (ut >> 1) & 1u;
+      if (tron) KSMM_TRACE(trole, 20);
+      int got = 1;
+      if (lane == 0) got = mbar_wait<128>(tfull_bar(buf), bph, abort_flag, P.status, 6) ? 1 : 0;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (!got) break;
       tc_fence_after();
+      if (tron) KSMM_TRACE(trole, 21);
       // rows of this warp that exist (warp-uniform): j rows (batch-last) or batch rows
-      const int64_t row_limit = BS_LAST ? static_cast<int64_t>(P.b) - j0 : P.batch - n0;
+      const int row_limit = BS_LAST ? P.b - j0 : static_cast<int>(min(P.batch - n0, static_cast<int64_t>(128)));
       const bool warp_active = (q * 32) < row_limit;
-      const int64_t col_limit = BS_LAST ? P.batch - n0 : static_cast<int64_t>(P.b) - j0;
+      const int col_limit = BS_LAST ? static_cast<int>(min(P.batch - n0, static_cast<int64_t>(NT))) : P.b - j0;
       float bias_row = 0.f;
-      if (BS_LAST && P.bias != nullptr && row < row_limit)
-        bias_row = bias_at(P.bias, (static_cast<int64_t>(i) * P.b + j0 + row) * d + l, P.out_dtype);
+      if (BS_LAST && P.bias != nullptr && q * 32 + lane < row_limit)
+        bias_row = bias_at(P.bias, (static_cast<int64_t>(i) * P.b + j0 + q * 32 + lane) * d + l,
+                           P.out_dtype);
+      if (warp_active && !(P.ablate & 4)) {
 #pragma unroll 1
-      for (int cbi = 0; cbi < NT / C::CB; ++cbi) {
-        if (static_cast<int64_t>(cbi) * C::CB >= col_limit) break;  // uniform
-        const uint32_t sb = stg_count & 1u;
-        ++stg_count;
-        if (epi_tid == 0) bulk_wait_read<1>();  // the store that last used this buffer has read it
-        bar_sync_named(1, 128);
-        const uint32_t stg = stg0 + sb * C::STG_BYTES;
-        if (warp_active) {
+        for (int cbi = grp; cbi < NT / C::CB; cbi += kEpilogueWarps / 4) {
+          if (cbi * C::CB >= col_limit) break;
+          if (lane == 0) bulk_wait_read<0>();  // this warp's previous store has read the tile
+          __syncwarp();
+          uint32_t r[C::CB];
 #pragma unroll
-          for (int h = 0; h < C::CB / 32; ++h) {
-            uint32_t r[32];
-            tmem_ld32(tmem_base + lane_addr + buf * NT + cbi * C::CB + h * 32, r);
-            tmem_ld_wait();
-            float v[32];
+          for (int h = 0; h < C::CB / 32; ++h)
+            tmem_ld32(tmem_base + lane_addr + buf * NT + cbi * C::CB + h * 32, r + h * 32);
+          tmem_ld_wait();
+          if (tron) KSMM_TRACE(trole, 23);
+          if (!plain) {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
+            for (int e = 0; e < C::CB; ++e) {
               float bv = bias_row;
               if (!BS_LAST && P.bias != nullptr) {
-                const int col = cbi * C::CB + h * 32 + e;
+                const int col = cbi * C::CB + e;
                 bv = col < col_limit
                          ? bias_at(P.bias, static_cast<int64_t>(i) * P.b + j0 + col, P.out_dtype)
                          : 0.f;
               }
-              v[e] = fmaf(P.alpha, __uint_as_float(r[e]), bv);
-            }
-            const uint32_t rowaddr = stg + row * 128;
-            if constexpr (OS == 2) {
-#pragma unroll
-              for (int ch = 0; ch < 4; ++ch) {
-                uint32_t w0 = pack2(v[ch * 8 + 0], v[ch * 8 + 1], P.out_dtype);
-                uint32_t w1 = pack2(v[ch * 8 + 2], v[ch * 8 + 3], P.out_dtype);
-                uint32_t w2 = pack2(v[ch * 8 + 4], v[ch * 8 + 5], P.out_dtype);
-                uint32_t w3 = pack2(v[ch * 8 + 6], v[ch * 8 + 7], P.out_dtype);
-                const uint32_t chunk = static_cast<uint32_t>((h * 4 + ch) ^ (row & 7));
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + chunk * 16),
-                             "r"(w0), "r"(w1), "r"(w2), "r"(w3)
-                             : "memory");
-              }
-            } else {
-#pragma unroll
-              for (int ch = 0; ch < 8; ++ch) {
-                const uint32_t chunk = static_cast<uint32_t>(ch ^ (row & 7));
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + chunk * 16),
-                             "r"(__float_as_uint(v[ch * 4 + 0])), "r"(__float_as_uint(v[ch * 4 + 1])),
-                             "r"(__float_as_uint(v[ch * 4 + 2])), "r"(__float_as_uint(v[ch * 4 + 3]))
-                             : "memory");
-              }
+              r[e] = __float_as_uint(fmaf(P.alpha, __uint_as_float(r[e]), bv));
             }
           }
-        }
-        fence_proxy_async();
-        bar_sync_named(1, 128);
-        if (epi_tid == 0) {
-          if constexpr (BS_LAST) {
-            tma_store_4d(&tmY, stg, n0 + cbi * C::CB, l, j0, i);
+          const uint32_t rowaddr = stg + lane * 128;
+          if constexpr (OS == 2) {
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                w[e] = pack2(__uint_as_float(r[ch * 8 + 2 * e]),
+                             __uint_as_float(r[ch * 8 + 2 * e + 1]), P.out_dtype);
+              const uint32_t chunk = static_cast<uint32_t>(ch ^ (lane & 7));
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + chunk * 16),
+                           "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                           : "memory");
+            }
           } else {
-            tma_store_3d(&tmY, stg, j0 + cbi * C::CB, i, n0);
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+              const uint32_t chunk = static_cast<uint32_t>(ch ^ (lane & 7));
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + chunk * 16),
+                           "r"(r[ch * 4 + 0]), "r"(r[ch * 4 + 1]), "r"(r[ch * 4 + 2]),
+                           "r"(r[ch * 4 + 3])
+                           : "memory");
+            }
           }
-          bulk_commit();
+          fence_proxy_async();
+          __syncwarp();
+          if (tron) KSMM_TRACE(trole, 25);
+          if (lane == 0) {
+            if constexpr (BS_LAST) {
+              tma_store_4d(&tmY, stg, n0 + cbi * C::CB, l, j0 + q * 32, i);
+            } else {
+              tma_store_3d(&tmY, stg, j0 + cbi * C::CB, i, n0 + q * 32);
+            }
+            bulk_commit();
+          }
         }
       }
-      // this thread's TMEM reads of the buffer are complete: hand it back
+      // this warp's TMEM reads of the buffer are complete: hand it back
       tc_fence_before();
-      mbar_arrive(tempty_bar(buf));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(buf));
+      if (tron) KSMM_TRACE(trole, 27);
     }
-    if (epi_tid == 0) bulk_wait<0>();  // all stores have left shared memory and are visible
+    if (lane == 0) bulk_wait<0>();  // all stores have left shared memory and are visible
     __syncwarp();
   }
 
   // ===================== teardown =====================
   tc_fence_before();
   __syncthreads();
-  if (*abort_flag || *epi_abort) {
+  if (*abort_flag) {
     // give copies that may still be in flight time to land before the CTA's
     // shared memory is handed to another CTA
     __nanosleep(20000);
@@ -596,10 +696,10 @@ static int num_sms() {
   return sms[dev];
 }
 
-template <bool BS_LAST, int ES, int OS, int NT, int KC, int ST>
+template <bool BS_LAST, int ES, int OS, int NT, int KC, bool WRES, int NWC, int SX>
 static int launch_one(const Problem& p, cudaStream_t stream) {
-  using C = Cfg<BS_LAST, ES, OS, NT, KC, ST>;
-  auto kern = ksmm_tc_kernel<BS_LAST, ES, OS, NT, KC, ST>;
+  using C = Cfg<BS_LAST, ES, OS, NT, KC, WRES, NWC, SX>;
+  auto kern = ksmm_tc_kernel<BS_LAST, ES, OS, NT, KC, WRES, NWC, SX>;
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -629,6 +729,10 @@ static int launch_one(const Problem& p, cudaStream_t stream) {
   P.bias = p.bias;
   P.out_dtype = p.out_dtype;
   P.status = status_word();
+  {
+    static const int ablate = [] { const char* e = getenv("KSMM_TC_ABLATE"); return e ? atoi(e) : 0; }();
+    P.ablate = ablate;
+  }
   if (!P.status) return set_error(KSMM_ERR_CUDA, "cannot resolve the device status word");
   const uint32_t fmt = p.in_dtype == KSMM_BF16 ? 1u : 0u;  // f16 / e4m3 = 0, bf16 = 1
   uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) |
@@ -641,7 +745,7 @@ static int launch_one(const Problem& p, cudaStream_t stream) {
     if ((st = encode_map(&tmX, p.in_dtype, 4, p.in, xd, xs, xb)) != KSMM_OK) return st;
     const uint64_t yd[4] = {B, d, b, a};
     const uint64_t ys[4] = {1, B, d * B, b * d * B};
-    const uint32_t yb[4] = {static_cast<uint32_t>(C::CB), 1, 128, 1};
+    const uint32_t yb[4] = {static_cast<uint32_t>(C::CB), 1, 32, 1};  // one epilogue warp's rows
     if ((st = encode_map(&tmY, p.out_dtype, 4, p.out, yd, ys, yb)) != KSMM_OK) return st;
     P.tiles_n = static_cast<int>((B + NT - 1) / NT);
     P.tiles_j = static_cast<int>((b + 127) / 128);
@@ -652,17 +756,25 @@ static int launch_one(const Problem& p, cudaStream_t stream) {
     if ((st = encode_map(&tmX, p.in_dtype, 3, p.in, xd, xs, xb)) != KSMM_OK) return st;
     const uint64_t yd[3] = {b, a, B};
     const uint64_t ys[3] = {1, b, a * b};
-    const uint32_t yb[3] = {static_cast<uint32_t>(C::CB), 1, 128};
+    const uint32_t yb[3] = {static_cast<uint32_t>(C::CB), 1, 32};
     if ((st = encode_map(&tmY, p.out_dtype, 3, p.out, yd, ys, yb)) != KSMM_OK) return st;
     P.tiles_n = static_cast<int>((B + 127) / 128);
     P.tiles_j = static_cast<int>((b + NT - 1) / NT);
   }
   P.idesc = idesc;
-  P.units = static_cast<int64_t>(P.tiles_n) * P.tiles_j * p.a * p.d;
   const int sms = num_sms();
   if (sms <= 0) return set_error(KSMM_ERR_NO_DEVICE, "no CUDA device");
-  const unsigned grid = static_cast<unsigned>(P.units < sms ? P.units : sms);
-  kern<<<grid, 192, C::SMEM_BYTES, stream>>>(tmX, tmW, tmY, P);
+  const int64_t rows = static_cast<int64_t>(P.tiles_n) * p.a * p.d;
+  if (rows <= 0 || rows > 0x7fffffffLL || P.tiles_j > sms)
+    return set_error(KSMM_ERR_UNSUPPORTED,
+                     "tensor-core family: %lld rows x %d j tiles exceed the work-split limits",
+                     static_cast<long long>(rows), P.tiles_j);
+  P.rows = static_cast<uint32_t>(rows);
+  int64_t groups = sms / P.tiles_j;
+  if (groups > rows) groups = rows;
+  P.row_groups = static_cast<uint32_t>(groups);
+  const unsigned grid = static_cast<unsigned>(groups * P.tiles_j);
+  kern<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tmX, tmW, tmY, P);
   count_launch();
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess)
@@ -670,27 +782,40 @@ static int launch_one(const Problem& p, cudaStream_t stream) {
   return KSMM_OK;
 }
 
+// Tile configurations.  Each has a weight-stationary and a streaming flavour;
+// the first is used when all k chunks of the weight tile fit in its NWC slots.
+//   <layout, ES, OS, N tile, bytes of k per chunk row, resident weight chunks,
+//    ring stages (weight-stationary), ring stages (streaming)>
+template <bool BS_LAST, int ES, int OS, int NT, int KCB, int NWC, int SX_W, int SX_S>
+static int launch_flavour(const Problem& p, cudaStream_t stream) {
+  constexpr int KC = KCB / ES;
+  const int nk = (p.c + KC - 1) / KC;
+  if (nk <= NWC) return launch_one<BS_LAST, ES, OS, NT, KC, true, NWC, SX_W>(p, stream);
+  return launch_one<BS_LAST, ES, OS, NT, KC, false, 0, SX_S>(p, stream);
+}
+
 template <bool BS_LAST, int ES, int OS>
 static int launch_cfg(const Problem& p, int config, cudaStream_t stream) {
-  constexpr int R = ES == 2 ? 1 : 2;  // k rows per stage scale with 1 / element size
+  // batch-last, 16-bit: input chunk = NT x 64 x 2 bytes, weight chunk = 16 KB
+  // batch-first, 16-bit: input chunk = 16 KB, weight chunk = NT x 64 x 2 bytes
   if constexpr (BS_LAST) {
     switch (config) {
-      case 0: return launch_one<true, ES, OS, 256, 64 * R, 3>(p, stream);
-      case 1: return launch_one<true, ES, OS, 128, 64 * R, 4>(p, stream);
-      case 2: return launch_one<true, ES, OS, 256, 32 * R, 4>(p, stream);
-      case 3: return launch_one<true, ES, OS, 128, 32 * R, 6>(p, stream);
+      case 0: return launch_flavour<true, ES, OS, 256, 128, 3, 4, 4>(p, stream);
+      case 1: return launch_flavour<true, ES, OS, 128, 128, 6, 6, 6>(p, stream);
+      case 2: return launch_flavour<true, ES, OS, 256, 128, 1, 5, 4>(p, stream);
+      case 3: return launch_flavour<true, ES, OS, 128, 128, 3, 8, 6>(p, stream);
       case 4:
-        if constexpr (ES == 2) return launch_one<true, ES, OS, 64, 64 * R, 4>(p, stream);
+        if constexpr (ES == 2) return launch_flavour<true, ES, OS, 64, 128, 6, 8, 8>(p, stream);
         break;
     }
   } else {
     switch (config) {
-      case 0: return launch_one<false, ES, OS, 256, 64 * R, 3>(p, stream);
-      case 1: return launch_one<false, ES, OS, 128, 64 * R, 4>(p, stream);
-      case 2: return launch_one<false, ES, OS, 256, 64 * R, 4>(p, stream);
-      case 3: return launch_one<false, ES, OS, 128, 64 * R, 6>(p, stream);
+      case 0: return launch_flavour<false, ES, OS, 256, 128, 3, 6, 4>(p, stream);
+      case 1: return launch_flavour<false, ES, OS, 128, 128, 6, 6, 6>(p, stream);
+      case 2: return launch_flavour<false, ES, OS, 256, 128, 1, 10, 4>(p, stream);
+      case 3: return launch_flavour<false, ES, OS, 128, 128, 3, 8, 6>(p, stream);
       case 4:
-        if constexpr (ES == 2) return launch_one<false, ES, OS, 64, 64 * R, 4>(p, stream);
+        if constexpr (ES == 2) return launch_flavour<false, ES, OS, 64, 128, 6, 8, 8>(p, stream);
         break;
     }
   }
@@ -756,6 +881,17 @@ int tc_launch(const Problem& p, int config, cudaStream_t stream) {
               : tc::launch_cfg<false, 2, 2>(p, config, stream);
 }
 
+#ifdef KSMM_TC_TRACE
+extern "C" __attribute__((visibility("default"))) int ksmm_debug_trace(unsigned long long* host) {
+  cudaDeviceSynchronize();
+  return static_cast<int>(cudaMemcpyFromSymbol(host, tc::g_trace, sizeof(tc::g_trace)));
+}
+extern "C" __attribute__((visibility("default"))) int ksmm_debug_trace_clear() {
+  static unsigned long long zeros[4][8192];
+  return static_cast<int>(cudaMemcpyToSymbol(tc::g_trace, zeros, sizeof(zeros)));
+}
+#endif
+
 int tc_check_device(cudaStream_t stream) {
   cudaError_t e = cudaStreamSynchronize(stream);
   if (e != cudaSuccess)
@@ -771,8 +907,9 @@ int tc_check_device(cudaStream_t stream) {
     int zero = 0;
     cudaMemcpy(w, &zero, sizeof(int), cudaMemcpyHostToDevice);
     return set_error(KSMM_ERR_DEVICE_TIMEOUT,
-                     "a tensor-core kernel gave up waiting (role code %d: 1 producer/empty, "
-                     "2 mma/tmem-empty, 3 mma/full, 4 epilogue/tmem-full)",
+                     "a tensor-core kernel gave up waiting (code %d: 1 producer/input slot, "
+                     "2 producer/weight stage, 3 mma/accumulator, 4 mma/input, 5 mma/weights, "
+                     "6 epilogue/accumulator)",
                      code);
   }
   return KSMM_OK;
