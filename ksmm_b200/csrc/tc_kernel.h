@@ -17,4 +17,8 @@ int tc_launch(const Problem& p, int config, cudaStream_t stream);
 // earlier launch of this family on the current device (then clears it).
 int tc_check_device(cudaStream_t stream);
 
+// batch-first factors with d = 2 or 4 (tc_bsfirst_d.cu); a single configuration
+bool tc_bsfirst_d_supported(const Problem& p, bool check_pointers);
+int tc_bsfirst_d_launch(const Problem& p, cudaStream_t stream);
+
 }  // namespace ksmm

@@ -155,10 +155,27 @@ def test_tc_family_batch_first(config, dtype):
     kb.check_device()
 
 
+TC_PATTERNS_FIRST_D = [(1, 64, 64, 2), (2, 128, 32, 4), (1, 768, 192, 4), (1, 192, 768, 4),
+                       (1, 768, 192, 2), (3, 48, 80, 2), (1, 136, 72, 4), (4, 64, 64, 4), (2, 8, 200, 4)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_tc_family_batch_first_interleaved_blocks(dtype):
+    """Batch-first with d = 2 or 4: in-kernel split of the interleaved input by block."""
+    for pi, pattern in enumerate(TC_PATTERNS_FIRST_D):
+        for batch in (8, 136, 520):
+            x, w = _inputs(pattern, batch, dtype, False, seed=400 + pi)
+            y = _run(x, w, pattern, False, algo=_lib.KSMM_ALGO_TC, config=0)
+            assert not np.isnan(y).any(), (pattern, batch)
+            err = ko.rel_fro_error(y, _oracle(x, w, False))
+            assert err < TOL[dtype], (pattern, batch, err)
+    kb.check_device()
+
+
 def test_tc_refuses_what_it_cannot_run():
-    x, w = _inputs((1, 64, 64, 2), 16, torch.float16, False, seed=1)  # batch-first with d > 1
+    x, w = _inputs((1, 64, 64, 3), 16, torch.float16, False, seed=1)  # batch-first with d = 3
     with pytest.raises(kb.KsmmError) as ei:
-        _run(x, w, (1, 64, 64, 2), False, algo=_lib.KSMM_ALGO_TC, config=0)
+        _run(x, w, (1, 64, 64, 3), False, algo=_lib.KSMM_ALGO_TC, config=0)
     assert ei.value.status == _lib.KSMM_ERR_UNSUPPORTED
     x, w = _inputs((1, 64, 64, 1), 16, torch.float32, True, seed=1)
     with pytest.raises(kb.KsmmError):
