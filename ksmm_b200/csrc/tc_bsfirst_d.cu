@@ -46,35 +46,39 @@ struct ParamsD {
 
 constexpr int kThreadsD = (2 + 4 + kEpilogueWarps) * 32;
 
-template <int D, bool WRES, int NWC, int SX>
+template <int D, int NJ_, bool WRES, int NWC, int SX>
 struct CfgD {
-  static constexpr int NJ = 64;                     // j columns per accumulator
+  static constexpr int NJ = NJ_;                    // j columns per accumulator (64 or 128)
   static constexpr int KCL = 64 / D;                // k values per block in one raw chunk
   static constexpr int RAW_BYTES = 128 * 128;       // 128 rows x 64 elements
   static constexpr int A_BYTES = 128 * 128;         // d tiles of 128 rows x KCL elements
   static constexpr int AL_BYTES = A_BYTES / D;      // one block's tile
-  static constexpr int WL_BYTES = KCL * 128;        // one block's weight box: KCL rows x 64 j
-  static constexpr int WCH_BYTES = D * WL_BYTES;    // weights that go with one raw chunk (8 KB)
+  static constexpr int WBOX_BYTES = KCL * 128;      // one weight box: KCL rows x 64 j
+  static constexpr int WL_BYTES = (NJ / 64) * WBOX_BYTES;  // one block's weights for one raw chunk
+  static constexpr int WCH_BYTES = D * WL_BYTES;    // weights that go with one raw chunk
   static constexpr int STAGE_BYTES = RAW_BYTES + A_BYTES + (WRES ? 0 : WCH_BYTES);
   static constexpr int STG_WARP_BYTES = 32 * 128;
   static constexpr int STG_BYTES = kEpilogueWarps * STG_WARP_BYTES;
   static constexpr int NBAR = 3 * SX + 2 + 4;
   static constexpr int BAR_BYTES = 512;
   static constexpr int SMEM_BYTES = NWC * WCH_BYTES + SX * STAGE_BYTES + STG_BYTES + BAR_BYTES + 1024;
-  static constexpr int TMEM_COLS = 512;             // two buffers of d * 64 columns (d <= 4)
-  static constexpr int BUF_COLS = 256;
+  static constexpr int BUF_COLS = D * NJ;           // d accumulators side by side
+  static constexpr int NBUF = BUF_COLS <= 256 ? 2 : 1;  // double-buffered when TMEM has room
+  static constexpr int TMEM_COLS = 512;
+  static_assert(NJ == 64 || NJ == 128, "j tile");
+  static_assert(BUF_COLS <= 512, "TMEM capacity");
   static_assert(D == 2 || D == 4, "d = 2 or 4");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
   static_assert(SMEM_BYTES > 116 * 1024, "one CTA per SM, so that the TMEM allocation never waits");
   static_assert(8 * NBAR + 16 <= BAR_BYTES, "barrier area");
 };
 
-template <int D, bool WRES, int NWC, int SX>
+template <int D, int NJ_, bool WRES, int NWC, int SX>
 __global__ void __launch_bounds__(kThreadsD, 1)
     ksmm_tc_bsfirst_d_kernel(const __grid_constant__ CUtensorMap tmX,
                              const __grid_constant__ CUtensorMap tmW,
                              const __grid_constant__ CUtensorMap tmY, const ParamsD P) {
-  using C = CfgD<D, WRES, NWC, SX>;
+  using C = CfgD<D, NJ_, WRES, NWC, SX>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t sm0 = (raw + 1023u) & ~1023u;
@@ -143,8 +147,10 @@ __global__ void __launch_bounds__(kThreadsD, 1)
           for (int qc = 0; qc < nchunks; ++qc)
 #pragma unroll
             for (int l = 0; l < D; ++l)
-              tma_load_3d(wres0 + qc * C::WCH_BYTES + l * C::WL_BYTES, &tmW, wfull_bar, j0,
-                          qc * C::KCL, i * D + l);
+#pragma unroll
+              for (int jb = 0; jb < C::NJ / 64; ++jb)
+                tma_load_3d(wres0 + qc * C::WCH_BYTES + l * C::WL_BYTES + jb * C::WBOX_BYTES, &tmW,
+                            wfull_bar, j0 + jb * 64, qc * C::KCL, i * D + l);
           cur_i = i;
         }
         for (int qc = 0; qc < nchunks; ++qc) {
@@ -156,8 +162,10 @@ __global__ void __launch_bounds__(kThreadsD, 1)
           if constexpr (!WRES) {
 #pragma unroll
             for (int l = 0; l < D; ++l)
-              tma_load_3d(dst + C::RAW_BYTES + C::A_BYTES + l * C::WL_BYTES, &tmW, bar, j0,
-                          qc * C::KCL, i * D + l);
+#pragma unroll
+              for (int jb = 0; jb < C::NJ / 64; ++jb)
+                tma_load_3d(dst + C::RAW_BYTES + C::A_BYTES + l * C::WL_BYTES + jb * C::WBOX_BYTES,
+                            &tmW, bar, j0 + jb * 64, qc * C::KCL, i * D + l);
           }
           if (++si == SX) { si = 0; sph ^= 1u; }
         }
@@ -181,7 +189,7 @@ __global__ void __launch_bounds__(kThreadsD, 1)
           wph ^= 1u;
           cur_i = i;
         }
-        const uint32_t buf = ut & 1u, bph = (ut >> 1) & 1u;
+        const uint32_t buf = ut % C::NBUF, bph = (ut / C::NBUF) & 1u;
         if (!mbar_wait<0>(tempty_bar(buf), bph ^ 1u, abort_flag, P.status, 14)) { ok = false; break; }
         tc_fence_after();
         const uint32_t dcol = tmem_base + buf * C::BUF_COLS;
@@ -195,7 +203,9 @@ __global__ void __launch_bounds__(kThreadsD, 1)
 #pragma unroll
             for (int l = 0; l < D; ++l) {
               const uint64_t adesc = make_desc(abase + l * C::AL_BYTES + ks * 256, 128, kASbo, 0);
-              const uint64_t bdesc = make_desc(wbase + l * C::WL_BYTES + ks * 2048, 1024, 1024, 2);
+              // weights: MN-major, 128-byte swizzle; LBO = next 64-j box, SBO = next 8 k rows
+              const uint64_t bdesc =
+                  make_desc(wbase + l * C::WL_BYTES + ks * 2048, C::WBOX_BYTES, 1024, 2);
               umma<2>(dcol + l * C::NJ, adesc, bdesc, P.idesc, (qc | ks) != 0 ? 1u : 0u);
             }
           }
@@ -279,7 +289,7 @@ __global__ void __launch_bounds__(kThreadsD, 1)
     for (uint32_t row = row_begin; row < row_end; ++row, ++ut) {
       const int i = static_cast<int>(row / P.tiles_n);
       const int n0 = static_cast<int>(row % P.tiles_n) * 128;
-      const uint32_t buf = ut & 1u, bph = (ut >> 1) & 1u;
+      const uint32_t buf = ut % C::NBUF, bph = (ut / C::NBUF) & 1u;
       int got = 1;
       if (lane == 0) got = mbar_wait<128>(tfull_bar(buf), bph, abort_flag, P.status, 17) ? 1 : 0;
       got = __shfl_sync(0xffffffffu, got, 0);
@@ -288,7 +298,7 @@ __global__ void __launch_bounds__(kThreadsD, 1)
       const bool warp_active = n0 + q * 32 < P.batch;
       if (warp_active) {
 #pragma unroll 1
-        for (int cb = grp; cb < D; cb += kEpilogueWarps / 4) {
+        for (int cb = grp; cb < C::BUF_COLS / 64; cb += kEpilogueWarps / 4) {
           const int jj0 = cb * JB;
           if (j0 + jj0 >= P.b) break;
           if (lane == 0) bulk_wait_read<0>();
@@ -362,10 +372,10 @@ __global__ void __launch_bounds__(kThreadsD, 1)
   }
 }
 
-template <int D, bool WRES, int NWC, int SX>
+template <int D, int NJ_, bool WRES, int NWC, int SX>
 static int launch_d(const Problem& p, cudaStream_t stream) {
-  using C = CfgD<D, WRES, NWC, SX>;
-  auto kern = ksmm_tc_bsfirst_d_kernel<D, WRES, NWC, SX>;
+  using C = CfgD<D, NJ_, WRES, NWC, SX>;
+  auto kern = ksmm_tc_bsfirst_d_kernel<D, NJ_, WRES, NWC, SX>;
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -454,13 +464,20 @@ bool tc_bsfirst_d_supported(const Problem& p, bool check_pointers) {
 }
 
 int tc_bsfirst_d_launch(const Problem& p, cudaStream_t stream) {
+  // <d, j tile, weight-stationary, resident weight chunks, ring stages>
   const int nchunks = (p.c * p.d + 63) / 64;
+  const bool wide_j = p.b > 64;  // 128-wide j tiles halve the re-reads of the input
   if (p.d == 4) {
-    if (nchunks <= 12) return tc::launch_d<4, true, 12, 3>(p, stream);
-    return tc::launch_d<4, false, 0, 4>(p, stream);
+    if (wide_j) return tc::launch_d<4, 128, false, 0, 4>(p, stream);
+    if (nchunks <= 12) return tc::launch_d<4, 64, true, 12, 3>(p, stream);
+    return tc::launch_d<4, 64, false, 0, 4>(p, stream);
   }
-  if (nchunks <= 12) return tc::launch_d<2, true, 12, 3>(p, stream);
-  return tc::launch_d<2, false, 0, 4>(p, stream);
+  if (wide_j) {
+    if (nchunks <= 6) return tc::launch_d<2, 128, true, 6, 3>(p, stream);
+    return tc::launch_d<2, 128, false, 0, 4>(p, stream);
+  }
+  if (nchunks <= 12) return tc::launch_d<2, 64, true, 12, 3>(p, stream);
+  return tc::launch_d<2, 64, false, 0, 4>(p, stream);
 }
 
 }  // namespace ksmm
