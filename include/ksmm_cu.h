@@ -131,6 +131,36 @@ KSMM_API int ksmm_cu_chain_forward(const void* input, const void* const* values,
                           int dtype, int bs_last, void* stream);
 
 /*
+ * ksmm_cu_chain_forward without any allocation: the intermediate activations
+ * live in a fixed array of KSMM_CU_STATIC_SCRATCH_BYTES that is part of the
+ * library image (each GPU that loads the library carries it until the process
+ * exits).  No counterpart in the reference.
+ *
+ * It is meant for callers that cannot call cudaMalloc or grow a framework
+ * allocator at the point of the call: code that runs between other people's
+ * kernels on a latency-critical stream, where an allocation would synchronise
+ * the device, or an embedding host that gives plugins a fixed memory budget
+ * and forbids allocation after start-up.  Inputs, weights and the output are
+ * still the caller's buffers.
+ *
+ *   - chains whose intermediates exceed the array (see
+ *     ksmm_cu_chain_workspace_bytes) are rejected with KSMM_ERR_WORKSPACE; the
+ *     default size holds one 38.5 MB intermediate, e.g. the two-factor KS-ViT-B
+ *     MLP layers in fp16 or the README layer in fp32 at batch 25088;
+ *   - the first call on a device resolves the array's device address; make
+ *     that call before starting a stream capture;
+ *   - all calls on one GPU share the array, and it keeps the previous call's
+ *     contents: calls that may overlap on the GPU (different streams) race and
+ *     must be serialised by the caller.  Nothing has to be cleared between
+ *     calls, every intermediate is overwritten in full.
+ */
+#define KSMM_CU_STATIC_SCRATCH_BYTES (40u * 1024u * 1024u)
+KSMM_API int ksmm_cu_chain_forward_static(const void* input, const void* const* values,
+                                          void* output, const void* bias, int64_t batch,
+                                          int nfactors, const int32_t* patterns, int dtype,
+                                          int bs_last, void* stream);
+
+/*
  * Host-memory variant of ksmm_cu_chain_forward: input, values and output are
  * HOST buffers; the call stages them through device memory that the library
  * owns (grown on demand, reused across calls), runs the chain and returns

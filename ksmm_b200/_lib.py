@@ -23,11 +23,12 @@ KSMM_ERR_NO_DEVICE = 6
 
 KSMM_F32, KSMM_F16, KSMM_BF16, KSMM_F8E4M3 = 0, 1, 2, 3
 KSMM_ALGO_AUTO, KSMM_ALGO_SIMT, KSMM_ALGO_TC = 0, 1, 2
+STATIC_SCRATCH_BYTES = 40 * 1024 * 1024  # KSMM_CU_STATIC_SCRATCH_BYTES
 
 EXPORTS = (
     "ksmm_cu_version", "ksmm_cu_last_error", "ksmm_cu_status_string", "ksmm_cu_forward",
     "ksmm_cu_forward_ex", "ksmm_cu_chain_workspace_bytes", "ksmm_cu_chain_forward",
-    "ksmm_cu_chain_forward_host", "ksmm_cu_num_configs", "ksmm_cu_config_supported",
+    "ksmm_cu_chain_forward_static", "ksmm_cu_chain_forward_host", "ksmm_cu_num_configs", "ksmm_cu_config_supported",
     "ksmm_cu_tune", "ksmm_cu_set_choice", "ksmm_cu_get_choice", "ksmm_cu_check_device",
     "ksmm_cu_launch_count", "ksmm_cu_measure_ffma_peak",
 )
@@ -77,6 +78,9 @@ def load():
     lib.ksmm_cu_chain_forward.restype = i32
     lib.ksmm_cu_chain_forward.argtypes = [vp, ctypes.POINTER(vp), vp, vp, vp, ctypes.c_size_t, i64,
                                           i32, ctypes.POINTER(ctypes.c_int32), i32, i32, vp]
+    lib.ksmm_cu_chain_forward_static.restype = i32
+    lib.ksmm_cu_chain_forward_static.argtypes = [vp, ctypes.POINTER(vp), vp, vp, i64, i32,
+                                                 ctypes.POINTER(ctypes.c_int32), i32, i32, vp]
     lib.ksmm_cu_chain_forward_host.restype = i32
     lib.ksmm_cu_chain_forward_host.argtypes = [vp, ctypes.POINTER(vp), vp, vp, i64, i32,
                                                ctypes.POINTER(ctypes.c_int32), i32, i32, i32]

@@ -189,6 +189,35 @@ static int host_reserve(int which, size_t bytes) {
 
 static size_t align_up(size_t v, size_t al) { return (v + al - 1) / al * al; }
 
+// ---------------------------------------------------------------------------
+// Scratch for ksmm_cu_chain_forward_static: a fixed array inside the module
+// image, so that the call never allocates.  In host code the name below is only
+// a handle for cudaGetSymbolAddress; kernels must be given the resolved device
+// address, never the symbol itself.
+// ---------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_chain_static_scratch[KSMM_CU_STATIC_SCRATCH_BYTES];
+
+static std::mutex g_static_mu;
+static void* g_static_scratch_ptr[64] = {nullptr};
+
+// Device address of the scratch array on the current device (resolved once per device).
+static int static_scratch_address(void** out) {
+  int dev = 0;
+  KSMM_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return set_error(KSMM_ERR_UNSUPPORTED, "device ordinal %d", dev);
+  std::lock_guard<std::mutex> g(g_static_mu);
+  if (!g_static_scratch_ptr[dev]) {
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_chain_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr)
+      return set_error(KSMM_ERR_CUDA, "cannot resolve the static scratch array: %s",
+                       cudaGetErrorString(e));
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return KSMM_OK;
+}
+
 }  // namespace ksmm
 
 using namespace ksmm;
@@ -287,6 +316,29 @@ int ksmm_cu_chain_forward(const void* input, const void* const* values, void* ou
     cur = dst;
   }
   return KSMM_OK;
+}
+
+int ksmm_cu_chain_forward_static(const void* input, const void* const* values, void* output,
+                                 const void* bias, int64_t batch, int nfactors,
+                                 const int32_t* patterns, int dtype, int bs_last, void* stream) {
+  if (nfactors <= 0 || !patterns || !values)
+    return set_error(KSMM_ERR_BAD_ARGUMENT, "chain needs at least one factor");
+  const size_t need = ksmm_cu_chain_workspace_bytes(nfactors, patterns, batch, dtype);
+  if (need > static_cast<size_t>(KSMM_CU_STATIC_SCRATCH_BYTES))
+    return set_error(KSMM_ERR_WORKSPACE,
+                     "chain intermediates need %zu bytes but the built-in scratch holds %zu: use "
+                     "ksmm_cu_chain_forward with a caller-provided workspace",
+                     need, static_cast<size_t>(KSMM_CU_STATIC_SCRATCH_BYTES));
+  void* scratch = nullptr;
+  if (need > 0) {
+    int st = static_scratch_address(&scratch);
+    if (st != KSMM_OK) return st;
+  }
+  // every intermediate is fully overwritten by the factor that produces it, so
+  // nothing in the scratch has to start at zero
+  return ksmm_cu_chain_forward(input, values, output, bias, scratch,
+                               need > 0 ? static_cast<size_t>(KSMM_CU_STATIC_SCRATCH_BYTES) : 0,
+                               batch, nfactors, patterns, dtype, bs_last, stream);
 }
 
 int ksmm_cu_chain_forward_host(const void* host_input, const void* const* host_values,

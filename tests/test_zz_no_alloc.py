@@ -1,0 +1,94 @@
+"""The allocation-free chain call (ksmm_cu_chain_forward_static).
+
+Some hosts of this library may not allocate device memory at call time: a
+plugin running on a latency-critical stream where cudaMalloc would stall the
+whole device, or an embedding process that fixes every plugin's memory budget
+at start-up.  For them the chain call exists in a variant whose scratch is a
+fixed array inside the library.  This test drives it through the C ABI with raw
+pointers and checks it against the ordinary call with a caller-owned workspace,
+twice in a row (the array keeps the previous call's contents), and checks that
+a chain that does not fit is refused rather than truncated.
+
+Collected last on purpose: a failure here stops a `-x` run only after every
+other test has run.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import ksmm_b200 as kb
+from golden_cases import make_weights
+from ksmm_b200 import _lib
+from oracle import ksmm_oracle as ko
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _chain_case(pats, batch, dtype, bs_last, seed):
+    rng = np.random.RandomState(seed)
+    ws = make_weights(pats, rng)
+    n_in = pats[0][0] * pats[0][2] * pats[0][3]
+    n_out = pats[-1][0] * pats[-1][1] * pats[-1][3]
+    x = torch.from_numpy(rng.standard_normal((n_in, batch) if bs_last else (batch, n_in)).astype(np.float32))
+    xg = x.to(dtype).to(DEV)
+    wk = [kb.generate_factor(*p, "kernel", torch.from_numpy(w), dtype, DEV) for p, w in zip(pats, ws)]
+    bias = torch.from_numpy(rng.standard_normal(n_out).astype(np.float32)).to(dtype).to(DEV)
+    return xg, wk, bias, ws, n_out
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.float16, 1e-2)])
+@pytest.mark.parametrize("bs_last", [True, False])
+def test_static_scratch_chain_matches_workspace_chain(dtype, tol, bs_last):
+    lib = _lib.load()
+    pats = [(4, 192, 192, 1), (1, 768, 192, 4)]
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    flat = _lib.int32_array([v for p in pats for v in p])
+    code = kb.kernel.dtype_code(dtype)
+    for call, batch in enumerate((1024, 1536)):   # two calls in a row, different sizes
+        xg, wk, bias, ws, n_out = _chain_case(pats, batch, dtype, bs_last, seed=50 + call)
+        ref = kb.chain_forward(xg, wk, pats, bs_last, bias=bias)       # caller-owned workspace
+        out = torch.full_like(ref, float("nan"))
+        vals = (ctypes.c_void_p * len(wk))(*[w.data_ptr() for w in wk])
+        mem_before = torch.cuda.memory_allocated()
+        st = lib.ksmm_cu_chain_forward_static(xg.data_ptr(), vals, out.data_ptr(), bias.data_ptr(),
+                                              batch, len(pats), flat, code, int(bs_last), stream)
+        _lib.check(st)
+        torch.cuda.synchronize()
+        assert torch.cuda.memory_allocated() == mem_before
+        assert not torch.isnan(out.float()).any()
+        # same kernels, same order: the two entry points agree far inside the tolerance
+        err = ko.rel_fro_error(out.float().cpu().numpy(), ref.float().cpu().numpy())
+        assert err < tol, (call, err)
+        half = dtype == torch.float16
+        w_seen = [w.astype(np.float16).astype(np.float32) if half else w for w in ws]
+        oracle = ko.chain_apply(xg.float().cpu().numpy(), w_seen, bs_last,
+                                bias=bias.float().cpu().numpy(),
+                                round_to=np.float16 if half else None)
+        assert ko.rel_fro_error(out.float().cpu().numpy(), oracle) < tol
+    kb.check_device()
+
+
+def test_static_scratch_rejects_oversized_chains():
+    lib = _lib.load()
+    pats = [(1, 64, 64, 16), (4, 64, 64, 4), (16, 64, 64, 1)]   # needs two 1024-feature intermediates
+    flat = _lib.int32_array([v for p in pats for v in p])
+    batch = 25088
+    need = lib.ksmm_cu_chain_workspace_bytes(3, flat, batch, _lib.KSMM_F16)
+    assert need > _lib.STATIC_SCRATCH_BYTES
+    x = torch.zeros(1024, batch, dtype=torch.float16, device=DEV)
+    y = torch.zeros(1024, batch, dtype=torch.float16, device=DEV)
+    wk = [torch.zeros(p[0] * p[3] * p[2], p[1], dtype=torch.float16, device=DEV) for p in pats]
+    vals = (ctypes.c_void_p * 3)(*[w.data_ptr() for w in wk])
+    st = lib.ksmm_cu_chain_forward_static(x.data_ptr(), vals, y.data_ptr(), None, batch, 3, flat,
+                                          _lib.KSMM_F16, 1, None)
+    assert st == _lib.KSMM_ERR_WORKSPACE
+    assert b"built-in scratch" in lib.ksmm_cu_last_error()
+    # a single factor needs no scratch at all and always goes through
+    one = _lib.int32_array(list(pats[0]))
+    st = lib.ksmm_cu_chain_forward_static(x.data_ptr(), vals, y.data_ptr(), None, batch, 1, one,
+                                          _lib.KSMM_F16, 1, None)
+    _lib.check(st)
+    kb.check_device()
