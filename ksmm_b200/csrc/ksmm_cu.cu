@@ -44,9 +44,38 @@ int simt_launch_bf16(const Problem& p, int config, cudaStream_t stream);
 int simt_launch_f8(const Problem& p, int config, cudaStream_t stream);
 int simt_default_config_for(const Problem& p);
 int simt_num_configs();
+// fp32 batch-last kernel with TMA-staged operands (ffma_tma_kernel.cu): configurations
+// kFfmaTmaWide (128 x 128 tile) and kFfmaTmaNarrow (64 x 128 tile) of the FFMA family
+bool ffma_tma_supported(const Problem& p, bool check_pointers);
+int ffma_tma_launch(const Problem& p, int wide, cudaStream_t stream);
+// fp32 batch-first kernel with TMA-staged operands (ffma_tma_first.cu): configuration kFfmaTmaFirst
+bool ffma_tma_first_supported(const Problem& p, bool check_pointers);
+int ffma_tma_first_launch(const Problem& p, cudaStream_t stream);
+static constexpr int kFfmaTmaWide = 6, kFfmaTmaNarrow = 7, kFfmaTmaFirst = 8, kNumFfmaConfigs = 9;
 
 static int simt_launch(const Problem& p, int config, cudaStream_t stream) {
-  if (config < 0) config = simt_default_config_for(p);
+  if (config < 0) {
+    if (ffma_tma_supported(p, true) && p.b >= 48)
+      config = kFfmaTmaNarrow;  // 64 x 128 tiles, four CTAs per SM: fastest in every measured case
+    else if (ffma_tma_first_supported(p, true) && p.b >= 48)
+      config = kFfmaTmaFirst;
+    else
+      config = simt_default_config_for(p);
+  }
+  if (config == kFfmaTmaWide || config == kFfmaTmaNarrow) {
+    if (!ffma_tma_supported(p, true))
+      return set_error(KSMM_ERR_UNSUPPORTED,
+                       "the TMA-staged fp32 kernel needs fp32, batch-last, batch %% 4 == 0, "
+                       "b %% 4 == 0 and 16-byte aligned pointers");
+    return ffma_tma_launch(p, config == kFfmaTmaWide, stream);
+  }
+  if (config == kFfmaTmaFirst) {
+    if (!ffma_tma_first_supported(p, true))
+      return set_error(KSMM_ERR_UNSUPPORTED,
+                       "the TMA-staged batch-first fp32 kernel needs fp32, batch-first, d in {1, 2, 4}, "
+                       "b %% 4 == 0, c*d %% 4 == 0 and 16-byte aligned pointers");
+    return ffma_tma_first_launch(p, stream);
+  }
   switch (p.in_dtype) {
     case KSMM_F32:
       if (p.out_dtype != KSMM_F32)
@@ -407,7 +436,7 @@ int ksmm_cu_chain_forward_host(const void* host_input, const void* const* host_v
 }
 
 int ksmm_cu_num_configs(int algo) {
-  if (algo == KSMM_ALGO_SIMT) return simt_num_configs();
+  if (algo == KSMM_ALGO_SIMT) return kNumFfmaConfigs;
   if (algo == KSMM_ALGO_TC) return tc_num_configs();
   return 0;
 }
@@ -420,7 +449,9 @@ int ksmm_cu_config_supported(int algo, int config, int64_t batch, int a, int b, 
   p.in_dtype = in_dtype; p.out_dtype = out_dtype; p.bs_last = bs_last; p.alpha = 1.f;
   if (a <= 0 || b <= 0 || c <= 0 || d <= 0 || batch <= 0) return 0;
   if (algo == KSMM_ALGO_SIMT) {
-    if (config < 0 || config >= simt_num_configs()) return 0;
+    if (config < 0 || config >= kNumFfmaConfigs) return 0;
+    if (config == kFfmaTmaWide || config == kFfmaTmaNarrow) return ffma_tma_supported(p, false);
+    if (config == kFfmaTmaFirst) return ffma_tma_first_supported(p, false);
     if (in_dtype == KSMM_F8E4M3) return out_dtype != KSMM_F8E4M3;
     return in_dtype == out_dtype;
   }

@@ -83,7 +83,7 @@ def test_chain_validation_and_workspace():
 
 def test_config_tables():
     lib = _lib.load()
-    assert lib.ksmm_cu_num_configs(_lib.KSMM_ALGO_SIMT) >= 4
+    assert lib.ksmm_cu_num_configs(_lib.KSMM_ALGO_SIMT) == 9
     assert lib.ksmm_cu_num_configs(_lib.KSMM_ALGO_TC) >= 2
     assert lib.ksmm_cu_num_configs(99) == 0
     sup = lib.ksmm_cu_config_supported

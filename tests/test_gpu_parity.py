@@ -105,6 +105,52 @@ def test_simt_family_every_config(config, bs_last, dtype):
             assert err < TOL[dtype], (pattern, batch, err)
 
 
+@pytest.mark.parametrize("config", [6, 7])
+def test_ffma_tma_staged_fp32_batch_last(config):
+    """fp32 batch-last kernel with TMA-staged operands (FFMA family, configurations 6 and 7)."""
+    pats = [(2, 12, 8, 1), (1, 16, 16, 1), (2, 132, 20, 1), (1, 64, 64, 2), (4, 8, 8, 1),
+            (1, 768, 192, 2), (3, 72, 45, 3), (1, 4, 100, 2)]
+    for pi, pattern in enumerate(pats):
+        for batch in (36, 256, 388):
+            x, w = _inputs(pattern, batch, torch.float32, True, seed=150 + pi)
+            y = _run(x, w, pattern, True, algo=_lib.KSMM_ALGO_SIMT, config=config)
+            assert not np.isnan(y).any(), (pattern, batch)
+            err = ko.rel_fro_error(y, _oracle(x, w, True))
+            assert err < 1e-5, (pattern, batch, err)
+    # outside its envelope (odd batch, batch-first, 16-bit) the configuration is refused
+    x, w = _inputs((1, 16, 16, 1), 33, torch.float32, True, seed=1)
+    with pytest.raises(kb.KsmmError):
+        _run(x, w, (1, 16, 16, 1), True, algo=_lib.KSMM_ALGO_SIMT, config=config)
+    x, w = _inputs((1, 16, 16, 1), 32, torch.float32, False, seed=1)
+    with pytest.raises(kb.KsmmError):
+        _run(x, w, (1, 16, 16, 1), False, algo=_lib.KSMM_ALGO_SIMT, config=config)
+    kb.check_device()
+
+
+def test_ffma_tma_staged_fp32_batch_first():
+    """fp32 batch-first kernel with TMA-staged operands (FFMA family, configuration 8):
+    d = 1, d = 2 and d = 4 take three different thread tilings."""
+    pats = [(2, 12, 8, 1), (1, 64, 64, 1), (3, 72, 44, 1), (1, 768, 192, 1),        # d = 1
+            (2, 12, 8, 2), (1, 64, 64, 2), (1, 132, 50, 2), (1, 768, 192, 2),       # d = 2
+            (1, 64, 64, 4), (2, 12, 9, 4), (1, 768, 192, 4), (4, 64, 64, 4), (2, 72, 20, 4)]       # d = 4
+    rng = np.random.RandomState(7)
+    for pi, pattern in enumerate(pats):
+        for batch in (37, 256, 390):
+            x, w = _inputs(pattern, batch, torch.float32, False, seed=170 + pi)
+            a, b, c, d = pattern
+            bias = torch.from_numpy(rng.standard_normal(a * b * d).astype(np.float32))
+            y = _run(x, w, pattern, False, algo=_lib.KSMM_ALGO_SIMT, config=8, bias=bias.to(DEV),
+                     alpha=2.0)
+            assert not np.isnan(y).any(), (pattern, batch)
+            ref = 2.0 * _oracle(x, w, False) + bias.numpy()[None, :]
+            err = ko.rel_fro_error(y, ref)
+            assert err < 1e-5, (pattern, batch, err)
+    x, w = _inputs((1, 16, 16, 3), 32, torch.float32, False, seed=1)   # d = 3 is outside its envelope
+    with pytest.raises(kb.KsmmError):
+        _run(x, w, (1, 16, 16, 3), False, algo=_lib.KSMM_ALGO_SIMT, config=8)
+    kb.check_device()
+
+
 @pytest.mark.parametrize("bs_last", [True, False])
 def test_simt_unaligned_pointers_take_the_scalar_path(bs_last):
     pattern, batch = (2, 12, 8, 1), 36

@@ -71,3 +71,38 @@ def test_quantize_e4m3_matches_oracle():
     assert abs(s - s_ref) < 1e-7 * s_ref + 1e-12
     ref = ko.quantize_e4m3(x.astype(np.float32) / np.float32(s))
     assert np.array_equal(q.float().numpy(), ref.astype(np.float32))
+
+
+def test_tuner_table_round_trip(tmp_path):
+    """A saved tuner table is pushed back into the library without timing anything."""
+    import json
+    from ksmm_b200 import _lib, tuner
+    table = {"format": "ksmm_b200.tuner/1", "entries": [
+        {"sm": 100, "dtype": "f16", "out_dtype": "f16", "bs_last": True, "pattern": [1, 768, 192, 4],
+         "batch": 25088, "family": "tensor", "config": 0, "ms": 0.047},
+        {"sm": 100, "dtype": "f32", "out_dtype": "f32", "bs_last": True, "pattern": [1, 768, 192, 4],
+         "batch": 25088, "family": "ffma", "config": 7, "ms": 0.57},
+        # an entry the build cannot run (tensor family on fp32) is skipped, not fatal
+        {"sm": 100, "dtype": "f32", "out_dtype": "f32", "bs_last": True, "pattern": [1, 64, 64, 1],
+         "batch": 64, "family": "tensor", "config": 0, "ms": 1.0},
+        {"sm": 90, "dtype": "f16", "out_dtype": "f16", "bs_last": True, "pattern": [1, 64, 64, 1],
+         "batch": 64, "family": "tensor", "config": 1, "ms": 1.0}]}
+    path = tmp_path / "tuned.json"
+    path.write_text(json.dumps(table))
+    assert tuner.load(str(path), sm=100) == 2
+    lib = _lib.load()
+    import ctypes
+    algo, cfg = ctypes.c_int(), ctypes.c_int()
+    assert lib.ksmm_cu_get_choice(25088, 1, 768, 192, 4, _lib.KSMM_F32, _lib.KSMM_F32, 1,
+                                  ctypes.byref(algo), ctypes.byref(cfg)) == 0
+    assert (algo.value, cfg.value) == (_lib.KSMM_ALGO_SIMT, 7)
+    out = tmp_path / "again.json"
+    tuner.save(str(out))
+    assert len(json.loads(out.read_text())["entries"]) >= 2
+    best = tmp_path / "kernel.best"
+    tuner.export_best_rows(str(best))
+    assert best.read_text().splitlines()[0].split()[:5] == ["25088", "1", "768", "192", "4"]
+    with pytest.raises(ValueError):
+        bad = tmp_path / "bad.json"
+        bad.write_text("{}")
+        tuner.load(str(bad))
