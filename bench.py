@@ -185,7 +185,7 @@ def run_reference(args, rank, world):
 
 def workload_config():
     return {"workload": "single-factor sweep (configs[1] restricted to the 8 benchmark patterns): "
-                        "fp32+fp16 x batch-last+batch-first, B=25088 per GPU, 32 launches per step",
+                        "fp32+fp16 x batch-last+batch-first, B=25088 per GPU, 32 cases per step",
             "patterns": [list(p) for p in PATTERNS], "batch_per_gpu": BATCH,
             "l2": "a step touches ~5.4 GB of distinct buffers (> 126 MB L2) before any buffer repeats"}
 
@@ -233,8 +233,10 @@ def run_ours(args, rank, world, local_rank):
     torch.cuda.synchronize()
     kb.check_device()
     step_graph = torch.cuda.CUDAGraph()
+    launches_before = kb.launch_count()
     with torch.cuda.graph(step_graph):
         one_step()
+    launches_per_step = kb.launch_count() - launches_before  # kernels recorded into the graph
     for _ in range(max(args.warmup, 3)):
         step_graph.replay()
     torch.cuda.synchronize()
@@ -251,7 +253,7 @@ def run_ours(args, rank, world, local_rank):
     torch.cuda.synchronize()
     barrier()
     clocks = sampler.stop()
-    launches = args.steps * len(cs)
+    launches = args.steps * launches_per_step
     elapsed_ms = e0.elapsed_time(e1)
     if world > 1:
         t = torch.tensor([elapsed_ms], device=dev)

@@ -51,6 +51,8 @@ int ffma_tma_launch(const Problem& p, int wide, cudaStream_t stream);
 // fp32 batch-first kernel with TMA-staged operands (ffma_tma_first.cu): configuration kFfmaTmaFirst
 bool ffma_tma_first_supported(const Problem& p, bool check_pointers);
 int ffma_tma_first_launch(const Problem& p, cudaStream_t stream);
+int launch_transpose(const void* in, void* out, int64_t rows, int64_t cols, int es,
+                     cudaStream_t stream);
 static constexpr int kFfmaTmaWide = 6, kFfmaTmaNarrow = 7, kFfmaTmaFirst = 8, kNumFfmaConfigs = 9;
 
 static int simt_launch(const Problem& p, int config, cudaStream_t stream) {
@@ -142,6 +144,88 @@ static int run_family(const Problem& p, int algo, int config, cudaStream_t strea
   return set_error(KSMM_ERR_BAD_ARGUMENT, "unknown kernel family %d", algo);
 }
 
+// ---------------------------------------------------------------------------
+// Layout-conversion path for batch-first factors with d > 1 that no direct
+// kernel covers (e.g. d = 16): transpose the input to batch-last, run the
+// batch-last kernel, transpose the result back.  Three times the minimal HBM
+// traffic, but every access is a full line, which beats the strided
+// register-staged kernel by a wide margin.  The two transposed buffers live in
+// a per-device scratch that is grown on demand (never during a stream capture)
+// and shared by all calls on that device: calls that use this path on
+// different streams of one device must not overlap.
+// ---------------------------------------------------------------------------
+static size_t align_up(size_t v, size_t al) { return (v + al - 1) / al * al; }
+
+struct ConvScratch {
+  void* ptr = nullptr;
+  size_t cap = 0;
+};
+static std::mutex g_conv_mu;
+static ConvScratch g_conv[64];
+
+static bool conversion_applies(const Problem& p) {
+  if (p.bs_last || p.d == 1) return false;
+  if (reinterpret_cast<uintptr_t>(p.w) % 16 != 0) return false;
+  if (p.in_dtype == KSMM_F32) {
+    if (ffma_tma_first_supported(p, true)) return false;
+    Problem q = p;
+    q.bs_last = 1;
+    q.in = q.out = reinterpret_cast<void*>(16);  // alignment is that of the scratch (256 bytes)
+    return q.b >= 48 && ffma_tma_supported(q, false);
+  }
+  Problem q = p;
+  q.bs_last = 1;
+  if (tc_config_supported(p, 0, true)) return false;  // the interleaved-block kernel covers it
+  return q.b >= 32 && q.c >= 16 && tc_config_supported(q, 0, false);
+}
+
+static int run_family(const Problem& p, int algo, int config, cudaStream_t stream);
+static int dispatch(const Problem& p, int algo, int config, cudaStream_t stream);
+
+static int forward_via_transpose(const Problem& p, cudaStream_t stream) {
+  const int es = dtype_size(p.in_dtype), os = dtype_size(p.out_dtype);
+  const int64_t n_in = static_cast<int64_t>(p.a) * p.c * p.d, n_out = static_cast<int64_t>(p.a) * p.b * p.d;
+  const size_t in_bytes = align_up(static_cast<size_t>(n_in) * p.batch * es, 256);
+  const size_t out_bytes = align_up(static_cast<size_t>(n_out) * p.batch * os, 256);
+  int dev = 0;
+  KSMM_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return set_error(KSMM_ERR_UNSUPPORTED, "device ordinal %d", dev);
+  void* base = nullptr;
+  {
+    std::lock_guard<std::mutex> g(g_conv_mu);
+    ConvScratch& sc = g_conv[dev];
+    if (sc.cap < in_bytes + out_bytes) {
+      cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+      cudaStreamIsCapturing(stream, &cs);
+      if (cs != cudaStreamCaptureStatusNone)
+        return set_error(KSMM_ERR_WORKSPACE,
+                         "the layout-conversion scratch must grow to %zu bytes, which cannot happen "
+                         "inside a stream capture: make one call outside the capture first",
+                         in_bytes + out_bytes);
+      if (sc.ptr) {
+        KSMM_CUDA_OK(cudaStreamSynchronize(stream));
+        KSMM_CUDA_OK(cudaFree(sc.ptr));
+        sc.ptr = nullptr;
+        sc.cap = 0;
+      }
+      KSMM_CUDA_OK(cudaMalloc(&sc.ptr, in_bytes + out_bytes));
+      sc.cap = in_bytes + out_bytes;
+    }
+    base = sc.ptr;
+  }
+  void* xt = base;
+  void* yt = static_cast<char*>(base) + in_bytes;
+  int st = launch_transpose(p.in, xt, p.batch, n_in, es, stream);  // (batch, in) -> (in, batch)
+  if (st != KSMM_OK) return st;
+  Problem q = p;
+  q.in = xt;
+  q.out = yt;
+  q.bs_last = 1;
+  st = dispatch(q, KSMM_ALGO_AUTO, -1, stream);
+  if (st != KSMM_OK) return st;
+  return launch_transpose(yt, p.out, n_out, p.batch, os, stream);  // (out, batch) -> (batch, out)
+}
+
 static int dispatch(const Problem& p, int algo, int config, cudaStream_t stream) {
   int st = check_problem(p);
   if (st != KSMM_OK) return st;
@@ -151,6 +235,7 @@ static int dispatch(const Problem& p, int algo, int config, cudaStream_t stream)
     if (lookup_choice(p, &ch)) return run_family(p, ch.algo, ch.config, stream);
     const int tc_cfg = tc_default_config(p);
     if (tc_cfg >= 0) return tc_launch(p, tc_cfg, stream);
+    if (conversion_applies(p)) return forward_via_transpose(p, stream);
     return simt_launch(p, -1, stream);
   }
   return run_family(p, algo, config, stream);
@@ -216,7 +301,6 @@ static int host_reserve(int which, size_t bytes) {
   return KSMM_OK;
 }
 
-static size_t align_up(size_t v, size_t al) { return (v + al - 1) / al * al; }
 
 // ---------------------------------------------------------------------------
 // Scratch for ksmm_cu_chain_forward_static: a fixed array inside the module

@@ -218,6 +218,24 @@ def test_tc_family_batch_first_interleaved_blocks(dtype):
     kb.check_device()
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_batch_first_layout_conversion_path(dtype):
+    """Batch-first factors with a d that no direct kernel covers (here 16, 8, 3 x ...) run as
+    transpose -> batch-last kernel -> transpose, with bias and scale in the kernel's epilogue."""
+    rng = np.random.RandomState(3)
+    for pi, pattern in enumerate([(1, 64, 64, 16), (2, 128, 32, 8), (1, 72, 48, 6)]):
+        for batch in (40, 520):
+            x, w = _inputs(pattern, batch, dtype, False, seed=500 + pi)
+            a, b, c, d = pattern
+            bias = torch.from_numpy(rng.standard_normal(a * b * d).astype(np.float32)).to(dtype)
+            before = kb.launch_count()
+            y = _run(x, w, pattern, False, bias=bias.to(DEV), alpha=0.5)
+            assert kb.launch_count() - before == 3          # transpose, kernel, transpose
+            ref = 0.5 * _oracle(x, w, False) + bias.float().numpy()[None, :]
+            assert ko.rel_fro_error(y, ref) < TOL[dtype], (pattern, batch)
+    kb.check_device()
+
+
 def test_tc_refuses_what_it_cannot_run():
     x, w = _inputs((1, 64, 64, 3), 16, torch.float16, False, seed=1)  # batch-first with d = 3
     with pytest.raises(kb.KsmmError) as ei:
