@@ -389,6 +389,52 @@ def run_ours(args, rank, world, local_rank):
                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": e2e_steps,
                "api": "ksmm_cu_chain_forward_host (C ABI, pinned host buffers, wall clock)"}
 
+    # ---- KS-ViT-B/16 forward (128 images per GPU, fp16): the second half of the headline metric --
+    ksvit = None
+    if not args.no_vit and not args.only:
+        from ksmm_b200.ksvit import KSViTB
+        torch.manual_seed(7 + rank)
+        img = torch.randn(128, 3, 224, 224, device=dev, dtype=torch.float16)
+
+        def time_model(dense):
+            model = KSViTB(dtype=torch.float16, device=dev, dense_mlp=dense).eval()
+            with torch.no_grad():
+                for _ in range(2):
+                    model(img)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    out = model(img)
+                for _ in range(3):
+                    g.replay()
+                torch.cuda.synchronize()
+                barrier()
+                v0, v1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps = 10
+                v0.record()
+                for _ in range(reps):
+                    g.replay()
+                v1.record()
+                torch.cuda.synchronize()
+                barrier()
+            ms = v0.elapsed_time(v1) / reps
+            if world > 1:
+                t = torch.tensor([ms], device=dev)
+                torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+                ms = float(t.item())
+            assert torch.isfinite(out.float()).all()
+            del g, model
+            return ms
+
+        ks_ms = time_model(False)
+        dense_ms = time_model(True)
+        kb.check_device()
+        ksvit = {"imgs_per_s": world * 128 / (ks_ms * 1e-3), "ms_per_forward": ks_ms,
+                 "dense_mlp_imgs_per_s": world * 128 / (dense_ms * 1e-3), "dense_mlp_ms_per_forward": dense_ms,
+                 "config": "SimpleViT-B/16, 12 layers, 128 images of 224x224 per GPU, fp16, random init, "
+                           "fc1=[(4,192,192,1),(1,768,192,4)], fc2=[(1,192,768,4),(4,192,192,1)], batch-first; "
+                           "attention / LayerNorm / GELU are stock PyTorch; forward captured in a CUDA graph"}
+
     if rank != 0:
         return
 
@@ -415,7 +461,7 @@ def run_ours(args, rank, world, local_rank):
         "roofline": roofline_of(per[dom], cs[dom]),
         "roofline_hbm": roofline_of(per[dom_hbm], cs[dom_hbm]) if dom_hbm is not None else None,
         "ffma_peak_tflops": round(ffma_peak, 2),
-        "cpu_baseline": cpu, "per_pattern": per,
+        "cpu_baseline": cpu, "ksvit_b": ksvit, "per_pattern": per,
     }
     print(json.dumps(line), flush=True)
 
@@ -428,6 +474,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-vit", action="store_true", help="skip the KS-ViT-B/16 forward timing")
     ap.add_argument("--sweep-configs", action="store_true",
                     help="also time every tile configuration of every case (printed to stderr)")
     ap.add_argument("--only", default=None,

@@ -1,0 +1,96 @@
+"""KS-ViT-B/16 timing harness: a SimpleViT-B/16 whose MLP projections are
+``KSLinear`` layers with ``algo='kernel'``.
+
+This is benchmark scaffolding, not part of the KSMM hot path: attention,
+LayerNorm, GELU, residuals and the patch embedding are stock PyTorch, exactly
+as in the reference's timing script, where a SimpleViT is built and its
+FeedForward projections ``net[1]`` / ``net[3]`` are swapped for KSLinear
+(src/ksmm_py/model/vit.py:416-431, 770-800; get_vit.py:81-100;
+benchmark/ksvit_time.py:167-229).  Architecture: 224x224 images, 16x16 patches
+(196 tokens), width 768, 12 layers, 12 heads of 64, MLP 3072, mean pooling,
+1000 classes, random initialisation.
+
+    fc1 = KSLinear([(4,192,192,1), (1,768,192,4)])   768 -> 3072
+    fc2 = KSLinear([(1,192,768,4), (4,192,192,1)])   3072 -> 768
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from .interface import KSLinear
+
+FC1_PATTERNS = [(4, 192, 192, 1), (1, 768, 192, 4)]
+FC2_PATTERNS = [(1, 192, 768, 4), (4, 192, 192, 1)]
+
+
+def posemb_sincos_2d(h, w, dim, temperature=10000.0):
+    y, x = torch.meshgrid(torch.arange(h), torch.arange(w), indexing="ij")
+    omega = torch.arange(dim // 4) / (dim // 4 - 1)
+    omega = 1.0 / (temperature ** omega)
+    y = y.flatten()[:, None] * omega[None, :]
+    x = x.flatten()[:, None] * omega[None, :]
+    return torch.cat((x.sin(), x.cos(), y.sin(), y.cos()), dim=1)
+
+
+class KSFeedForward(nn.Module):
+    def __init__(self, dim, dtype, device, dense=False):
+        super().__init__()
+        self.norm = nn.LayerNorm(dim)
+        if dense:  # same shapes with nn.Linear, for an accuracy / speed comparison
+            self.fc1 = nn.Linear(dim, 4 * dim)
+            self.fc2 = nn.Linear(4 * dim, dim)
+        else:
+            self.fc1 = KSLinear(FC1_PATTERNS, bias=True, algo="kernel", dtype=dtype, bs_last=False,
+                                device=device)
+            self.fc2 = KSLinear(FC2_PATTERNS, bias=True, algo="kernel", dtype=dtype, bs_last=False,
+                                device=device)
+
+    def forward(self, x):
+        return self.fc2(F.gelu(self.fc1(self.norm(x))))
+
+
+class Attention(nn.Module):
+    def __init__(self, dim, heads=12, dim_head=64):
+        super().__init__()
+        self.heads = heads
+        self.norm = nn.LayerNorm(dim)
+        self.to_qkv = nn.Linear(dim, heads * dim_head * 3, bias=False)
+        self.to_out = nn.Linear(heads * dim_head, dim, bias=False)
+
+    def forward(self, x):
+        b, n, _ = x.shape
+        q, k, v = self.to_qkv(self.norm(x)).view(b, n, 3, self.heads, -1).permute(2, 0, 3, 1, 4)
+        out = F.scaled_dot_product_attention(q, k, v)
+        return self.to_out(out.transpose(1, 2).reshape(b, n, -1))
+
+
+class KSViTB(nn.Module):
+    def __init__(self, dtype=torch.float16, device="cuda", depth=12, dim=768, num_classes=1000,
+                 dense_mlp=False):
+        super().__init__()
+        self.patch = 16
+        patch_dim = 3 * 16 * 16
+        self.embed = nn.Sequential(nn.LayerNorm(patch_dim), nn.Linear(patch_dim, dim), nn.LayerNorm(dim))
+        self.register_buffer("pos", posemb_sincos_2d(14, 14, dim), persistent=False)
+        self.layers = nn.ModuleList(
+            [nn.ModuleList([Attention(dim), KSFeedForward(dim, dtype, device, dense_mlp)])
+             for _ in range(depth)])
+        self.norm = nn.LayerNorm(dim)
+        self.head = nn.Linear(dim, num_classes)
+        # stock layers to the requested dtype / device; KSLinear parameters were created there
+        for m in self.modules():
+            if isinstance(m, (nn.Linear, nn.LayerNorm)):
+                m.to(device=device, dtype=dtype)
+        self.pos = self.pos.to(device=device, dtype=dtype)
+
+    def forward(self, img):
+        b, c, h, w = img.shape
+        p = self.patch
+        x = img.view(b, c, h // p, p, w // p, p).permute(0, 2, 4, 3, 5, 1).reshape(b, -1, p * p * c)
+        x = self.embed(x) + self.pos
+        for attn, ff in self.layers:
+            x = attn(x) + x
+            x = ff(x) + x
+        return self.head(self.norm(x).mean(dim=1))
