@@ -54,10 +54,6 @@ namespace tc {
 // one status word per device that loads the module; 0 = no device-side timeout
 __device__ int g_tc_status_word = 0;
 
-#ifdef KSMM_TC_TRACE
-__device__ unsigned long long g_trace[4][8192];
-#endif
-
 struct Params {
   int a, b, c, d;
   int64_t batch;

@@ -11,8 +11,8 @@ namespace ksmm {
 namespace tc {
 
 #ifdef KSMM_TC_TRACE
-// Diagnostic build only: per-role timestamp log of CTA 0.
-extern __device__ unsigned long long g_trace[4][8192];
+// Diagnostic build only: per-role timestamp log of CTA 0 (one copy per translation unit).
+static __device__ unsigned long long g_trace[4][8192];
 #define KSMM_TRACE_DECL uint32_t tr_n = 0
 #define KSMM_TRACE(role, ev)                                                              \
   do {                                                                                    \
