@@ -167,10 +167,14 @@ static bool conversion_applies(const Problem& p) {
   if (p.bs_last || p.d == 1) return false;
   if (reinterpret_cast<uintptr_t>(p.w) % 16 != 0) return false;
   if (p.in_dtype == KSMM_F32) {
-    if (ffma_tma_first_supported(p, true)) return false;
     Problem q = p;
     q.bs_last = 1;
     q.in = q.out = reinterpret_cast<void*>(16);  // alignment is that of the scratch (256 bytes)
+    // for compute-heavy blocks the batch-last tensor-core kernel pays for the two transposes;
+    // small blocks are bandwidth problems that the direct FFMA kernel (d = 2, 4) serves better
+    const bool direct = ffma_tma_first_supported(p, true);
+    if (tc_default_config(q) >= 0 && (!direct || p.c >= 128)) return true;
+    if (direct) return false;
     return q.b >= 48 && ffma_tma_supported(q, false);
   }
   Problem q = p;

@@ -1,0 +1,620 @@
+// fp32 factors on the tensor cores: tcgen05 kind::tf32 with a three-term split
+// ("3xTF32"), fp32 accumulation in TMEM.  Kernel family KSMM_ALGO_TC for fp32
+// inputs, batch-last (any d) and batch-first (d = 1).
+//
+// A tf32 operand keeps the upper 19 bits of an fp32 value; the tensor core
+// ignores the other 13 mantissa bits (it truncates, it does not round).  Every
+// fp32 operand v is therefore used twice: once as it is (the hardware sees
+// hi = trunc(v)) and once as lo = v - trunc(v), which is exact in fp32.  The
+// product x * w is accumulated as
+//     hi(x) hi(w) + lo(x) hi(w) + hi(x) lo(w),
+// three MMAs per k step; the dropped lo * lo term and the truncation of lo
+// itself are of relative size 2^-22.  The tensor core also truncates when it
+// adds into the fp32 accumulator, once per MMA, and that error grows with the
+// number of accumulations: the two small terms therefore go to an accumulator
+// of their own (their truncation is 2^-11 times smaller) and are added to the
+// leading one in the epilogue, which leaves c / 8 truncating additions on the
+// leading accumulator.  Relative Frobenius error against an fp64 oracle: about
+// 3e-7 for c <= 192 and 2e-6 for c = 768, inside the 1e-5 of the reference's own
+// fp32 check (src/ksmm_cu/src/template_sparse_mm.cu:873-880); the default
+// dispatch uses this kernel up to c = 1024.  The exact FFMA kernels stay
+// available as KSMM_ALGO_SIMT.
+//
+// Operands are K-major in shared memory: the tensor core wants, for every row
+// (a batch entry of the input, a column j of the weights), the values of k next
+// to each other, but both the batch-last input X[(i, k, l), n] and the weights
+// W[(i, l, k), j] have k as their row index.  Two groups of four "splitter"
+// warps therefore sit between TMA and the MMA thread: they read a raw tile of
+// 32 k x 128 entries, transpose it and write the hi and lo operand tiles (core
+// matrices of 8 rows x 16 bytes, no swizzle).  In the batch-first layout the
+// input rows already hold consecutive k: the raw tile (128-byte swizzle) is the
+// hi operand as it stands and its splitters only add the lo tile.
+//
+// Warp roles (576 threads): warp 0 TMA producer, warp 1 TMEM owner and MMA
+// issuer, warps 2..5 input splitters, warps 6..9 weight splitters, warps
+// 10..17 epilogue (TMEM lane quarter = warp index mod 4).  Accumulator rows
+// are batch entries, columns are j.  A CTA keeps one j tile and walks a
+// contiguous range of (block, batch tile) pairs.  Waits are bounded and report
+// through the status word as in tc_kernel.cu.
+//
+// Reference counterparts: kernel_bs_last_float / kernel_bs_first_float
+// (src/ksmm_py/layer/kronecker_sparse/template_kernels_float.cuh:301-491, 51-299).
+#include <cuda.h>
+
+#include "tc_host.h"
+#include "tc_kernel.h"
+#include "tc_ptx.cuh"
+
+namespace ksmm {
+namespace tc {
+
+struct ParamsF {
+  int a, b, c, d;
+  int64_t batch;
+  int tiles_n, tiles_j;
+  uint32_t rows;        // blocks * tiles_n: (block, batch tile) pairs
+  uint32_t row_groups;  // CTAs per j tile
+  int nchunks;          // ceil(c / 32)
+  uint32_t idesc;
+  float alpha;
+  const float* bias;
+  int* status;
+};
+
+constexpr int kThreadsF = (2 + 4 + 4 + kEpilogueWarps) * 32;
+constexpr int kKC = 32;  // k values per chunk (128 bytes of fp32)
+
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ uint32_t lo_part(uint32_t v) {
+  return __float_as_uint(__uint_as_float(v) - __uint_as_float(v & 0xFFFFE000u));
+}
+
+// Transposes a raw tile [32 k][128 x] (512-byte rows) into the hi and lo operand
+// tiles [k / 4][x / 8][x % 8][4 k] (K-major core matrices, 2048 bytes per core
+// column).  Thread `t` of the group owns x = t.
+__device__ __forceinline__ void split_transposed(uint32_t rawbase, uint32_t hibase, uint32_t lobase,
+                                                 int t) {
+  const uint32_t dst = (t >> 3) * 128 + (t & 7) * 16;
+#pragma unroll
+  for (int kg = 0; kg < 8; ++kg) {
+    uint32_t v[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v[q]) : "r"(rawbase + (kg * 4 + q) * 512 + t * 4) : "memory");
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(hibase + kg * 2048 + dst),
+                 "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3])
+                 : "memory");
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(lobase + kg * 2048 + dst),
+                 "r"(lo_part(v[0])), "r"(lo_part(v[1])), "r"(lo_part(v[2])), "r"(lo_part(v[3]))
+                 : "memory");
+  }
+}
+
+// SRX / SRW: raw input / weight stages; SA: operand tile buffers (hi | lo) of
+// each kind.  In the batch-first flavour the raw input stage is the hi operand,
+// so the input ring holds SA stages of raw | lo and SRX is unused.
+template <bool BS_LAST, int NJ_, int SRX, int SRW, int SA_>
+struct CfgF {
+  static constexpr int NJ = NJ_;                    // j columns per accumulator (64 or 128)
+  static constexpr int SA = SA_;
+  static constexpr int XRAW_BYTES = kKC * 128 * 4;  // 32 k x 128 batch entries (either order)
+  static constexpr int WRAW_BYTES = kKC * NJ * 4;   // 32 k x NJ columns
+  static constexpr int XOP_BYTES = 2 * XRAW_BYTES;  // hi | lo
+  static constexpr int WOP_BYTES = 2 * WRAW_BYTES;
+  static constexpr int NXRAW = BS_LAST ? SRX : 0;
+  static constexpr int STG_WARP_BYTES = 32 * 128;   // 32 rows of 32 fp32
+  static constexpr int STG_BYTES = kEpilogueWarps * STG_WARP_BYTES;
+  // barriers: xraw full/empty, wraw full/empty, xop full/empty, wop full/empty, tmem full/empty
+  static constexpr int NBAR = 2 * (BS_LAST ? SRX : SA) + 2 * SRW + 4 * SA + 4;
+  static constexpr int BAR_BYTES = 512;
+  static constexpr int SMEM_BYTES = STG_BYTES + NXRAW * XRAW_BYTES + SRW * WRAW_BYTES +
+                                    SA * XOP_BYTES + SA * WOP_BYTES + BAR_BYTES + 1024;
+  static constexpr int NBUF = 2;
+  static constexpr int BUF_COLS = 2 * NJ;  // leading accumulator | small-terms accumulator
+  static constexpr int TMEM_COLS = NBUF * BUF_COLS;
+  static_assert(NJ == 64 || NJ == 128, "j tile");
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+  static_assert(SMEM_BYTES > 116 * 1024, "one CTA per SM, so that the TMEM allocation never waits");
+  static_assert(8 * NBAR + 16 <= BAR_BYTES, "barrier area");
+};
+
+template <bool BS_LAST, int NJ_, int SRX, int SRW, int SA_>
+__global__ void __launch_bounds__(kThreadsF, 1)
+    ksmm_tc_f32x3_kernel(const __grid_constant__ CUtensorMap tmX,
+                         const __grid_constant__ CUtensorMap tmW,
+                         const __grid_constant__ CUtensorMap tmY, const ParamsF P) {
+  using C = CfgF<BS_LAST, NJ_, SRX, SRW, SA_>;
+  constexpr int SA = C::SA;
+  constexpr int NXR = BS_LAST ? SRX : SA;  // stages the producer fills with input
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t sm0 = (raw + 1023u) & ~1023u;
+  uint8_t* sm_gen = smem_raw + (sm0 - raw);
+  const uint32_t stg0 = sm0;                               // epilogue staging tiles
+  const uint32_t xop0 = stg0 + C::STG_BYTES;               // input operands: hi | lo per buffer
+  const uint32_t wop0 = xop0 + SA * C::XOP_BYTES;          // weight operands: hi | lo per buffer
+  const uint32_t wraw0 = wop0 + SA * C::WOP_BYTES;         // raw weight tiles
+  const uint32_t xraw0 = wraw0 + SRW * C::WRAW_BYTES;      // raw input tiles (batch-last only)
+  const uint32_t bar0 = xraw0 + C::NXRAW * C::XRAW_BYTES;
+  uint8_t* bar_gen = sm_gen + (bar0 - sm0);
+  // input stage s: batch-last = raw tile s; batch-first = hi half of operand buffer s
+  auto xin_full = [&](int s) { return bar0 + 8u * s; };
+  auto xin_empty = [&](int s) { return bar0 + 8u * (NXR + s); };
+  auto wraw_full = [&](int s) { return bar0 + 8u * (2 * NXR + s); };
+  auto wraw_empty = [&](int s) { return bar0 + 8u * (2 * NXR + SRW + s); };
+  auto xop_full = [&](int s) { return bar0 + 8u * (2 * NXR + 2 * SRW + s); };
+  auto xop_empty = [&](int s) { return bar0 + 8u * (2 * NXR + 2 * SRW + SA + s); };
+  auto wop_full = [&](int s) { return bar0 + 8u * (2 * NXR + 2 * SRW + 2 * SA + s); };
+  auto wop_empty = [&](int s) { return bar0 + 8u * (2 * NXR + 2 * SRW + 3 * SA + s); };
+  auto tfull_bar = [&](int q) { return bar0 + 8u * (2 * NXR + 2 * SRW + 4 * SA + q); };
+  auto tempty_bar = [&](int q) { return bar0 + 8u * (2 * NXR + 2 * SRW + 4 * SA + 2 + q); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * C::NBAR);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 8 * C::NBAR + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NXR; ++s) {
+      mbar_init(xin_full(s), 1);
+      // batch-last: the four splitter warps hand the raw tile back;
+      // batch-first: the MMA commit frees the whole operand buffer (xop_empty), unused here
+      mbar_init(xin_empty(s), 4);
+    }
+    for (int s = 0; s < SRW; ++s) {
+      mbar_init(wraw_full(s), 1);
+      mbar_init(wraw_empty(s), 4);
+    }
+    for (int s = 0; s < SA; ++s) {
+      mbar_init(xop_full(s), 4);
+      mbar_init(xop_empty(s), 1);
+      mbar_init(wop_full(s), 4);
+      mbar_init(wop_empty(s), 1);
+    }
+    for (int q = 0; q < 2; ++q) {
+      mbar_init(tfull_bar(q), 1);
+      mbar_init(tempty_bar(q), kEpilogueWarps);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int nchunks = P.nchunks;
+  const int tj = static_cast<int>(blockIdx.x % P.tiles_j);
+  const uint32_t rc = blockIdx.x / P.tiles_j;
+  const uint32_t row_begin = static_cast<uint32_t>(static_cast<uint64_t>(rc) * P.rows / P.row_groups);
+  const uint32_t row_end = static_cast<uint32_t>(static_cast<uint64_t>(rc + 1) * P.rows / P.row_groups);
+  const int j0 = tj * C::NJ;
+
+  if (warp == 0) {
+    // ===================== TMA producer =====================
+    if (lane == 0) {
+      uint32_t xi = 0, xph = 0, wi = 0, wph = 0;
+      bool ok = true;
+      KSMM_TRACE_DECL;
+      for (uint32_t row = row_begin; row < row_end && ok; ++row) {
+        const int blk = static_cast<int>(row / P.tiles_n);  // batch-last: (i, l); batch-first: i
+        const int n0 = static_cast<int>(row % P.tiles_n) * 128;
+        for (int qc = 0; qc < nchunks; ++qc) {
+          // weights first: their splitters have the longer job
+          KSMM_TRACE(0, 1);
+          if (!mbar_wait<64>(wraw_empty(wi), wph ^ 1u, abort_flag, P.status, 31)) { ok = false; break; }
+          KSMM_TRACE(0, 2);
+          mbar_expect_tx(wraw_full(wi), C::WRAW_BYTES);
+          // weights (a*d*c, b) seen as (b, c, block in (i, l) order); batch-first has d = 1
+          tma_load_3d(wraw0 + wi * C::WRAW_BYTES, &tmW, wraw_full(wi), j0, qc * kKC, blk);
+          if (++wi == SRW) { wi = 0; wph ^= 1u; }
+          if constexpr (BS_LAST) {
+            if (!mbar_wait<64>(xin_empty(xi), xph ^ 1u, abort_flag, P.status, 32)) { ok = false; break; }
+            mbar_expect_tx(xin_full(xi), C::XRAW_BYTES);
+            tma_load_4d(xraw0 + xi * C::XRAW_BYTES, &tmX, xin_full(xi), n0, blk % P.d, qc * kKC,
+                        blk / P.d);
+          } else {
+            // the raw tile is the hi operand: it goes straight into the operand buffer,
+            // which the MMA commit frees
+            if (!mbar_wait<64>(xop_empty(xi), xph ^ 1u, abort_flag, P.status, 32)) { ok = false; break; }
+            mbar_expect_tx(xin_full(xi), C::XRAW_BYTES);
+            tma_load_3d(xop0 + xi * C::XOP_BYTES, &tmX, xin_full(xi), qc * kKC, blk, n0);
+          }
+          KSMM_TRACE(0, 3);
+          if (++xi == NXR) { xi = 0; xph ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ===================== MMA issuer =====================
+    if (lane == 0) {
+      uint32_t ai = 0, aph = 0, ut = 0;
+      bool ok = true;
+      KSMM_TRACE_DECL;
+      for (uint32_t row = row_begin; row < row_end && ok; ++row, ++ut) {
+        const uint32_t buf = ut % C::NBUF, bph = (ut / C::NBUF) & 1u;
+        KSMM_TRACE(1, 10);
+        if (!mbar_wait<0>(tempty_bar(buf), bph ^ 1u, abort_flag, P.status, 33)) { ok = false; break; }
+        KSMM_TRACE(1, 11);
+        tc_fence_after();
+        const uint32_t dcol = tmem_base + buf * C::BUF_COLS, dsmall = dcol + C::NJ;
+        for (int qc = 0; qc < nchunks; ++qc) {
+          KSMM_TRACE(1, 14);
+          if (!mbar_wait<0>(wop_full(ai), aph, abort_flag, P.status, 34)) { ok = false; break; }
+          KSMM_TRACE(1, 12);
+          if (!mbar_wait<0>(xop_full(ai), aph, abort_flag, P.status, 35)) { ok = false; break; }
+          KSMM_TRACE(1, 13);
+          tc_fence_after();
+          const uint32_t xb = xop0 + ai * C::XOP_BYTES, wb = wop0 + ai * C::WOP_BYTES;
+#pragma unroll
+          for (int ks = 0; ks < kKC / 8; ++ks) {
+            uint64_t xhi, xlo;
+            if constexpr (BS_LAST) {
+              // transposed tiles: core columns of 4 k, 2048 bytes apart; 8-row groups 128 bytes apart
+              xhi = make_desc(xb + ks * 2 * 2048, 2048, 128, 0);
+              xlo = make_desc(xb + C::XRAW_BYTES + ks * 2 * 2048, 2048, 128, 0);
+            } else {
+              // raw rows of 32 k with the 128-byte swizzle; a k step is 32 bytes inside the row
+              xhi = make_desc(xb + ks * 32, 16, 1024, 2);
+              xlo = make_desc(xb + C::XRAW_BYTES + ks * 32, 16, 1024, 2);
+            }
+            const uint64_t whi = make_desc(wb + ks * 2 * (C::NJ * 16), C::NJ * 16, 128, 0);
+            const uint64_t wlo =
+                make_desc(wb + C::WRAW_BYTES + ks * 2 * (C::NJ * 16), C::NJ * 16, 128, 0);
+            const uint32_t acc = (qc | ks) != 0 ? 1u : 0u;
+            umma_tf32(dsmall, xlo, whi, P.idesc, acc);
+            umma_tf32(dsmall, xhi, wlo, P.idesc, 1u);
+            umma_tf32(dcol, xhi, whi, P.idesc, acc);
+          }
+          KSMM_TRACE(1, 19);
+          umma_commit(xop_empty(ai));
+          umma_commit(wop_empty(ai));
+          if (++ai == SA) { ai = 0; aph ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(tfull_bar(buf));
+      }
+    }
+    __syncwarp();
+  } else if (warp < 6) {
+    // ===================== input splitters =====================
+    const int tt = (warp - 2) * 32 + lane;
+    uint32_t xi = 0, xph = 0, ai = 0, aph = 0;
+    bool ok = true;
+    KSMM_TRACE_DECL;
+    const bool tron = warp == 2 && lane == 0;
+    for (uint32_t row = row_begin; row < row_end && ok; ++row) {
+      for (int qc = 0; qc < nchunks; ++qc) {
+        int got = 1;
+        if (tron) KSMM_TRACE(2, 30);
+        if (lane == 0) {
+          got = mbar_wait<32>(xin_full(xi), xph, abort_flag, P.status, 36) ? 1 : 0;
+          if (tron) KSMM_TRACE(2, 31);
+          if (BS_LAST && got) got = mbar_wait<32>(xop_empty(ai), aph ^ 1u, abort_flag, P.status, 37) ? 1 : 0;
+        }
+        got = __shfl_sync(0xffffffffu, got, 0);
+        if (!got) { ok = false; break; }
+        if (tron) KSMM_TRACE(2, 33);
+        const uint32_t ob = xop0 + ai * C::XOP_BYTES;
+        if constexpr (BS_LAST) {
+          split_transposed(xraw0 + xi * C::XRAW_BYTES, ob, ob + C::XRAW_BYTES, tt);
+        } else {
+          // lo tile at the same (swizzled) offsets as the raw tile
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const uint32_t off = (tt + it * 128) * 16;
+            uint32_t v[4];
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+                         : "r"(ob + off)
+                         : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(ob + C::XRAW_BYTES + off),
+                         "r"(lo_part(v[0])), "r"(lo_part(v[1])), "r"(lo_part(v[2])), "r"(lo_part(v[3]))
+                         : "memory");
+          }
+        }
+        fence_proxy_async();  // the tiles are read by the tensor core through the async proxy
+        __syncwarp();
+        if (lane == 0) {
+          if (BS_LAST) mbar_arrive(xin_empty(xi));
+          mbar_arrive(xop_full(ai));
+        }
+        if (tron) KSMM_TRACE(2, 34);
+        if (++xi == NXR) { xi = 0; xph ^= 1u; }
+        if (++ai == SA) { ai = 0; aph ^= 1u; }
+      }
+    }
+    __syncwarp();
+  } else if (warp < 10) {
+    // ===================== weight splitters =====================
+    // raw tile [32 k][NJ j] -> hi / lo tiles [k / 4][j / 8][j % 8][4 k]; thread t owns j = t
+    const int tt = (warp - 6) * 32 + lane;
+    uint32_t wi = 0, wph = 0, ai = 0, aph = 0;
+    bool ok = true;
+    KSMM_TRACE_DECL;
+    const bool tron = warp == 6 && lane == 0;
+    for (uint32_t row = row_begin; row < row_end && ok; ++row) {
+      for (int qc = 0; qc < nchunks; ++qc) {
+        int got = 1;
+        if (tron) KSMM_TRACE(3, 40);
+        if (lane == 0) {
+          got = mbar_wait<32>(wraw_full(wi), wph, abort_flag, P.status, 38) ? 1 : 0;
+          if (tron) KSMM_TRACE(3, 41);
+          if (got) got = mbar_wait<32>(wop_empty(ai), aph ^ 1u, abort_flag, P.status, 39) ? 1 : 0;
+        }
+        got = __shfl_sync(0xffffffffu, got, 0);
+        if (!got) { ok = false; break; }
+        if (tron) KSMM_TRACE(3, 43);
+        if (tt < C::NJ) {
+          const uint32_t rb = wraw0 + wi * C::WRAW_BYTES;
+          const uint32_t hb = wop0 + ai * C::WOP_BYTES, lb = hb + C::WRAW_BYTES;
+          const uint32_t dst = (tt >> 3) * 128 + (tt & 7) * 16;
+#pragma unroll
+          for (int kg = 0; kg < 8; ++kg) {
+            uint32_t v[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              asm volatile("ld.shared.b32 %0, [%1];"
+                           : "=r"(v[q])
+                           : "r"(rb + (kg * 4 + q) * (C::NJ * 4) + tt * 4)
+                           : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(hb + kg * (C::NJ * 16) + dst),
+                         "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3])
+                         : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(lb + kg * (C::NJ * 16) + dst),
+                         "r"(lo_part(v[0])), "r"(lo_part(v[1])), "r"(lo_part(v[2])), "r"(lo_part(v[3]))
+                         : "memory");
+          }
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(wraw_empty(wi));
+          mbar_arrive(wop_full(ai));
+        }
+        if (tron) KSMM_TRACE(3, 44);
+        if (++wi == SRW) { wi = 0; wph ^= 1u; }
+        if (++ai == SA) { ai = 0; aph ^= 1u; }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ===================== epilogue =====================
+    // A warp owns 32 accumulator rows (batch entries) and every other group of
+    // 32 columns (j); one staging tile of 32 x 32 fp32 per TMA store.
+    const int ew = warp - 10;
+    const int q = warp & 3;
+    const int grp = ew >> 2;
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    const bool plain = (P.alpha == 1.f) && (P.bias == nullptr);
+    const uint32_t stg = stg0 + ew * C::STG_WARP_BYTES;
+    uint32_t ut = 0;
+    for (uint32_t row = row_begin; row < row_end; ++row, ++ut) {
+      const int blk = static_cast<int>(row / P.tiles_n);
+      const int n0 = static_cast<int>(row % P.tiles_n) * 128;
+      const uint32_t buf = ut % C::NBUF, bph = (ut / C::NBUF) & 1u;
+      int got = 1;
+      if (lane == 0) got = mbar_wait<128>(tfull_bar(buf), bph, abort_flag, P.status, 40) ? 1 : 0;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (!got) break;
+      tc_fence_after();
+      const bool warp_active = n0 + q * 32 < P.batch;
+      int jlim = P.b - j0;
+      if (jlim > C::NJ) jlim = C::NJ;
+      const int n_it = warp_active ? ((jlim + 31) / 32 - grp + 1) / 2 : 0;
+      bool released = false;
+#pragma unroll 1
+      for (int it = 0; it < n_it; ++it) {
+        const int jj0 = (grp + 2 * it) * 32;
+        uint32_t r[32], rs[32];
+        tmem_ld32(tmem_base + lane_addr + buf * C::BUF_COLS + jj0, r);
+        tmem_ld32(tmem_base + lane_addr + buf * C::BUF_COLS + C::NJ + jj0, rs);
+        tmem_ld_wait();
+        if (it == n_it - 1) {
+          // the accumulator is in registers: the MMA warp may overwrite it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty_bar(buf));
+          released = true;
+        }
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj)
+          r[jj] = __float_as_uint(__uint_as_float(r[jj]) + __uint_as_float(rs[jj]));
+        if (!plain) {
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) {
+            float bv = 0.f;
+            const int j = j0 + jj0 + jj;
+            if (P.bias != nullptr && j < P.b) {
+              // output feature: batch-last (i*b + j)*d + l with blk = i*d + l; batch-first i*b + j
+              const int64_t f = BS_LAST ? (static_cast<int64_t>(blk / P.d) * P.b + j) * P.d + blk % P.d
+                                        : static_cast<int64_t>(blk) * P.b + j;
+              bv = P.bias[f];
+            }
+            r[jj] = __float_as_uint(fmaf(P.alpha, __uint_as_float(r[jj]), bv));
+          }
+        }
+        if (lane == 0) bulk_wait_read<0>();  // the previous store has read the staging tile
+        __syncwarp();
+        if constexpr (BS_LAST) {
+          // staging tile [32 j][32 n]: lane = n, so every store fills one 128-byte row segment
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj)
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(stg + jj * 128 + lane * 4), "r"(r[jj]) : "memory");
+        } else {
+          // staging tile [32 n][32 j], 128-byte swizzle: lane = n owns one row
+          const uint32_t rowaddr = stg + lane * 128;
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + ((ch ^ (lane & 7)) << 4)),
+                         "r"(r[ch * 4 + 0]), "r"(r[ch * 4 + 1]), "r"(r[ch * 4 + 2]), "r"(r[ch * 4 + 3])
+                         : "memory");
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (BS_LAST)
+            tma_store_4d(&tmY, stg, n0 + q * 32, blk % P.d, j0 + jj0, blk / P.d);
+          else
+            tma_store_3d(&tmY, stg, j0 + jj0, blk, n0 + q * 32);
+          bulk_commit();
+        }
+      }
+      if (!released) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(buf));
+      }
+    }
+    if (lane == 0) bulk_wait<0>();
+    __syncwarp();
+  }
+
+  // ===================== teardown =====================
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    __nanosleep(20000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+template <bool BS_LAST, int NJ_, int SRX, int SRW, int SA_>
+static int launch_f(const Problem& p, cudaStream_t stream) {
+  using C = CfgF<BS_LAST, NJ_, SRX, SRW, SA_>;
+  auto kern = ksmm_tc_f32x3_kernel<BS_LAST, NJ_, SRX, SRW, SA_>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess)
+      return set_error(KSMM_ERR_CUDA, "cannot reserve %d bytes of shared memory: %s",
+                       C::SMEM_BYTES, cudaGetErrorString(e));
+    attr_set[dev] = true;
+  }
+  const uint64_t a = p.a, b = p.b, c = p.c, d = p.d, B = p.batch;
+  CUtensorMap tmX, tmW, tmY;
+  int st;
+  if (BS_LAST) {
+    // input (a*c*d, batch): row (i*c + k)*d + l; raw tile = 32 k x 128 batch entries, plain rows
+    const uint64_t dims[4] = {B, d, c, a};
+    const uint64_t str[4] = {1, B, d * B, c * d * B};
+    const uint32_t box[4] = {128, 1, kKC, 1};
+    if ((st = encode_map(&tmX, KSMM_F32, 4, p.in, dims, str, box, false)) != KSMM_OK) return st;
+  } else {
+    // input (batch, a*c): tile = 128 rows x 32 k of block i, 128-byte swizzle (it is the hi operand)
+    const uint64_t dims[3] = {c, a, B};
+    const uint64_t str[3] = {1, c, a * c};
+    const uint32_t box[3] = {kKC, 1, 128};
+    if ((st = encode_map(&tmX, KSMM_F32, 3, p.in, dims, str, box, true)) != KSMM_OK) return st;
+  }
+  {
+    // weights (a*d*c, b) row-major seen as (b, c, a*d); raw tile = 32 k x NJ columns, plain rows
+    const uint64_t dims[3] = {b, c, a * d};
+    const uint64_t str[3] = {1, b, c * b};
+    const uint32_t box[3] = {static_cast<uint32_t>(C::NJ), kKC, 1};
+    if ((st = encode_map(&tmW, KSMM_F32, 3, p.w, dims, str, box, false)) != KSMM_OK) return st;
+  }
+  if (BS_LAST) {
+    // output (a*b*d, batch): row (i*b + j)*d + l; store = 32 j x 32 batch entries
+    const uint64_t dims[4] = {B, d, b, a};
+    const uint64_t str[4] = {1, B, d * B, b * d * B};
+    const uint32_t box[4] = {32, 1, 32, 1};
+    if ((st = encode_map(&tmY, KSMM_F32, 4, p.out, dims, str, box, false)) != KSMM_OK) return st;
+  } else {
+    // output (batch, a*b): store = 32 rows x 32 j of block i, 128-byte swizzle
+    const uint64_t dims[3] = {b, a, B};
+    const uint64_t str[3] = {1, b, a * b};
+    const uint32_t box[3] = {32, 1, 32};
+    if ((st = encode_map(&tmY, KSMM_F32, 3, p.out, dims, str, box, true)) != KSMM_OK) return st;
+  }
+  ParamsF P;
+  P.a = p.a; P.b = p.b; P.c = p.c; P.d = p.d;
+  P.batch = p.batch;
+  P.tiles_n = static_cast<int>((B + 127) / 128);
+  P.tiles_j = static_cast<int>((b + C::NJ - 1) / C::NJ);
+  P.nchunks = (p.c + kKC - 1) / kKC;
+  P.alpha = p.alpha;
+  P.bias = static_cast<const float*>(p.bias);
+  P.status = status_word();
+  if (!P.status) return set_error(KSMM_ERR_CUDA, "cannot resolve the device status word");
+  // fp32 accumulate, tf32 operands, both K-major, N = NJ, M = 128
+  P.idesc = (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(C::NJ >> 3) << 17) |
+            (static_cast<uint32_t>(128 >> 4) << 24);
+  const int sms = num_sms();
+  if (sms <= 0) return set_error(KSMM_ERR_NO_DEVICE, "no CUDA device");
+  const int64_t rows = static_cast<int64_t>(P.tiles_n) * p.a * p.d;
+  if (rows <= 0 || rows > 0x7fffffffLL || P.tiles_j > sms)
+    return set_error(KSMM_ERR_UNSUPPORTED, "tensor-core family: work-split limits exceeded");
+  P.rows = static_cast<uint32_t>(rows);
+  int64_t groups = sms / P.tiles_j;
+  if (groups > rows) groups = rows;
+  P.row_groups = static_cast<uint32_t>(groups);
+  const unsigned grid = static_cast<unsigned>(groups * P.tiles_j);
+  kern<<<grid, kThreadsF, C::SMEM_BYTES, stream>>>(tmX, tmW, tmY, P);
+  count_launch();
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess)
+    return set_error(KSMM_ERR_CUDA, "tensor-core kernel launch failed: %s", cudaGetErrorString(err));
+  return KSMM_OK;
+}
+
+}  // namespace tc
+
+bool tc_f32x3_supported(const Problem& p, bool check_pointers) {
+  if (p.in_dtype != KSMM_F32 || p.out_dtype != KSMM_F32) return false;
+  if (p.batch <= 0 || p.batch > 0x7fffffffLL) return false;
+  // tensor-map rules: every global stride is a multiple of 16 bytes
+  if (p.b % 4 != 0) return false;
+  if (p.bs_last) {
+    if (p.batch % 4 != 0) return false;
+  } else {
+    if (p.d != 1 || p.c % 4 != 0) return false;
+  }
+  if (check_pointers) {
+    if (reinterpret_cast<uintptr_t>(p.in) % 16 || reinterpret_cast<uintptr_t>(p.w) % 16 ||
+        reinterpret_cast<uintptr_t>(p.out) % 16)
+      return false;
+  }
+  return true;
+}
+
+int tc_f32x3_launch(const Problem& p, cudaStream_t stream) {
+  // <batch-last, j tile, raw input stages, raw weight stages, operand buffers>
+  if (p.bs_last)
+    return p.b > 64 ? tc::launch_f<true, 128, 2, 2, 2>(p, stream)
+                    : tc::launch_f<true, 64, 3, 4, 2>(p, stream);
+  return p.b > 64 ? tc::launch_f<false, 128, 0, 4, 2>(p, stream)
+                  : tc::launch_f<false, 64, 0, 4, 3>(p, stream);
+}
+
+}  // namespace ksmm
+
+#ifdef KSMM_TC_TRACE
+extern "C" __attribute__((visibility("default"))) int ksmm_debug_trace_f(unsigned long long* host) {
+  using namespace ksmm;
+  return static_cast<int>(cudaMemcpyFromSymbol(host, tc::g_trace, sizeof(tc::g_trace)));
+}
+extern "C" __attribute__((visibility("default"))) int ksmm_debug_trace_f_clear() {
+  using namespace ksmm;
+  static unsigned long long zeros[4][8192];
+  return static_cast<int>(cudaMemcpyToSymbol(tc::g_trace, zeros, sizeof(zeros)));
+}
+#endif

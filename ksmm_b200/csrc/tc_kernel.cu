@@ -607,10 +607,10 @@ int tc_num_configs() { return tc::kNumConfigs; }
 
 bool tc_config_supported(const Problem& p, int config, bool check_pointers) {
   if (config < 0 || config >= tc::kNumConfigs) return false;
+  if (p.in_dtype == KSMM_F32) return config == 0 && tc_f32x3_supported(p, check_pointers);
   if (!p.bs_last && p.d != 1) return config == 0 && tc_bsfirst_d_supported(p, check_pointers);
   if (config == 4 && p.in_dtype == KSMM_F8E4M3) return false;
   const int es = dtype_size(p.in_dtype), os = dtype_size(p.out_dtype);
-  if (p.in_dtype == KSMM_F32) return false;
   if (p.in_dtype == KSMM_F16 || p.in_dtype == KSMM_BF16) {
     if (p.out_dtype != p.in_dtype) return false;
   } else if (p.in_dtype != KSMM_F8E4M3) {
@@ -638,6 +638,9 @@ int tc_default_config(const Problem& p) {
   if (!tc_config_supported(p, 0, true)) return -1;
   // tiny blocks are bandwidth problems that the FFMA family tiles more tightly
   if (p.b < 32 || p.c < 16) return -1;
+  // fp32 on the tensor cores: the accumulator truncates once per k step of 8, so the default
+  // stops at c = 1024 (relative error about 2e-6 at c = 768); longer sums take the FFMA family
+  if (p.in_dtype == KSMM_F32) return p.c <= 1024 ? 0 : -1;
   if (!p.bs_last && p.d != 1) return 0;
   if (p.bs_last) return p.batch >= 256 * 148 / 2 || p.batch >= 4096 ? 0 : 1;
   return p.b > 128 ? 0 : (p.b > 64 ? 1 : 4);
@@ -651,6 +654,7 @@ int tc_launch(const Problem& p, int config, cudaStream_t stream) {
                      "bs_last %d (alignment or layout rule)",
                      p.a, p.b, p.c, p.d, static_cast<long long>(p.batch), p.in_dtype, p.bs_last);
   const bool last = p.bs_last != 0;
+  if (p.in_dtype == KSMM_F32) return tc_f32x3_launch(p, stream);
   if (!last && p.d != 1) return tc_bsfirst_d_launch(p, stream);
   if (p.in_dtype == KSMM_F8E4M3) {
     if (p.out_dtype == KSMM_F32)

@@ -21,4 +21,8 @@ int tc_check_device(cudaStream_t stream);
 bool tc_bsfirst_d_supported(const Problem& p, bool check_pointers);
 int tc_bsfirst_d_launch(const Problem& p, cudaStream_t stream);
 
+// fp32 factors as three tf32 products per term (tc_f32x3.cu); a single configuration
+bool tc_f32x3_supported(const Problem& p, bool check_pointers);
+int tc_f32x3_launch(const Problem& p, cudaStream_t stream);
+
 }  // namespace ksmm

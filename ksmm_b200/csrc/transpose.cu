@@ -4,8 +4,9 @@
 //
 // One CTA moves a 64 x 64 tile through shared memory: 16-byte global loads
 // along the input rows, element-wise shared stores into a padded tile, strided
-// shared reads along the tile columns, 16-byte global stores along the output
-// rows.  Edges and unaligned shapes fall back to element accesses.
+// shared reads along the tile columns, 16-byte global stores in which the lanes
+// of a warp follow the output rows (whole 128-byte lines per warp).  Edges and
+// unaligned shapes fall back to element accesses.
 #include "common.cuh"
 
 namespace ksmm {
@@ -45,7 +46,8 @@ __global__ void __launch_bounds__(256)
   if (full) {
     constexpr int VPR = TILE / V;
     for (int v = tid; v < TILE * VPR; v += 256) {
-      const int c = v % TILE, rv = v / TILE;  // lanes walk consecutive tile columns
+      // lanes walk along an output row, so that a warp writes whole 128-byte lines
+      const int c = v / VPR, rv = v % VPR;
       uint4 raw;
       T* e = reinterpret_cast<T*>(&raw);
 #pragma unroll
