@@ -311,36 +311,72 @@ def run_ours(args, rank, world, local_rank):
     ffma = ctypes.c_float(0.0)
     _lib.check(lib.ksmm_cu_measure_ffma_peak(ctypes.byref(ffma), None))
     ffma_peak = float(ffma.value)
+    # Compute roofs.  fp16: the measured dense bf16 tensor throughput.  fp32: what the library's
+    # default runs decides: the FFMA kernels are bound by the fp32 FMA rate (live probe); the
+    # tensor-core kernel issues three tf32 MMAs per product, and tf32 runs at half the bf16
+    # rate, so its roof for useful flops is the measured bf16 figure / 6.
+    tf32x3_peak = peaks["bf16_tflops"] / 6.0
     per = []
+    ms_exact = {}
     for idx, c in enumerate(cs):
         ms = case_ms(c)
+        tdt = torch.float32 if c["dtype"] == "fp32" else torch.float16
+        family, cfg, conv = kb.default_choice(c["pattern"], BATCH, tdt, c["bs_last"])
         t_hbm = c["bytes"] / (peaks["hbm_gbs"] * 1e9)
-        pk = ffma_peak if c["dtype"] == "fp32" else peaks["bf16_tflops"]
+        if c["dtype"] != "fp32":
+            pk, cb = peaks["bf16_tflops"], "tensor"
+        elif family == "tensor":
+            pk, cb = tf32x3_peak, "tensor_tf32x3"
+        else:
+            pk, cb = ffma_peak, "ffma"
         t_fl = c["flops"] / (pk * 1e12)
         t_roof = max(t_hbm, t_fl)
+        ms_ffma = None
+        if c["dtype"] == "fp32" and (family == "tensor") and not args.only:
+            # the same case on the exact-fp32 FFMA family, for the comparison line below
+            ms_ffma = ms_exact[idx] = case_ms(c, _lib.KSMM_ALGO_SIMT, -1)
         per.append({"pattern": list(c["pattern"]), "dtype": c["dtype"],
                     "layout": "bs_last" if c["bs_last"] else "bs_first", "ms": round(ms, 5),
+                    "ms_ffma_family": None if ms_ffma is None else round(ms_ffma, 5),
+                    "kernel": family + (" via transposes" if conv else ""),
                     "gbs": round(c["bytes"] / (ms * 1e-3) / 1e9, 1),
                     "tflops": round(c["flops"] / (ms * 1e-3) / 1e12, 2),
-                    "bound": "hbm" if t_hbm >= t_fl else ("ffma" if c["dtype"] == "fp32" else "tensor"),
+                    "bound": "hbm" if t_hbm >= t_fl else cb,
                     "roofline_frac": round(t_roof / (ms * 1e-3), 4)})
 
     def roofline_of(entry, c):
         ms = entry["ms"]
         if entry["bound"] == "hbm":
             ach, pk, unit = c["bytes"] / (ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s"
+            src = f"MEASURED_PEAKS.json ({peaks['source']})"
         else:
             ach = c["flops"] / (ms * 1e-3) / 1e12
-            pk = ffma_peak if entry["bound"] == "ffma" else peaks["bf16_tflops"]
             unit = "TFLOP/s"
-        return {"bound": entry["bound"], "achieved": round(ach, 2), "peak": round(pk, 2), "unit": unit,
+            if entry["bound"] == "ffma":
+                pk = ffma_peak
+                src = "ksmm_cu_measure_ffma_peak (live FFMA probe; no fp32 figure in MEASURED_PEAKS.json)"
+            elif entry["bound"] == "tensor_tf32x3":
+                pk = tf32x3_peak
+                src = (f"MEASURED_PEAKS.json ({peaks['source']}) bf16_tflops / 6: tf32 at half the bf16 "
+                       "rate, three MMAs per product")
+            else:
+                pk = peaks["bf16_tflops"]
+                src = f"MEASURED_PEAKS.json ({peaks['source']})"
+        return {"bound": "tensor" if entry["bound"] == "tensor_tf32x3" else entry["bound"],
+                "achieved": round(ach, 2), "peak": round(pk, 2), "unit": unit,
                 "frac": round(ach / pk, 4), "traffic": None,
-                "kernel": f"{entry['dtype']} {entry['layout']} {tuple(entry['pattern'])}",
-                "peak_source": ("ksmm_cu_measure_ffma_peak (live FFMA probe; no fp32 figure in "
-                                "MEASURED_PEAKS.json)" if entry["bound"] == "ffma"
-                                else f"MEASURED_PEAKS.json ({peaks['source']})"),
+                "kernel": f"{entry['dtype']} {entry['layout']} {tuple(entry['pattern'])} ({entry['kernel']})",
+                "peak_source": src,
                 "share_of_step": round(ms / (elapsed_ms / args.steps), 4)}
 
+    # the sweep with every fp32 case on the FFMA family (sum of the per-case launch durations)
+    fp32_exact = None
+    if ms_exact:
+        t_all = sum(ms_exact.get(q, per[q]["ms"]) for q in range(len(cs)))
+        fp32_exact = {"value": round(world * step_flops / (t_all * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+                      "ms_per_step": round(t_all, 4),
+                      "note": "same sweep with algo=KSMM_ALGO_SIMT (fp32 FFMA, no tf32 split) for the fp32 "
+                              "cases; sum of per-case launch durations"}
     dom = max(range(len(cs)), key=lambda q: per[q]["ms"])
     hbm_idx = [q for q in range(len(cs)) if per[q]["bound"] == "hbm"]
     dom_hbm = max(hbm_idx, key=lambda q: per[q]["ms"]) if hbm_idx else None
@@ -456,11 +492,13 @@ def run_ours(args, rank, world, local_rank):
         "metric": "ksmm_sweep_throughput", "value": value, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32+f16 (fp32 accumulate)", "data": "synthetic",
+        "dtype": "f32 (three tf32 tensor-core products per term where the default dispatch picks that "
+                 "kernel, else fp32 FFMA) + f16; fp32 accumulate",
+        "data": "synthetic",
         "config": workload_config(), "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
         "roofline": roofline_of(per[dom], cs[dom]),
         "roofline_hbm": roofline_of(per[dom_hbm], cs[dom_hbm]) if dom_hbm is not None else None,
-        "ffma_peak_tflops": round(ffma_peak, 2),
+        "ffma_peak_tflops": round(ffma_peak, 2), "fp32_ffma_only": fp32_exact,
         "cpu_baseline": cpu, "ksvit_b": ksvit, "per_pattern": per,
     }
     print(json.dumps(line), flush=True)

@@ -189,6 +189,11 @@ KSMM_API int ksmm_cu_chain_forward_host(const void* host_input, const void* cons
  *   in the in-process cache, and reports it.  best_ms may be NULL.
  * ksmm_cu_set_choice / ksmm_cu_get_choice: write / read the cache directly,
  *   so that a saved table can be re-loaded without re-timing.
+ * ksmm_cu_default_choice: what KSMM_ALGO_AUTO runs for this problem (a cached
+ *   choice if there is one, else the heuristic): the kernel family, its
+ *   configuration (-1 = the family's own default) and whether the call goes
+ *   through the layout-conversion path (transpose, batch-last kernel,
+ *   transpose).  Pointers in `desc` are only checked for alignment.
  */
 KSMM_API int ksmm_cu_num_configs(int algo);
 KSMM_API int ksmm_cu_config_supported(int algo, int config, int64_t batch, int a, int b, int c, int d,
@@ -199,6 +204,8 @@ KSMM_API int ksmm_cu_set_choice(int64_t batch, int a, int b, int c, int d, int i
                        int bs_last, int algo, int config);
 KSMM_API int ksmm_cu_get_choice(int64_t batch, int a, int b, int c, int d, int in_dtype, int out_dtype,
                        int bs_last, int* algo, int* config);
+KSMM_API int ksmm_cu_default_choice(const ksmm_forward_desc_t* desc, int* algo, int* config,
+                           int* via_transpose);
 
 /*
  * Synchronises `stream` and returns KSMM_ERR_DEVICE_TIMEOUT if a kernel

@@ -29,7 +29,8 @@ EXPORTS = (
     "ksmm_cu_version", "ksmm_cu_last_error", "ksmm_cu_status_string", "ksmm_cu_forward",
     "ksmm_cu_forward_ex", "ksmm_cu_chain_workspace_bytes", "ksmm_cu_chain_forward",
     "ksmm_cu_chain_forward_static", "ksmm_cu_chain_forward_host", "ksmm_cu_num_configs", "ksmm_cu_config_supported",
-    "ksmm_cu_tune", "ksmm_cu_set_choice", "ksmm_cu_get_choice", "ksmm_cu_check_device",
+    "ksmm_cu_tune", "ksmm_cu_set_choice", "ksmm_cu_get_choice", "ksmm_cu_default_choice",
+    "ksmm_cu_check_device",
     "ksmm_cu_launch_count", "ksmm_cu_measure_ffma_peak",
 )
 
@@ -96,6 +97,9 @@ def load():
     lib.ksmm_cu_get_choice.restype = i32
     lib.ksmm_cu_get_choice.argtypes = [i64, i32, i32, i32, i32, i32, i32, i32,
                                        ctypes.POINTER(i32), ctypes.POINTER(i32)]
+    lib.ksmm_cu_default_choice.restype = i32
+    lib.ksmm_cu_default_choice.argtypes = [ctypes.POINTER(ForwardDesc), ctypes.POINTER(i32),
+                                           ctypes.POINTER(i32), ctypes.POINTER(i32)]
     lib.ksmm_cu_check_device.restype = i32
     lib.ksmm_cu_check_device.argtypes = [vp]
     lib.ksmm_cu_launch_count.restype = ctypes.c_uint64

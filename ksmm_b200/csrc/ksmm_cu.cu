@@ -630,6 +630,40 @@ int ksmm_cu_get_choice(int64_t batch, int a, int b, int c, int d, int in_dtype, 
   return KSMM_OK;
 }
 
+int ksmm_cu_default_choice(const ksmm_forward_desc_t* desc, int* algo, int* config,
+                           int* via_transpose) {
+  if (!desc) return set_error(KSMM_ERR_BAD_ARGUMENT, "null descriptor");
+  Problem p = problem_of(*desc);
+  int st = check_problem(p);
+  if (st != KSMM_OK) return st;
+  int al = KSMM_ALGO_SIMT, cfg = -1, conv = 0;
+  Choice ch;
+  if (lookup_choice(p, &ch)) {
+    al = ch.algo;
+    cfg = ch.config;
+  } else if (tc_default_config(p) >= 0) {
+    al = KSMM_ALGO_TC;
+    cfg = tc_default_config(p);
+  } else if (conversion_applies(p)) {
+    // the batch-last problem the conversion path dispatches
+    conv = 1;
+    Problem q = p;
+    q.bs_last = 1;
+    q.in = q.out = reinterpret_cast<void*>(256);
+    if (lookup_choice(q, &ch)) {
+      al = ch.algo;
+      cfg = ch.config;
+    } else if (tc_default_config(q) >= 0) {
+      al = KSMM_ALGO_TC;
+      cfg = tc_default_config(q);
+    }
+  }
+  if (algo) *algo = al;
+  if (config) *config = cfg;
+  if (via_transpose) *via_transpose = conv;
+  return KSMM_OK;
+}
+
 int ksmm_cu_measure_ffma_peak(float* tflops, void* stream) {
   if (!tflops) return set_error(KSMM_ERR_BAD_ARGUMENT, "null result pointer");
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -101,6 +101,22 @@ def forward_ex(input, factor, bs_last, a, b, c, d, *, out_dtype=None, alpha=1.0,
     return out
 
 
+def default_choice(pattern, batch, dtype, bs_last, out_dtype=None):
+    """What the automatic dispatch runs for one factor: ``(family, config, via_transpose)`` with
+    family ``"ffma"`` or ``"tensor"``; ``via_transpose`` is true when the call goes through the
+    layout-conversion path (transpose, batch-last kernel, transpose)."""
+    lib = _lib.load()
+    a, b, c, d = (int(v) for v in pattern)
+    out_dtype = dtype if out_dtype is None else out_dtype
+    desc = ForwardDesc(input=256, values=256, output=256, bias=None, batch=int(batch), a=a, b=b, c=c,
+                       d=d, in_dtype=dtype_code(dtype), out_dtype=dtype_code(out_dtype),
+                       bs_last=int(bool(bs_last)), algo=0, config=-1, alpha=1.0)
+    algo, cfg, conv = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    _lib.check(lib.ksmm_cu_default_choice(ctypes.byref(desc), ctypes.byref(algo), ctypes.byref(cfg),
+                                          ctypes.byref(conv)))
+    return ("tensor" if algo.value == _lib.KSMM_ALGO_TC else "ffma"), cfg.value, bool(conv.value)
+
+
 class Kernel:
     """Drop-in for the reference's ``Kernel`` (kernel.py:62-329).  Inference
     only, like the reference (its ``backward`` is a stub, kernel.py:323-329)."""

@@ -90,9 +90,14 @@ def test_config_tables():
     F16, F32, F8, BF16 = _lib.KSMM_F16, _lib.KSMM_F32, _lib.KSMM_F8E4M3, _lib.KSMM_BF16
     # the fp32 FFMA family takes anything
     assert sup(_lib.KSMM_ALGO_SIMT, 0, 25088, 1, 449, 514, 3, F32, F32, 0) == 1
-    # tensor-core family: 16-bit and fp8 only, TMA stride rules
+    # tensor-core family: TMA stride rules; fp32 (three tf32 products) has one configuration and
+    # covers batch-last and batch-first d = 1
     assert sup(_lib.KSMM_ALGO_TC, 0, 25088, 1, 768, 192, 4, F16, F16, 1) == 1
-    assert sup(_lib.KSMM_ALGO_TC, 0, 25088, 1, 768, 192, 4, F32, F32, 1) == 0
+    assert sup(_lib.KSMM_ALGO_TC, 0, 25088, 1, 768, 192, 4, F32, F32, 1) == 1
+    assert sup(_lib.KSMM_ALGO_TC, 1, 25088, 1, 768, 192, 4, F32, F32, 1) == 0
+    assert sup(_lib.KSMM_ALGO_TC, 0, 25088, 1, 768, 192, 4, F32, F32, 0) == 0
+    assert sup(_lib.KSMM_ALGO_TC, 0, 25088, 4, 192, 192, 1, F32, F32, 0) == 1
+    assert sup(_lib.KSMM_ALGO_TC, 0, 25086, 4, 192, 192, 1, F32, F32, 1) == 0   # batch*4 % 16 != 0
     assert sup(_lib.KSMM_ALGO_TC, 0, 25087, 1, 768, 192, 4, F16, F16, 1) == 0   # batch*2 % 16 != 0
     assert sup(_lib.KSMM_ALGO_TC, 0, 25088, 1, 449, 192, 4, F16, F16, 1) == 0   # b*2 % 16 != 0
     assert sup(_lib.KSMM_ALGO_TC, 0, 25088, 4, 192, 192, 1, BF16, BF16, 0) == 1
@@ -109,3 +114,17 @@ def test_choice_cache_round_trip():
     assert (algo.value, cfg.value) == (_lib.KSMM_ALGO_SIMT, 1)
     # a configuration that cannot run the problem is refused
     assert lib.ksmm_cu_set_choice(77, 1, 64, 64, 1, 0, 0, 1, _lib.KSMM_ALGO_TC, 0) == _lib.KSMM_ERR_UNSUPPORTED
+
+
+def test_default_choice_reports_family_and_conversion_path():
+    """What the automatic dispatch would run (no launch is made): fp32 and fp16 benchmark factors go
+    to the tensor-core family; a batch-first d = 16 factor goes through the layout conversion; a
+    block too small for the tensor cores stays on the FFMA family."""
+    import torch
+    import ksmm_b200 as kb
+    assert kb.default_choice((1, 768, 192, 4), 4096, torch.float32, True)[::2] == ("tensor", False)
+    assert kb.default_choice((1, 768, 192, 4), 4096, torch.float16, False)[::2] == ("tensor", False)
+    assert kb.default_choice((1, 64, 64, 16), 4096, torch.float16, False)[::2] == ("tensor", True)
+    assert kb.default_choice((4, 64, 64, 4), 4096, torch.float32, False)[::2] == ("ffma", False)
+    assert kb.default_choice((1, 8, 8, 1), 4096, torch.float32, True)[::2] == ("ffma", False)
+    assert kb.default_choice((1, 64, 2048, 1), 4096, torch.float32, True)[0] == "ffma"  # c > 1024
