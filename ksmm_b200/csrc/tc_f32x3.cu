@@ -102,7 +102,7 @@ __device__ __forceinline__ void split_transposed(uint32_t rawbase, uint32_t hiba
 // so the input ring holds SA stages of raw | lo and SRX is unused.
 template <bool BS_LAST, int NJ_, int SRX, int SRW, int SA_>
 struct CfgF {
-  static constexpr int NJ = NJ_;                    // j columns per accumulator (64 or 128)
+  static constexpr int NJ = NJ_;                    // j columns per accumulator (64, 96 or 128)
   static constexpr int SA = SA_;
   static constexpr int XRAW_BYTES = kKC * 128 * 4;  // 32 k x 128 batch entries (either order)
   static constexpr int WRAW_BYTES = kKC * NJ * 4;   // 32 k x NJ columns
@@ -118,8 +118,9 @@ struct CfgF {
                                     SA * XOP_BYTES + SA * WOP_BYTES + BAR_BYTES + 1024;
   static constexpr int NBUF = 2;
   static constexpr int BUF_COLS = 2 * NJ;  // leading accumulator | small-terms accumulator
-  static constexpr int TMEM_COLS = NBUF * BUF_COLS;
-  static_assert(NJ == 64 || NJ == 128, "j tile");
+  // allocations are powers of two
+  static constexpr int TMEM_COLS = NBUF * BUF_COLS <= 128 ? 128 : (NBUF * BUF_COLS <= 256 ? 256 : 512);
+  static_assert(NJ == 64 || NJ == 96 || NJ == 128, "j tile");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
   static_assert(SMEM_BYTES > 116 * 1024, "one CTA per SM, so that the TMEM allocation never waits");
   static_assert(8 * NBAR + 16 <= BAR_BYTES, "barrier area");
@@ -597,12 +598,22 @@ bool tc_f32x3_supported(const Problem& p, bool check_pointers) {
 }
 
 int tc_f32x3_launch(const Problem& p, cudaStream_t stream) {
-  // <batch-last, j tile, raw input stages, raw weight stages, operand buffers>
-  if (p.bs_last)
-    return p.b > 64 ? tc::launch_f<true, 128, 2, 2, 2>(p, stream)
-                    : tc::launch_f<true, 64, 3, 4, 2>(p, stream);
-  return p.b > 64 ? tc::launch_f<false, 128, 0, 4, 2>(p, stream)
-                  : tc::launch_f<false, 64, 0, 4, 3>(p, stream);
+  // <batch-last, j tile, raw input stages, raw weight stages, operand buffers>.  The j tile
+  // is the one with the least padded work: a tile costs about 0.4 (input side) + 0.6 * NJ / 128.
+  int nj = 128;
+  double best = 1e30;
+  for (int cand : {128, 96, 64}) {
+    const double cost = ((p.b + cand - 1) / cand) * (0.4 + 0.6 * cand / 128.0);
+    if (cost < best - 1e-9) { best = cost; nj = cand; }
+  }
+  if (p.bs_last) {
+    if (nj == 128) return tc::launch_f<true, 128, 2, 2, 2>(p, stream);
+    if (nj == 96) return tc::launch_f<true, 96, 3, 2, 2>(p, stream);
+    return tc::launch_f<true, 64, 3, 4, 2>(p, stream);
+  }
+  if (nj == 128) return tc::launch_f<false, 128, 0, 4, 2>(p, stream);
+  if (nj == 96) return tc::launch_f<false, 96, 0, 2, 3>(p, stream);
+  return tc::launch_f<false, 64, 0, 4, 3>(p, stream);
 }
 
 }  // namespace ksmm

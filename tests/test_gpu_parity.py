@@ -237,9 +237,9 @@ def test_batch_first_layout_conversion_path(dtype):
 
 
 F32_TC_LAST = [(1, 64, 64, 1), (2, 128, 32, 4), (1, 768, 192, 4), (6, 64, 64, 1), (3, 48, 80, 2),
-               (1, 136, 72, 4), (1, 64, 64, 16), (1, 192, 768, 2), (2, 36, 200, 3)]
+               (1, 136, 72, 4), (1, 64, 64, 16), (1, 192, 768, 2), (2, 36, 200, 3), (2, 96, 40, 2)]
 F32_TC_FIRST = [(1, 64, 64, 1), (4, 192, 192, 1), (3, 48, 80, 1), (2, 72, 48, 1), (6, 64, 64, 1),
-                (1, 200, 100, 1), (1, 768, 192, 1)]
+                (1, 200, 100, 1), (1, 768, 192, 1), (2, 96, 40, 1), (1, 88, 64, 1)]
 
 
 @pytest.mark.parametrize("bs_last", [True, False])
