@@ -8,7 +8,8 @@
 // hi = trunc(v)) and once as lo = v - trunc(v), which is exact in fp32.  The
 // product x * w is accumulated as
 //     hi(x) hi(w) + lo(x) hi(w) + hi(x) lo(w),
-// three MMAs per k step; the dropped lo * lo term and the truncation of lo
+// two MMAs per k step (hi(x) against the stacked rows [hi(w) | lo(w)], N = 2 NJ,
+// and lo(x) against hi(w), N = NJ); the dropped lo * lo term and the truncation of lo
 // itself are of relative size 2^-22.  The tensor core also truncates when it
 // adds into the fp32 accumulator, once per MMA, and that error grows with the
 // number of accumulations: the two small terms therefore go to an accumulator
@@ -55,7 +56,8 @@ struct ParamsF {
   uint32_t rows;        // blocks * tiles_n: (block, batch tile) pairs
   uint32_t row_groups;  // CTAs per j tile
   int nchunks;          // ceil(c / 32)
-  uint32_t idesc;
+  uint32_t idesc;   // N = NJ
+  uint32_t idesc2;  // N = 2 NJ
   float alpha;
   const float* bias;
   int* status;
@@ -270,13 +272,13 @@ __global__ void __launch_bounds__(kThreadsF, 1)
               xhi = make_desc(xb + ks * 32, 16, 1024, 2);
               xlo = make_desc(xb + C::XRAW_BYTES + ks * 32, 16, 1024, 2);
             }
-            const uint64_t whi = make_desc(wb + ks * 2 * (C::NJ * 16), C::NJ * 16, 128, 0);
-            const uint64_t wlo =
-                make_desc(wb + C::WRAW_BYTES + ks * 2 * (C::NJ * 16), C::NJ * 16, 128, 0);
+            // weights: core columns of 4 k, each holding the NJ hi rows and then the NJ lo rows
+            const uint64_t wst = make_desc(wb + ks * 2 * (C::NJ * 32), C::NJ * 32, 128, 0);
             const uint32_t acc = (qc | ks) != 0 ? 1u : 0u;
-            umma_tf32(dsmall, xlo, whi, P.idesc, acc);
-            umma_tf32(dsmall, xhi, wlo, P.idesc, 1u);
-            umma_tf32(dcol, xhi, whi, P.idesc, acc);
+            // hi(x) * [hi(w) | lo(w)]: the leading accumulator and, next to it, the small one
+            umma_tf32(dcol, xhi, wst, P.idesc2, acc);
+            // lo(x) * hi(w): only the first NJ rows of the same operand
+            umma_tf32(dsmall, xlo, wst, P.idesc, 1u);
           }
           KSMM_TRACE(1, 19);
           umma_commit(xop_empty(ai));
@@ -359,7 +361,8 @@ __global__ void __launch_bounds__(kThreadsF, 1)
         if (tron) KSMM_TRACE(3, 43);
         if (tt < C::NJ) {
           const uint32_t rb = wraw0 + wi * C::WRAW_BYTES;
-          const uint32_t hb = wop0 + ai * C::WOP_BYTES, lb = hb + C::WRAW_BYTES;
+          // per core column of 4 k: the NJ hi rows, then the NJ lo rows (one operand of 2 NJ rows)
+          const uint32_t hb = wop0 + ai * C::WOP_BYTES, lb = hb + C::NJ * 16;
           const uint32_t dst = (tt >> 3) * 128 + (tt & 7) * 16;
 #pragma unroll
           for (int kg = 0; kg < 8; ++kg) {
@@ -370,10 +373,10 @@ __global__ void __launch_bounds__(kThreadsF, 1)
                            : "=r"(v[q])
                            : "r"(rb + (kg * 4 + q) * (C::NJ * 4) + tt * 4)
                            : "memory");
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(hb + kg * (C::NJ * 16) + dst),
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(hb + kg * (C::NJ * 32) + dst),
                          "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3])
                          : "memory");
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(lb + kg * (C::NJ * 16) + dst),
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(lb + kg * (C::NJ * 32) + dst),
                          "r"(lo_part(v[0])), "r"(lo_part(v[1])), "r"(lo_part(v[2])), "r"(lo_part(v[3]))
                          : "memory");
           }
@@ -559,6 +562,8 @@ static int launch_f(const Problem& p, cudaStream_t stream) {
   // fp32 accumulate, tf32 operands, both K-major, N = NJ, M = 128
   P.idesc = (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(C::NJ >> 3) << 17) |
             (static_cast<uint32_t>(128 >> 4) << 24);
+  P.idesc2 = (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(2 * C::NJ >> 3) << 17) |
+             (static_cast<uint32_t>(128 >> 4) << 24);
   const int sms = num_sms();
   if (sms <= 0) return set_error(KSMM_ERR_NO_DEVICE, "no CUDA device");
   const int64_t rows = static_cast<int64_t>(P.tiles_n) * p.a * p.d;
