@@ -344,8 +344,17 @@ def run_ours(args, rank, world, local_rank):
                     "bound": "hbm" if t_hbm >= t_fl else cb,
                     "roofline_frac": round(t_roof / (ms * 1e-3), 4)})
 
+    # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) at B = 25088 from the ncu
+    # captures summarised under profiles/: (dtype, batch-last, pattern) -> bytes
+    ncu_traffic = {("fp32", True, (1, 192, 768, 4)): 371.2e6, ("fp32", True, (1, 768, 192, 4)): 330.4e6,
+                   ("fp32", False, (4, 192, 192, 1)): 111.9e6, ("fp32", False, (4, 64, 64, 4)): 155.4e6,
+                   ("fp16", True, (1, 768, 192, 4)): 135.2e6, ("fp16", False, (1, 768, 192, 4)): 136.5e6}
+
     def roofline_of(entry, c):
         ms = entry["ms"]
+        traffic = ncu_traffic.get((c["dtype"], bool(c["bs_last"]), tuple(c["pattern"])))
+        if BATCH != 25088:
+            traffic = None
         if entry["bound"] == "hbm":
             ach, pk, unit = c["bytes"] / (ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s"
             src = f"MEASURED_PEAKS.json ({peaks['source']})"
@@ -364,7 +373,7 @@ def run_ours(args, rank, world, local_rank):
                 src = f"MEASURED_PEAKS.json ({peaks['source']})"
         return {"bound": "tensor" if entry["bound"] == "tensor_tf32x3" else entry["bound"],
                 "achieved": round(ach, 2), "peak": round(pk, 2), "unit": unit,
-                "frac": round(ach / pk, 4), "traffic": None,
+                "frac": round(ach / pk, 4), "traffic": traffic, "algorithmic_bytes": c["bytes"],
                 "kernel": f"{entry['dtype']} {entry['layout']} {tuple(entry['pattern'])} ({entry['kernel']})",
                 "peak_source": src,
                 "share_of_step": round(ms / (elapsed_ms / args.steps), 4)}
