@@ -60,6 +60,7 @@ struct ParamsF {
   uint32_t idesc2;  // N = 2 NJ
   float alpha;
   const float* bias;
+  float* out;  // batch-last: the epilogue stores straight from registers
   int* status;
 };
 
@@ -112,7 +113,10 @@ struct CfgF {
   static constexpr int WOP_BYTES = 2 * WRAW_BYTES;
   static constexpr int NXRAW = BS_LAST ? SRX : 0;
   static constexpr int STG_WARP_BYTES = 32 * 128;   // 32 rows of 32 fp32
-  static constexpr int STG_BYTES = kEpilogueWarps * STG_WARP_BYTES;
+  // batch-last can do without staging: a warp's 32 lanes hold 32 consecutive batch entries of
+  // one output row, so a plain store already writes a whole 128-byte line
+  static constexpr bool DIRECT = BS_LAST && NJ_ > 64;  // (narrow tiles measured faster through TMA stores)
+  static constexpr int STG_BYTES = DIRECT ? 0 : kEpilogueWarps * STG_WARP_BYTES;
   // barriers: xraw full/empty, wraw full/empty, xop full/empty, wop full/empty, tmem full/empty
   static constexpr int NBAR = 2 * (BS_LAST ? SRX : SA) + 2 * SRW + 4 * SA + 4;
   static constexpr int BAR_BYTES = 512;
@@ -449,30 +453,44 @@ __global__ void __launch_bounds__(kThreadsF, 1)
             r[jj] = __float_as_uint(fmaf(P.alpha, __uint_as_float(r[jj]), bv));
           }
         }
-        if (lane == 0) bulk_wait_read<0>();  // the previous store has read the staging tile
-        __syncwarp();
-        if constexpr (BS_LAST) {
-          // staging tile [32 j][32 n]: lane = n, so every store fills one 128-byte row segment
+        if constexpr (C::DIRECT) {
+          // lane = batch entry n, register jj = output row (i*b + j)*d + l: every store instruction
+          // of the warp writes 32 consecutive floats of one row
+          const int64_t n = static_cast<int64_t>(n0) + q * 32 + lane;
+          if (n < P.batch) {
+            const int i = blk / P.d, l = blk % P.d;
+            float* dst = P.out + ((static_cast<int64_t>(i) * P.b + j0 + jj0) * P.d + l) * P.batch + n;
+            const int64_t jstride = static_cast<int64_t>(P.d) * P.batch;
 #pragma unroll
-          for (int jj = 0; jj < 32; ++jj)
-            asm volatile("st.shared.b32 [%0], %1;" ::"r"(stg + jj * 128 + lane * 4), "r"(r[jj]) : "memory");
+            for (int jj = 0; jj < 32; ++jj)
+              if (j0 + jj0 + jj < P.b) dst[jj * jstride] = __uint_as_float(r[jj]);
+          }
         } else {
-          // staging tile [32 n][32 j], 128-byte swizzle: lane = n owns one row
-          const uint32_t rowaddr = stg + lane * 128;
+          if (lane == 0) bulk_wait_read<0>();  // the previous store has read the staging tile
+          __syncwarp();
+          if constexpr (BS_LAST) {
+            // staging tile [32 j][32 n]: lane = n, so every store fills one 128-byte row segment
 #pragma unroll
-          for (int ch = 0; ch < 8; ++ch)
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + ((ch ^ (lane & 7)) << 4)),
-                         "r"(r[ch * 4 + 0]), "r"(r[ch * 4 + 1]), "r"(r[ch * 4 + 2]), "r"(r[ch * 4 + 3])
-                         : "memory");
-        }
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) {
-          if constexpr (BS_LAST)
-            tma_store_4d(&tmY, stg, n0 + q * 32, blk % P.d, j0 + jj0, blk / P.d);
-          else
-            tma_store_3d(&tmY, stg, j0 + jj0, blk, n0 + q * 32);
-          bulk_commit();
+            for (int jj = 0; jj < 32; ++jj)
+              asm volatile("st.shared.b32 [%0], %1;" ::"r"(stg + jj * 128 + lane * 4), "r"(r[jj]) : "memory");
+          } else {
+            // staging tile [32 n][32 j], 128-byte swizzle: lane = n owns one row
+            const uint32_t rowaddr = stg + lane * 128;
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + ((ch ^ (lane & 7)) << 4)),
+                           "r"(r[ch * 4 + 0]), "r"(r[ch * 4 + 1]), "r"(r[ch * 4 + 2]), "r"(r[ch * 4 + 3])
+                           : "memory");
+          }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (BS_LAST)
+              tma_store_4d(&tmY, stg, n0 + q * 32, blk % P.d, j0 + jj0, blk / P.d);
+            else
+              tma_store_3d(&tmY, stg, j0 + jj0, blk, n0 + q * 32);
+            bulk_commit();
+          }
         }
       }
       if (!released) {
@@ -481,7 +499,7 @@ __global__ void __launch_bounds__(kThreadsF, 1)
         if (lane == 0) mbar_arrive(tempty_bar(buf));
       }
     }
-    if (lane == 0) bulk_wait<0>();
+    if (!C::DIRECT && lane == 0) bulk_wait<0>();
     __syncwarp();
   }
 
@@ -536,7 +554,9 @@ static int launch_f(const Problem& p, cudaStream_t stream) {
     const uint32_t box[3] = {static_cast<uint32_t>(C::NJ), kKC, 1};
     if ((st = encode_map(&tmW, KSMM_F32, 3, p.w, dims, str, box, false)) != KSMM_OK) return st;
   }
-  if (BS_LAST) {
+  if (C::DIRECT) {
+    tmY = tmW;  // unused: the epilogue stores from registers
+  } else if (BS_LAST) {
     // output (a*b*d, batch): row (i*b + j)*d + l; store = 32 j x 32 batch entries
     const uint64_t dims[4] = {B, d, b, a};
     const uint64_t str[4] = {1, B, d * B, b * d * B};
@@ -557,6 +577,7 @@ static int launch_f(const Problem& p, cudaStream_t stream) {
   P.nchunks = (p.c + kKC - 1) / kKC;
   P.alpha = p.alpha;
   P.bias = static_cast<const float*>(p.bias);
+  P.out = static_cast<float*>(p.out);
   P.status = status_word();
   if (!P.status) return set_error(KSMM_ERR_CUDA, "cannot resolve the device status word");
   // fp32 accumulate, tf32 operands, both K-major, N = NJ, M = 128
@@ -612,8 +633,8 @@ int tc_f32x3_launch(const Problem& p, cudaStream_t stream) {
     if (cost < best - 1e-9) { best = cost; nj = cand; }
   }
   if (p.bs_last) {
-    if (nj == 128) return tc::launch_f<true, 128, 2, 2, 2>(p, stream);
-    if (nj == 96) return tc::launch_f<true, 96, 3, 2, 2>(p, stream);
+    if (nj == 128) return tc::launch_f<true, 128, 3, 3, 2>(p, stream);
+    if (nj == 96) return tc::launch_f<true, 96, 4, 4, 2>(p, stream);
     return tc::launch_f<true, 64, 3, 4, 2>(p, stream);
   }
   if (nj == 128) return tc::launch_f<false, 128, 0, 4, 2>(p, stream);
