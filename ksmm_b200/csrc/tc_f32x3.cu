@@ -117,8 +117,8 @@ struct CfgF {
   // one output row, so a plain store already writes a whole 128-byte line
   static constexpr bool DIRECT = BS_LAST && NJ_ > 64;  // (narrow tiles measured faster through TMA stores)
   static constexpr int STG_BYTES = DIRECT ? 0 : kEpilogueWarps * STG_WARP_BYTES;
-  // barriers: xraw full/empty, wraw full/empty, xop full/empty, wop full/empty, tmem full/empty
-  static constexpr int NBAR = 2 * (BS_LAST ? SRX : SA) + 2 * SRW + 4 * SA + 4;
+  // barriers: xraw full/empty, wraw full/empty, operand buffers full/empty, tmem full/empty
+  static constexpr int NBAR = 2 * (BS_LAST ? SRX : SA) + 2 * SRW + 2 * SA + 4;
   static constexpr int BAR_BYTES = 512;
   static constexpr int SMEM_BYTES = STG_BYTES + NXRAW * XRAW_BYTES + SRW * WRAW_BYTES +
                                     SA * XOP_BYTES + SA * WOP_BYTES + BAR_BYTES + 1024;
@@ -158,10 +158,12 @@ __global__ void __launch_bounds__(kThreadsF, 1)
   auto wraw_empty = [&](int s) { return bar0 + 8u * (2 * NXR + SRW + s); };
   auto xop_full = [&](int s) { return bar0 + 8u * (2 * NXR + 2 * SRW + s); };
   auto xop_empty = [&](int s) { return bar0 + 8u * (2 * NXR + 2 * SRW + SA + s); };
-  auto wop_full = [&](int s) { return bar0 + 8u * (2 * NXR + 2 * SRW + 2 * SA + s); };
-  auto wop_empty = [&](int s) { return bar0 + 8u * (2 * NXR + 2 * SRW + 3 * SA + s); };
-  auto tfull_bar = [&](int q) { return bar0 + 8u * (2 * NXR + 2 * SRW + 4 * SA + q); };
-  auto tempty_bar = [&](int q) { return bar0 + 8u * (2 * NXR + 2 * SRW + 4 * SA + 2 + q); };
+  // one full / empty pair per operand buffer pair: both splitter groups arrive on op_full and
+  // both wait for the MMA thread's single commit on op_empty
+  auto wop_full = xop_full;
+  auto wop_empty = xop_empty;
+  auto tfull_bar = [&](int q) { return bar0 + 8u * (2 * NXR + 2 * SRW + 2 * SA + q); };
+  auto tempty_bar = [&](int q) { return bar0 + 8u * (2 * NXR + 2 * SRW + 2 * SA + 2 + q); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * C::NBAR);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 8 * C::NBAR + 4);
 
@@ -179,10 +181,8 @@ __global__ void __launch_bounds__(kThreadsF, 1)
       mbar_init(wraw_empty(s), 4);
     }
     for (int s = 0; s < SA; ++s) {
-      mbar_init(xop_full(s), 4);
+      mbar_init(xop_full(s), 8);  // four input-splitter and four weight-splitter warps
       mbar_init(xop_empty(s), 1);
-      mbar_init(wop_full(s), 4);
-      mbar_init(wop_empty(s), 1);
     }
     for (int q = 0; q < 2; ++q) {
       mbar_init(tfull_bar(q), 1);
@@ -258,7 +258,6 @@ __global__ void __launch_bounds__(kThreadsF, 1)
         const uint32_t dcol = tmem_base + buf * C::BUF_COLS, dsmall = dcol + C::NJ;
         for (int qc = 0; qc < nchunks; ++qc) {
           KSMM_TRACE(1, 14);
-          if (!mbar_wait<0>(wop_full(ai), aph, abort_flag, P.status, 34)) { ok = false; break; }
           KSMM_TRACE(1, 12);
           if (!mbar_wait<0>(xop_full(ai), aph, abort_flag, P.status, 35)) { ok = false; break; }
           KSMM_TRACE(1, 13);
@@ -286,7 +285,6 @@ __global__ void __launch_bounds__(kThreadsF, 1)
           }
           KSMM_TRACE(1, 19);
           umma_commit(xop_empty(ai));
-          umma_commit(wop_empty(ai));
           if (++ai == SA) { ai = 0; aph ^= 1u; }
         }
         if (!ok) break;
