@@ -79,23 +79,28 @@ __device__ __forceinline__ uint32_t lo_part(uint32_t v) {
   return __float_as_uint(__uint_as_float(v) - __uint_as_float(v & 0xFFFFE000u));
 }
 
-// Transposes a raw tile [32 k][128 x] (512-byte rows) into the hi and lo operand
-// tiles [k / 4][x / 8][x % 8][4 k] (K-major core matrices, 2048 bytes per core
-// column).  Thread `t` of the group owns x = t.
+// Transposes a raw tile [32 k][x] into the hi and lo operand tiles
+// [k / 4][x / 8][x % 8][4 k] (K-major core matrices).  Thread `t` of the group owns x = t.
+// ROW_BYTES: bytes per raw row (128 x 4 for the input, NJ x 4 for the weights); COL_BYTES: bytes
+// per core column of the operand tiles.  All 32 loads are issued before the first store, so
+// that the shared-memory latency is paid once per chunk.
+template <int ROW_BYTES, int COL_BYTES>
 __device__ __forceinline__ void split_transposed(uint32_t rawbase, uint32_t hibase, uint32_t lobase,
                                                  int t) {
   const uint32_t dst = (t >> 3) * 128 + (t & 7) * 16;
+  uint32_t v[8][4];
 #pragma unroll
-  for (int kg = 0; kg < 8; ++kg) {
-    uint32_t v[4];
+  for (int kg = 0; kg < 8; ++kg)
 #pragma unroll
     for (int q = 0; q < 4; ++q)
-      asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v[q]) : "r"(rawbase + (kg * 4 + q) * 512 + t * 4) : "memory");
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(hibase + kg * 2048 + dst),
-                 "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3])
+      asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v[kg][q]) : "r"(rawbase + (kg * 4 + q) * ROW_BYTES + t * 4));
+#pragma unroll
+  for (int kg = 0; kg < 8; ++kg) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(hibase + kg * COL_BYTES + dst),
+                 "r"(v[kg][0]), "r"(v[kg][1]), "r"(v[kg][2]), "r"(v[kg][3])
                  : "memory");
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(lobase + kg * 2048 + dst),
-                 "r"(lo_part(v[0])), "r"(lo_part(v[1])), "r"(lo_part(v[2])), "r"(lo_part(v[3]))
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(lobase + kg * COL_BYTES + dst),
+                 "r"(lo_part(v[kg][0])), "r"(lo_part(v[kg][1])), "r"(lo_part(v[kg][2])), "r"(lo_part(v[kg][3]))
                  : "memory");
   }
 }
@@ -313,7 +318,7 @@ __global__ void __launch_bounds__(kThreadsF, 1)
         if (tron) KSMM_TRACE(2, 33);
         const uint32_t ob = xop0 + ai * C::XOP_BYTES;
         if constexpr (BS_LAST) {
-          split_transposed(xraw0 + xi * C::XRAW_BYTES, ob, ob + C::XRAW_BYTES, tt);
+          split_transposed<512, 2048>(xraw0 + xi * C::XRAW_BYTES, ob, ob + C::XRAW_BYTES, tt);
         } else {
           // lo tile at the same (swizzled) offsets as the raw tile
 #pragma unroll
@@ -365,23 +370,7 @@ __global__ void __launch_bounds__(kThreadsF, 1)
           const uint32_t rb = wraw0 + wi * C::WRAW_BYTES;
           // per core column of 4 k: the NJ hi rows, then the NJ lo rows (one operand of 2 NJ rows)
           const uint32_t hb = wop0 + ai * C::WOP_BYTES, lb = hb + C::NJ * 16;
-          const uint32_t dst = (tt >> 3) * 128 + (tt & 7) * 16;
-#pragma unroll
-          for (int kg = 0; kg < 8; ++kg) {
-            uint32_t v[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              asm volatile("ld.shared.b32 %0, [%1];"
-                           : "=r"(v[q])
-                           : "r"(rb + (kg * 4 + q) * (C::NJ * 4) + tt * 4)
-                           : "memory");
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(hb + kg * (C::NJ * 32) + dst),
-                         "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3])
-                         : "memory");
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(lb + kg * (C::NJ * 32) + dst),
-                         "r"(lo_part(v[0])), "r"(lo_part(v[1])), "r"(lo_part(v[2])), "r"(lo_part(v[3]))
-                         : "memory");
-          }
+          split_transposed<C::NJ * 4, C::NJ * 32>(rb, hb, lb, tt);
         }
         fence_proxy_async();
         __syncwarp();
