@@ -156,9 +156,19 @@ def cpu_reference_pass(sample_cols, seed=0):
     return total_fl, total_s
 
 
+def use_all_host_threads():
+    """torchrun exports OMP_NUM_THREADS=1; the CPU legs use every core the process may run on."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
+    use_all_host_threads()
     cols = 3136
     for _ in range(args.warmup):
         cpu_reference_pass(cols)
@@ -488,6 +498,7 @@ def run_ours(args, rank, world, local_rank):
     # ---- CPU baseline: bounded sample on the host cores (rank 0, N = 1 only) -----------------
     cpu = None
     if world == 1 and not args.no_cpu:
+        use_all_host_threads()
         cols = 3136
         cpu_reference_pass(cols)
         fl, secs, passes = 0.0, 0.0, 0
