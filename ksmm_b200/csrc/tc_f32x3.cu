@@ -21,22 +21,30 @@
 // dispatch uses this kernel up to c = 1024.  The exact FFMA kernels stay
 // available as KSMM_ALGO_SIMT.
 //
-// Operands are K-major in shared memory: the tensor core wants, for every row
-// (a batch entry of the input, a column j of the weights), the values of k next
-// to each other, but both the batch-last input X[(i, k, l), n] and the weights
-// W[(i, l, k), j] have k as their row index.  Two groups of four "splitter"
-// warps therefore sit between TMA and the MMA thread: they read a raw tile of
-// 32 k x 128 entries, transpose it and write the hi and lo operand tiles (core
-// matrices of 8 rows x 16 bytes, no swizzle).  In the batch-first layout the
-// input rows already hold consecutive k: the raw tile (128-byte swizzle) is the
-// hi operand as it stands and its splitters only add the lo tile.
+// Operand tiles come from TMA in the layout the tensor core reads, so the raw
+// tile is the hi operand as it stands.  The batch-last input X[(i, k, l), n] and
+// the weights W[(i, l, k), j] have k as their row index: they are MN-major
+// operands, which for 32-bit elements use the 128-byte swizzle with 32-byte
+// atoms (tile of 32 x-values by 32 k rows of 128 bytes; the 32-byte piece p of row k
+// sits at p ^ (k % 4); CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B on the TMA side,
+// descriptor layout type 1 on the MMA side).  The batch-first input rows hold
+// consecutive k: K-major, plain 128-byte swizzle.  Two groups of four
+// "splitter" warps only add the lo tiles, element by element at the same
+// offsets (16-byte loads and stores).  One shared-memory stage holds
+// [X hi | X lo | W hi | W lo]; the lo weights follow the hi weights directly, so the
+// two together are one operand of 2 NJ rows.
 //
 // Warp roles (576 threads): warp 0 TMA producer, warp 1 TMEM owner and MMA
 // issuer, warps 2..5 input splitters, warps 6..9 weight splitters, warps
 // 10..17 epilogue (TMEM lane quarter = warp index mod 4).  Accumulator rows
 // are batch entries, columns are j.  A CTA keeps one j tile and walks a
-// contiguous range of (block, batch tile) pairs.  Waits are bounded and report
-// through the status word as in tc_kernel.cu.
+// contiguous range of (block, batch tile) pairs.  Per chunk of 32 k there are three
+// hand-offs: TMA -> splitters (one barrier for both tiles), splitters -> MMA
+// thread (eight warp arrivals), MMA commit -> producer.  Waits are bounded and
+// report through the status word as in tc_kernel.cu.
+//
+// Shapes: b a multiple of 32 and, batch-last, a batch that is a multiple of 32 (the tiles are
+// addressed in atoms of 32 columns); batch-first needs d = 1 and c a multiple of 4.
 //
 // Reference counterparts: kernel_bs_last_float / kernel_bs_first_float
 // (src/ksmm_py/layer/kronecker_sparse/template_kernels_float.cuh:301-491, 51-299).
@@ -79,54 +87,24 @@ __device__ __forceinline__ uint32_t lo_part(uint32_t v) {
   return __float_as_uint(__uint_as_float(v) - __uint_as_float(v & 0xFFFFE000u));
 }
 
-// Transposes a raw tile [32 k][x] into the hi and lo operand tiles
-// [k / 4][x / 8][x % 8][4 k] (K-major core matrices).  Thread `t` of the group owns x = t.
-// ROW_BYTES: bytes per raw row (128 x 4 for the input, NJ x 4 for the weights); COL_BYTES: bytes
-// per core column of the operand tiles.  All 32 loads are issued before the first store, so
-// that the shared-memory latency is paid once per chunk.
-template <int ROW_BYTES, int COL_BYTES>
-__device__ __forceinline__ void split_transposed(uint32_t rawbase, uint32_t hibase, uint32_t lobase,
-                                                 int t) {
-  const uint32_t dst = (t >> 3) * 128 + (t & 7) * 16;
-  uint32_t v[8][4];
-#pragma unroll
-  for (int kg = 0; kg < 8; ++kg)
-#pragma unroll
-    for (int q = 0; q < 4; ++q)
-      asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v[kg][q]) : "r"(rawbase + (kg * 4 + q) * ROW_BYTES + t * 4));
-#pragma unroll
-  for (int kg = 0; kg < 8; ++kg) {
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(hibase + kg * COL_BYTES + dst),
-                 "r"(v[kg][0]), "r"(v[kg][1]), "r"(v[kg][2]), "r"(v[kg][3])
-                 : "memory");
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(lobase + kg * COL_BYTES + dst),
-                 "r"(lo_part(v[kg][0])), "r"(lo_part(v[kg][1])), "r"(lo_part(v[kg][2])), "r"(lo_part(v[kg][3]))
-                 : "memory");
-  }
-}
-
-// SRX / SRW: raw input / weight stages; SA: operand tile buffers (hi | lo) of
-// each kind.  In the batch-first flavour the raw input stage is the hi operand,
-// so the input ring holds SA stages of raw | lo and SRX is unused.
-template <bool BS_LAST, int NJ_, int SRX, int SRW, int SA_>
+// ST stages of [X hi | X lo | W hi | W lo].
+template <bool BS_LAST, int NJ_, int ST_>
 struct CfgF {
   static constexpr int NJ = NJ_;                    // j columns per accumulator (64, 96 or 128)
-  static constexpr int SA = SA_;
-  static constexpr int XRAW_BYTES = kKC * 128 * 4;  // 32 k x 128 batch entries (either order)
-  static constexpr int WRAW_BYTES = kKC * NJ * 4;   // 32 k x NJ columns
-  static constexpr int XOP_BYTES = 2 * XRAW_BYTES;  // hi | lo
-  static constexpr int WOP_BYTES = 2 * WRAW_BYTES;
-  static constexpr int NXRAW = BS_LAST ? SRX : 0;
+  static constexpr int ST = ST_;
+  static constexpr int XT_BYTES = kKC * 128 * 4;    // 32 k x 128 batch entries (either order)
+  static constexpr int WT_BYTES = kKC * NJ * 4;     // 32 k x NJ columns
+  static constexpr int W_OFF = 2 * XT_BYTES;
+  static constexpr int STAGE_BYTES = 2 * XT_BYTES + 2 * WT_BYTES;
   static constexpr int STG_WARP_BYTES = 32 * 128;   // 32 rows of 32 fp32
   // batch-last can do without staging: a warp's 32 lanes hold 32 consecutive batch entries of
   // one output row, so a plain store already writes a whole 128-byte line
   static constexpr bool DIRECT = BS_LAST && NJ_ > 64;  // (narrow tiles measured faster through TMA stores)
   static constexpr int STG_BYTES = DIRECT ? 0 : kEpilogueWarps * STG_WARP_BYTES;
-  // barriers: xraw full/empty, wraw full/empty, operand buffers full/empty, tmem full/empty
-  static constexpr int NBAR = 2 * (BS_LAST ? SRX : SA) + 2 * SRW + 2 * SA + 4;
+  // barriers per stage: tiles landed, lo tiles written, stage free; tmem full/empty
+  static constexpr int NBAR = 3 * ST + 4;
   static constexpr int BAR_BYTES = 512;
-  static constexpr int SMEM_BYTES = STG_BYTES + NXRAW * XRAW_BYTES + SRW * WRAW_BYTES +
-                                    SA * XOP_BYTES + SA * WOP_BYTES + BAR_BYTES + 1024;
+  static constexpr int SMEM_BYTES = STG_BYTES + ST * STAGE_BYTES + BAR_BYTES + 1024;
   static constexpr int NBUF = 2;
   static constexpr int BUF_COLS = 2 * NJ;  // leading accumulator | small-terms accumulator
   // allocations are powers of two
@@ -137,57 +115,36 @@ struct CfgF {
   static_assert(8 * NBAR + 16 <= BAR_BYTES, "barrier area");
 };
 
-template <bool BS_LAST, int NJ_, int SRX, int SRW, int SA_>
+template <bool BS_LAST, int NJ_, int ST_>
 __global__ void __launch_bounds__(kThreadsF, 1)
     ksmm_tc_f32x3_kernel(const __grid_constant__ CUtensorMap tmX,
                          const __grid_constant__ CUtensorMap tmW,
                          const __grid_constant__ CUtensorMap tmY, const ParamsF P) {
-  using C = CfgF<BS_LAST, NJ_, SRX, SRW, SA_>;
-  constexpr int SA = C::SA;
-  constexpr int NXR = BS_LAST ? SRX : SA;  // stages the producer fills with input
+  using C = CfgF<BS_LAST, NJ_, ST_>;
+  constexpr int ST = C::ST;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t sm0 = (raw + 1023u) & ~1023u;
   uint8_t* sm_gen = smem_raw + (sm0 - raw);
-  const uint32_t stg0 = sm0;                               // epilogue staging tiles
-  const uint32_t xop0 = stg0 + C::STG_BYTES;               // input operands: hi | lo per buffer
-  const uint32_t wop0 = xop0 + SA * C::XOP_BYTES;          // weight operands: hi | lo per buffer
-  const uint32_t wraw0 = wop0 + SA * C::WOP_BYTES;         // raw weight tiles
-  const uint32_t xraw0 = wraw0 + SRW * C::WRAW_BYTES;      // raw input tiles (batch-last only)
-  const uint32_t bar0 = xraw0 + C::NXRAW * C::XRAW_BYTES;
+  const uint32_t stg0 = sm0;                     // epilogue staging tiles
+  const uint32_t stage0 = stg0 + C::STG_BYTES;   // operand stages
+  const uint32_t bar0 = stage0 + ST * C::STAGE_BYTES;
   uint8_t* bar_gen = sm_gen + (bar0 - sm0);
-  // input stage s: batch-last = raw tile s; batch-first = hi half of operand buffer s
-  auto xin_full = [&](int s) { return bar0 + 8u * s; };
-  auto xin_empty = [&](int s) { return bar0 + 8u * (NXR + s); };
-  auto wraw_full = [&](int s) { return bar0 + 8u * (2 * NXR + s); };
-  auto wraw_empty = [&](int s) { return bar0 + 8u * (2 * NXR + SRW + s); };
-  auto xop_full = [&](int s) { return bar0 + 8u * (2 * NXR + 2 * SRW + s); };
-  auto xop_empty = [&](int s) { return bar0 + 8u * (2 * NXR + 2 * SRW + SA + s); };
-  // one full / empty pair per operand buffer pair: both splitter groups arrive on op_full and
-  // both wait for the MMA thread's single commit on op_empty
-  auto wop_full = xop_full;
-  auto wop_empty = xop_empty;
-  auto tfull_bar = [&](int q) { return bar0 + 8u * (2 * NXR + 2 * SRW + 2 * SA + q); };
-  auto tempty_bar = [&](int q) { return bar0 + 8u * (2 * NXR + 2 * SRW + 2 * SA + 2 + q); };
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };             // TMA: X hi and W hi landed
+  auto split_bar = [&](int s) { return bar0 + 8u * (ST + s); };     // splitters: lo tiles written
+  auto free_bar = [&](int s) { return bar0 + 8u * (2 * ST + s); };  // MMA commit: stage consumed
+  auto tfull_bar = [&](int q) { return bar0 + 8u * (3 * ST + q); };
+  auto tempty_bar = [&](int q) { return bar0 + 8u * (3 * ST + 2 + q); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * C::NBAR);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 8 * C::NBAR + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < NXR; ++s) {
-      mbar_init(xin_full(s), 1);
-      // batch-last: the four splitter warps hand the raw tile back;
-      // batch-first: the MMA commit frees the whole operand buffer (xop_empty), unused here
-      mbar_init(xin_empty(s), 4);
-    }
-    for (int s = 0; s < SRW; ++s) {
-      mbar_init(wraw_full(s), 1);
-      mbar_init(wraw_empty(s), 4);
-    }
-    for (int s = 0; s < SA; ++s) {
-      mbar_init(xop_full(s), 8);  // four input-splitter and four weight-splitter warps
-      mbar_init(xop_empty(s), 1);
+    for (int s = 0; s < ST; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(split_bar(s), 8);  // four input-splitter and four weight-splitter warps
+      mbar_init(free_bar(s), 1);
     }
     for (int q = 0; q < 2; ++q) {
       mbar_init(tfull_bar(q), 1);
@@ -215,35 +172,28 @@ __global__ void __launch_bounds__(kThreadsF, 1)
   if (warp == 0) {
     // ===================== TMA producer =====================
     if (lane == 0) {
-      uint32_t xi = 0, xph = 0, wi = 0, wph = 0;
+      uint32_t si = 0, sph = 0;
       bool ok = true;
       KSMM_TRACE_DECL;
       for (uint32_t row = row_begin; row < row_end && ok; ++row) {
         const int blk = static_cast<int>(row / P.tiles_n);  // batch-last: (i, l); batch-first: i
         const int n0 = static_cast<int>(row % P.tiles_n) * 128;
         for (int qc = 0; qc < nchunks; ++qc) {
-          // weights first: their splitters have the longer job
           KSMM_TRACE(0, 1);
-          if (!mbar_wait<64>(wraw_empty(wi), wph ^ 1u, abort_flag, P.status, 31)) { ok = false; break; }
+          if (!mbar_wait<64>(free_bar(si), sph ^ 1u, abort_flag, P.status, 31)) { ok = false; break; }
           KSMM_TRACE(0, 2);
-          mbar_expect_tx(wraw_full(wi), C::WRAW_BYTES);
-          // weights (a*d*c, b) seen as (b, c, block in (i, l) order); batch-first has d = 1
-          tma_load_3d(wraw0 + wi * C::WRAW_BYTES, &tmW, wraw_full(wi), j0, qc * kKC, blk);
-          if (++wi == SRW) { wi = 0; wph ^= 1u; }
+          const uint32_t sb = stage0 + si * C::STAGE_BYTES;
+          mbar_expect_tx(full_bar(si), C::XT_BYTES + C::WT_BYTES);
           if constexpr (BS_LAST) {
-            if (!mbar_wait<64>(xin_empty(xi), xph ^ 1u, abort_flag, P.status, 32)) { ok = false; break; }
-            mbar_expect_tx(xin_full(xi), C::XRAW_BYTES);
-            tma_load_4d(xraw0 + xi * C::XRAW_BYTES, &tmX, xin_full(xi), n0, blk % P.d, qc * kKC,
-                        blk / P.d);
+            // (n % 32, k, n / 32, l, i): four atoms of 32 batch entries x 32 k rows
+            tma_load_5d(sb, &tmX, full_bar(si), 0, qc * kKC, n0 / 32, blk % P.d, blk / P.d);
           } else {
-            // the raw tile is the hi operand: it goes straight into the operand buffer,
-            // which the MMA commit frees
-            if (!mbar_wait<64>(xop_empty(xi), xph ^ 1u, abort_flag, P.status, 32)) { ok = false; break; }
-            mbar_expect_tx(xin_full(xi), C::XRAW_BYTES);
-            tma_load_3d(xop0 + xi * C::XOP_BYTES, &tmX, xin_full(xi), qc * kKC, blk, n0);
+            tma_load_3d(sb, &tmX, full_bar(si), qc * kKC, blk, n0);
           }
+          // (j % 32, k, j / 32, block): NJ / 32 atoms of 32 columns x 32 k rows
+          tma_load_4d(sb + C::W_OFF, &tmW, full_bar(si), 0, qc * kKC, j0 / 32, blk);
           KSMM_TRACE(0, 3);
-          if (++xi == NXR) { xi = 0; xph ^= 1u; }
+          if (++si == ST) { si = 0; sph ^= 1u; }
         }
       }
     }
@@ -251,7 +201,7 @@ __global__ void __launch_bounds__(kThreadsF, 1)
   } else if (warp == 1) {
     // ===================== MMA issuer =====================
     if (lane == 0) {
-      uint32_t ai = 0, aph = 0, ut = 0;
+      uint32_t si = 0, sph = 0, ut = 0;
       bool ok = true;
       KSMM_TRACE_DECL;
       for (uint32_t row = row_begin; row < row_end && ok; ++row, ++ut) {
@@ -262,26 +212,26 @@ __global__ void __launch_bounds__(kThreadsF, 1)
         tc_fence_after();
         const uint32_t dcol = tmem_base + buf * C::BUF_COLS, dsmall = dcol + C::NJ;
         for (int qc = 0; qc < nchunks; ++qc) {
-          KSMM_TRACE(1, 14);
           KSMM_TRACE(1, 12);
-          if (!mbar_wait<0>(xop_full(ai), aph, abort_flag, P.status, 35)) { ok = false; break; }
+          if (!mbar_wait<0>(split_bar(si), sph, abort_flag, P.status, 35)) { ok = false; break; }
           KSMM_TRACE(1, 13);
           tc_fence_after();
-          const uint32_t xb = xop0 + ai * C::XOP_BYTES, wb = wop0 + ai * C::WOP_BYTES;
+          const uint32_t xb = stage0 + si * C::STAGE_BYTES, wb = xb + C::W_OFF;
 #pragma unroll
           for (int ks = 0; ks < kKC / 8; ++ks) {
             uint64_t xhi, xlo;
             if constexpr (BS_LAST) {
-              // transposed tiles: core columns of 4 k, 2048 bytes apart; 8-row groups 128 bytes apart
-              xhi = make_desc(xb + ks * 2 * 2048, 2048, 128, 0);
-              xlo = make_desc(xb + C::XRAW_BYTES + ks * 2 * 2048, 2048, 128, 0);
+              // MN-major, 32-byte atoms: 4 KB between the atoms of 32 batch entries, 512 bytes
+              // between groups of 4 k rows; a k step of 8 is two groups
+              xhi = make_desc(xb + ks * 1024, 4096, 512, 1);
+              xlo = make_desc(xb + C::XT_BYTES + ks * 1024, 4096, 512, 1);
             } else {
-              // raw rows of 32 k with the 128-byte swizzle; a k step is 32 bytes inside the row
+              // K-major rows of 32 k with the 128-byte swizzle; a k step is 32 bytes inside the row
               xhi = make_desc(xb + ks * 32, 16, 1024, 2);
-              xlo = make_desc(xb + C::XRAW_BYTES + ks * 32, 16, 1024, 2);
+              xlo = make_desc(xb + C::XT_BYTES + ks * 32, 16, 1024, 2);
             }
-            // weights: core columns of 4 k, each holding the NJ hi rows and then the NJ lo rows
-            const uint64_t wst = make_desc(wb + ks * 2 * (C::NJ * 32), C::NJ * 32, 128, 0);
+            // weights: MN-major, the NJ / 32 hi atoms and then the NJ / 32 lo atoms
+            const uint64_t wst = make_desc(wb + ks * 1024, 4096, 512, 1);
             const uint32_t acc = (qc | ks) != 0 ? 1u : 0u;
             // hi(x) * [hi(w) | lo(w)]: the leading accumulator and, next to it, the small one
             umma_tf32(dcol, xhi, wst, P.idesc2, acc);
@@ -289,98 +239,53 @@ __global__ void __launch_bounds__(kThreadsF, 1)
             umma_tf32(dsmall, xlo, wst, P.idesc, 1u);
           }
           KSMM_TRACE(1, 19);
-          umma_commit(xop_empty(ai));
-          if (++ai == SA) { ai = 0; aph ^= 1u; }
+          umma_commit(free_bar(si));
+          if (++si == ST) { si = 0; sph ^= 1u; }
         }
         if (!ok) break;
         umma_commit(tfull_bar(buf));
       }
     }
     __syncwarp();
-  } else if (warp < 6) {
-    // ===================== input splitters =====================
-    const int tt = (warp - 2) * 32 + lane;
-    uint32_t xi = 0, xph = 0, ai = 0, aph = 0;
+  } else if (warp < 10) {
+    // ===================== splitters =====================
+    // warps 2..5: lo tile of the input, warps 6..9: lo tile of the weights; same offsets as the
+    // hi tile, so the swizzle does not matter here
+    const bool on_w = warp >= 6;
+    const int tt = ((warp - 2) & 3) * 32 + lane;
+    const uint32_t off0 = on_w ? C::W_OFF : 0u;
+    const uint32_t tile_bytes = on_w ? C::WT_BYTES : C::XT_BYTES;
+    uint32_t si = 0, sph = 0;
     bool ok = true;
     KSMM_TRACE_DECL;
-    const bool tron = warp == 2 && lane == 0;
+    const bool tron = (warp == 2 || warp == 6) && lane == 0;
+    const int trole = on_w ? 3 : 2;
     for (uint32_t row = row_begin; row < row_end && ok; ++row) {
       for (int qc = 0; qc < nchunks; ++qc) {
         int got = 1;
-        if (tron) KSMM_TRACE(2, 30);
-        if (lane == 0) {
-          got = mbar_wait<32>(xin_full(xi), xph, abort_flag, P.status, 36) ? 1 : 0;
-          if (tron) KSMM_TRACE(2, 31);
-          if (BS_LAST && got) got = mbar_wait<32>(xop_empty(ai), aph ^ 1u, abort_flag, P.status, 37) ? 1 : 0;
-        }
+        if (tron) KSMM_TRACE(trole, 30);
+        if (lane == 0) got = mbar_wait<32>(full_bar(si), sph, abort_flag, P.status, 36) ? 1 : 0;
         got = __shfl_sync(0xffffffffu, got, 0);
         if (!got) { ok = false; break; }
-        if (tron) KSMM_TRACE(2, 33);
-        const uint32_t ob = xop0 + ai * C::XOP_BYTES;
-        if constexpr (BS_LAST) {
-          split_transposed<512, 2048>(xraw0 + xi * C::XRAW_BYTES, ob, ob + C::XRAW_BYTES, tt);
-        } else {
-          // lo tile at the same (swizzled) offsets as the raw tile
-#pragma unroll
-          for (int it = 0; it < 8; ++it) {
-            const uint32_t off = (tt + it * 128) * 16;
-            uint32_t v[4];
-            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
-                         : "r"(ob + off)
-                         : "memory");
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(ob + C::XRAW_BYTES + off),
-                         "r"(lo_part(v[0])), "r"(lo_part(v[1])), "r"(lo_part(v[2])), "r"(lo_part(v[3]))
-                         : "memory");
-          }
+        if (tron) KSMM_TRACE(trole, 33);
+        const uint32_t hb = stage0 + si * C::STAGE_BYTES + off0, lb = hb + tile_bytes;
+        const int npieces = static_cast<int>(tile_bytes / 16);
+#pragma unroll 4
+        for (int pc = tt; pc < npieces; pc += 128) {
+          uint32_t v[4];
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+                       : "r"(hb + pc * 16)
+                       : "memory");
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(lb + pc * 16),
+                       "r"(lo_part(v[0])), "r"(lo_part(v[1])), "r"(lo_part(v[2])), "r"(lo_part(v[3]))
+                       : "memory");
         }
         fence_proxy_async();  // the tiles are read by the tensor core through the async proxy
         __syncwarp();
-        if (lane == 0) {
-          if (BS_LAST) mbar_arrive(xin_empty(xi));
-          mbar_arrive(xop_full(ai));
-        }
-        if (tron) KSMM_TRACE(2, 34);
-        if (++xi == NXR) { xi = 0; xph ^= 1u; }
-        if (++ai == SA) { ai = 0; aph ^= 1u; }
-      }
-    }
-    __syncwarp();
-  } else if (warp < 10) {
-    // ===================== weight splitters =====================
-    // raw tile [32 k][NJ j] -> hi / lo tiles [k / 4][j / 8][j % 8][4 k]; thread t owns j = t
-    const int tt = (warp - 6) * 32 + lane;
-    uint32_t wi = 0, wph = 0, ai = 0, aph = 0;
-    bool ok = true;
-    KSMM_TRACE_DECL;
-    const bool tron = warp == 6 && lane == 0;
-    for (uint32_t row = row_begin; row < row_end && ok; ++row) {
-      for (int qc = 0; qc < nchunks; ++qc) {
-        int got = 1;
-        if (tron) KSMM_TRACE(3, 40);
-        if (lane == 0) {
-          got = mbar_wait<32>(wraw_full(wi), wph, abort_flag, P.status, 38) ? 1 : 0;
-          if (tron) KSMM_TRACE(3, 41);
-          if (got) got = mbar_wait<32>(wop_empty(ai), aph ^ 1u, abort_flag, P.status, 39) ? 1 : 0;
-        }
-        got = __shfl_sync(0xffffffffu, got, 0);
-        if (!got) { ok = false; break; }
-        if (tron) KSMM_TRACE(3, 43);
-        if (tt < C::NJ) {
-          const uint32_t rb = wraw0 + wi * C::WRAW_BYTES;
-          // per core column of 4 k: the NJ hi rows, then the NJ lo rows (one operand of 2 NJ rows)
-          const uint32_t hb = wop0 + ai * C::WOP_BYTES, lb = hb + C::NJ * 16;
-          split_transposed<C::NJ * 4, C::NJ * 32>(rb, hb, lb, tt);
-        }
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(wraw_empty(wi));
-          mbar_arrive(wop_full(ai));
-        }
-        if (tron) KSMM_TRACE(3, 44);
-        if (++wi == SRW) { wi = 0; wph ^= 1u; }
-        if (++ai == SA) { ai = 0; aph ^= 1u; }
+        if (lane == 0) mbar_arrive(split_bar(si));
+        if (tron) KSMM_TRACE(trole, 34);
+        if (++si == ST) { si = 0; sph ^= 1u; }
       }
     }
     __syncwarp();
@@ -503,10 +408,10 @@ __global__ void __launch_bounds__(kThreadsF, 1)
   }
 }
 
-template <bool BS_LAST, int NJ_, int SRX, int SRW, int SA_>
+template <bool BS_LAST, int NJ_, int ST_>
 static int launch_f(const Problem& p, cudaStream_t stream) {
-  using C = CfgF<BS_LAST, NJ_, SRX, SRW, SA_>;
-  auto kern = ksmm_tc_f32x3_kernel<BS_LAST, NJ_, SRX, SRW, SA_>;
+  using C = CfgF<BS_LAST, NJ_, ST_>;
+  auto kern = ksmm_tc_f32x3_kernel<BS_LAST, NJ_, ST_>;
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -522,24 +427,25 @@ static int launch_f(const Problem& p, cudaStream_t stream) {
   CUtensorMap tmX, tmW, tmY;
   int st;
   if (BS_LAST) {
-    // input (a*c*d, batch): row (i*c + k)*d + l; raw tile = 32 k x 128 batch entries, plain rows
-    const uint64_t dims[4] = {B, d, c, a};
-    const uint64_t str[4] = {1, B, d * B, c * d * B};
-    const uint32_t box[4] = {128, 1, kKC, 1};
-    if ((st = encode_map(&tmX, KSMM_F32, 4, p.in, dims, str, box, false)) != KSMM_OK) return st;
+    // input (a*c*d, batch), row (i*c + k)*d + l, seen as (n % 32, k, n / 32, l, i): one box is the
+    // four atoms (32 batch entries x 32 k rows) of an MN-major operand tile
+    const uint64_t dims[5] = {32, c, B / 32, d, a};
+    const uint64_t str[5] = {1, d * B, 32, B, c * d * B};
+    const uint32_t box[5] = {32, kKC, 4, 1, 1};
+    if ((st = encode_map(&tmX, KSMM_F32, 5, p.in, dims, str, box, true, true)) != KSMM_OK) return st;
   } else {
-    // input (batch, a*c): tile = 128 rows x 32 k of block i, 128-byte swizzle (it is the hi operand)
+    // input (batch, a*c): tile = 128 rows x 32 k of block i, 128-byte swizzle (K-major operand)
     const uint64_t dims[3] = {c, a, B};
     const uint64_t str[3] = {1, c, a * c};
     const uint32_t box[3] = {kKC, 1, 128};
     if ((st = encode_map(&tmX, KSMM_F32, 3, p.in, dims, str, box, true)) != KSMM_OK) return st;
   }
   {
-    // weights (a*d*c, b) row-major seen as (b, c, a*d); raw tile = 32 k x NJ columns, plain rows
-    const uint64_t dims[3] = {b, c, a * d};
-    const uint64_t str[3] = {1, b, c * b};
-    const uint32_t box[3] = {static_cast<uint32_t>(C::NJ), kKC, 1};
-    if ((st = encode_map(&tmW, KSMM_F32, 3, p.w, dims, str, box, false)) != KSMM_OK) return st;
+    // weights (a*d*c, b) row-major seen as (j % 32, k, j / 32, block): NJ / 32 atoms per box
+    const uint64_t dims[4] = {32, c, b / 32, a * d};
+    const uint64_t str[4] = {1, b, 32, c * b};
+    const uint32_t box[4] = {32, kKC, static_cast<uint32_t>(C::NJ / 32), 1};
+    if ((st = encode_map(&tmW, KSMM_F32, 4, p.w, dims, str, box, true, true)) != KSMM_OK) return st;
   }
   if (C::DIRECT) {
     tmY = tmW;  // unused: the epilogue stores from registers
@@ -567,11 +473,11 @@ static int launch_f(const Problem& p, cudaStream_t stream) {
   P.out = static_cast<float*>(p.out);
   P.status = status_word();
   if (!P.status) return set_error(KSMM_ERR_CUDA, "cannot resolve the device status word");
-  // fp32 accumulate, tf32 operands, both K-major, N = NJ, M = 128
-  P.idesc = (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(C::NJ >> 3) << 17) |
-            (static_cast<uint32_t>(128 >> 4) << 24);
-  P.idesc2 = (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(2 * C::NJ >> 3) << 17) |
-             (static_cast<uint32_t>(128 >> 4) << 24);
+  // fp32 accumulate, tf32 operands, weights MN-major, batch-last input MN-major, M = 128
+  const uint32_t common = (1u << 4) | (2u << 7) | (2u << 10) | (BS_LAST ? (1u << 15) : 0u) | (1u << 16) |
+                          (static_cast<uint32_t>(128 >> 4) << 24);
+  P.idesc = common | (static_cast<uint32_t>(C::NJ >> 3) << 17);
+  P.idesc2 = common | (static_cast<uint32_t>(2 * C::NJ >> 3) << 17);
   const int sms = num_sms();
   if (sms <= 0) return set_error(KSMM_ERR_NO_DEVICE, "no CUDA device");
   const int64_t rows = static_cast<int64_t>(P.tiles_n) * p.a * p.d;
@@ -595,10 +501,10 @@ static int launch_f(const Problem& p, cudaStream_t stream) {
 bool tc_f32x3_supported(const Problem& p, bool check_pointers) {
   if (p.in_dtype != KSMM_F32 || p.out_dtype != KSMM_F32) return false;
   if (p.batch <= 0 || p.batch > 0x7fffffffLL) return false;
-  // tensor-map rules: every global stride is a multiple of 16 bytes
-  if (p.b % 4 != 0) return false;
+  // the operand tiles are addressed in atoms of 32 columns; global strides are multiples of 16 bytes
+  if (p.b % 32 != 0) return false;
   if (p.bs_last) {
-    if (p.batch % 4 != 0) return false;
+    if (p.batch % 32 != 0) return false;
   } else {
     if (p.d != 1 || p.c % 4 != 0) return false;
   }
@@ -611,7 +517,7 @@ bool tc_f32x3_supported(const Problem& p, bool check_pointers) {
 }
 
 int tc_f32x3_launch(const Problem& p, cudaStream_t stream) {
-  // <batch-last, j tile, raw input stages, raw weight stages, operand buffers>.  The j tile
+  // <batch-last, j tile, stages>.  The j tile
   // is the one with the least padded work: a tile costs about 0.4 (input side) + 0.6 * NJ / 128.
   int nj = 128;
   double best = 1e30;
@@ -620,13 +526,13 @@ int tc_f32x3_launch(const Problem& p, cudaStream_t stream) {
     if (cost < best - 1e-9) { best = cost; nj = cand; }
   }
   if (p.bs_last) {
-    if (nj == 128) return tc::launch_f<true, 128, 3, 3, 2>(p, stream);
-    if (nj == 96) return tc::launch_f<true, 96, 4, 4, 2>(p, stream);
-    return tc::launch_f<true, 64, 3, 4, 2>(p, stream);
+    if (nj == 128) return tc::launch_f<true, 128, 3>(p, stream);
+    if (nj == 96) return tc::launch_f<true, 96, 4>(p, stream);
+    return tc::launch_f<true, 64, 4>(p, stream);
   }
-  if (nj == 128) return tc::launch_f<false, 128, 0, 4, 2>(p, stream);
-  if (nj == 96) return tc::launch_f<false, 96, 0, 2, 3>(p, stream);
-  return tc::launch_f<false, 64, 0, 4, 3>(p, stream);
+  if (nj == 128) return tc::launch_f<false, 128, 3>(p, stream);
+  if (nj == 96) return tc::launch_f<false, 96, 3>(p, stream);
+  return tc::launch_f<false, 64, 4>(p, stream);
 }
 
 }  // namespace ksmm

@@ -423,10 +423,10 @@ static CUtensorMapDataType tm_dtype(int dt) {
   }
 }
 
-// rank-R tiled map with 128-byte swizzle; dims/strides innermost first,
-// strides in elements (stride of dim 0 is implicitly 1)
+// rank-R tiled map with 128-byte swizzle (16-byte or, with atom32, 32-byte atoms) or none;
+// dims/strides innermost first, strides in elements (stride of dim 0 is implicitly 1)
 int encode_map(CUtensorMap* tm, int dt, int rank, const void* base, const uint64_t* dims,
-               const uint64_t* strides_elems, const uint32_t* box, bool swizzle128) {
+               const uint64_t* strides_elems, const uint32_t* box, bool swizzle128, bool atom32) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return set_error(KSMM_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
   cuuint64_t gdim[5], gstr[5];
@@ -440,7 +440,8 @@ int encode_map(CUtensorMap* tm, int dt, int rank, const void* base, const uint64
   }
   CUresult res = fn(tm, tm_dtype(dt), rank, const_cast<void*>(base), gdim, gstr, bx, es,
                     CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    swizzle128 ? (atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B)
+                               : CU_TENSOR_MAP_SWIZZLE_NONE,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (res != CUDA_SUCCESS)
     return set_error(KSMM_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rank %d)",

@@ -97,7 +97,8 @@ def test_config_tables():
     assert sup(_lib.KSMM_ALGO_TC, 1, 25088, 1, 768, 192, 4, F32, F32, 1) == 0
     assert sup(_lib.KSMM_ALGO_TC, 0, 25088, 1, 768, 192, 4, F32, F32, 0) == 0
     assert sup(_lib.KSMM_ALGO_TC, 0, 25088, 4, 192, 192, 1, F32, F32, 0) == 1
-    assert sup(_lib.KSMM_ALGO_TC, 0, 25086, 4, 192, 192, 1, F32, F32, 1) == 0   # batch*4 % 16 != 0
+    assert sup(_lib.KSMM_ALGO_TC, 0, 25080, 4, 192, 192, 1, F32, F32, 1) == 0   # batch % 32 != 0
+    assert sup(_lib.KSMM_ALGO_TC, 0, 25088, 4, 200, 192, 1, F32, F32, 1) == 0   # b % 32 != 0
     assert sup(_lib.KSMM_ALGO_TC, 0, 25087, 1, 768, 192, 4, F16, F16, 1) == 0   # batch*2 % 16 != 0
     assert sup(_lib.KSMM_ALGO_TC, 0, 25088, 1, 449, 192, 4, F16, F16, 1) == 0   # b*2 % 16 != 0
     assert sup(_lib.KSMM_ALGO_TC, 0, 25088, 4, 192, 192, 1, BF16, BF16, 0) == 1

@@ -236,10 +236,10 @@ def test_batch_first_layout_conversion_path(dtype):
     kb.check_device()
 
 
-F32_TC_LAST = [(1, 64, 64, 1), (2, 128, 32, 4), (1, 768, 192, 4), (6, 64, 64, 1), (3, 48, 80, 2),
-               (1, 136, 72, 4), (1, 64, 64, 16), (1, 192, 768, 2), (2, 36, 200, 3), (2, 96, 40, 2)]
-F32_TC_FIRST = [(1, 64, 64, 1), (4, 192, 192, 1), (3, 48, 80, 1), (2, 72, 48, 1), (6, 64, 64, 1),
-                (1, 200, 100, 1), (1, 768, 192, 1), (2, 96, 40, 1), (1, 88, 64, 1)]
+F32_TC_LAST = [(1, 64, 64, 1), (2, 128, 32, 4), (1, 768, 192, 4), (6, 64, 64, 1), (3, 96, 80, 2),
+               (1, 160, 72, 4), (1, 64, 64, 16), (1, 192, 768, 2), (2, 32, 200, 3), (2, 96, 40, 2)]
+F32_TC_FIRST = [(1, 64, 64, 1), (4, 192, 192, 1), (3, 96, 80, 1), (2, 64, 48, 1), (6, 64, 64, 1),
+                (1, 224, 100, 1), (1, 768, 192, 1), (2, 96, 40, 1)]
 
 
 @pytest.mark.parametrize("bs_last", [True, False])
@@ -249,7 +249,7 @@ def test_tc_family_fp32_split_into_three_tf32_products(bs_last):
     (a single tf32 product would sit at about 5e-4), so the test asks for 3e-6 (measured: 3e-7
     for c <= 192, 2e-6 for c = 768, where the truncating accumulator shows)."""
     for pi, pattern in enumerate(F32_TC_LAST if bs_last else F32_TC_FIRST):
-        for batch in (8, 136, 520):
+        for batch in ((32, 160, 544) if bs_last else (8, 136, 520)):   # batch-last: multiples of 32
             x, w = _inputs(pattern, batch, torch.float32, bs_last, seed=600 + pi)
             y = _run(x, w, pattern, bs_last, algo=_lib.KSMM_ALGO_TC, config=0)
             assert not np.isnan(y).any(), (pattern, batch)
@@ -273,10 +273,10 @@ def test_bias_and_alpha_epilogue(bs_last):
     for dtype, algo in ((torch.float32, _lib.KSMM_ALGO_SIMT), (torch.float32, _lib.KSMM_ALGO_TC),
                         (torch.float16, _lib.KSMM_ALGO_SIMT),
                         (torch.float16, _lib.KSMM_ALGO_TC), (torch.bfloat16, _lib.KSMM_ALGO_TC)):
-        pattern, batch = (2, 72, 48, 1), 72
+        pattern, batch = (2, 96, 48, 1), 96
         x, w = _inputs(pattern, batch, dtype, bs_last, seed=9)
         rng = np.random.RandomState(10)
-        bias = torch.from_numpy(rng.standard_normal(2 * 72).astype(np.float32)).to(dtype)
+        bias = torch.from_numpy(rng.standard_normal(2 * 96).astype(np.float32)).to(dtype)
         y = _run(x, w, pattern, bs_last, algo=algo, bias=bias.to(DEV), alpha=0.5)
         ref = 0.5 * _oracle(x, w, bs_last)
         bf = bias.float().numpy()
