@@ -492,6 +492,58 @@ def run_ours(args, rank, world, local_rank):
                            "fc1=[(4,192,192,1),(1,768,192,4)], fc2=[(1,192,768,4),(4,192,192,1)], batch-first; "
                            "attention / LayerNorm / GELU are stock PyTorch; forward captured in a CUDA graph"}
 
+    # ---- chains: one chained call (layout-fused intermediates) against per-factor calls ------------
+    chains = None
+    if not args.no_vit and not args.only:
+        import math
+        chain_list = [("ks_vit_fc1", [(4, 192, 192, 1), (1, 768, 192, 4)]),
+                      ("ks_vit_fc2", [(1, 192, 768, 4), (4, 192, 192, 1)]),
+                      ("three_factor_1024", [(1, 64, 64, 16), (4, 64, 64, 4), (16, 64, 64, 1)])]
+        chains = []
+        for name, pats in chain_list:
+            gen = torch.Generator(device=dev).manual_seed(11)
+            n_in = pats[0][0] * pats[0][2] * pats[0][3]
+            xs = [torch.randn((BATCH, n_in), device=dev, dtype=torch.float16, generator=gen) for _ in range(4)]
+            layer = kb.KSLinear(pats, weights=None, bias=False, algo="kernel", dtype=torch.float16,
+                                bs_last=False, device=dev)
+
+            def run_chained(x):
+                return layer(x)
+
+            def run_per_factor(x):
+                for p_, w_ in zip(pats, layer.factors):
+                    x = kb.forward_ex(x, w_, False, *p_)
+                return x
+
+            res = {}
+            with torch.no_grad():
+                for label, fn in (("chained", run_chained), ("per_factor", run_per_factor)):
+                    for x in xs[:2]:
+                        fn(x)
+                    torch.cuda.synchronize()
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g):
+                        for r in range(8):
+                            fn(xs[r % 4])
+                    g.replay()
+                    torch.cuda.synchronize()
+                    t0_, t1_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    t0_.record()
+                    g.replay()
+                    t1_.record()
+                    torch.cuda.synchronize()
+                    res[label] = t0_.elapsed_time(t1_) / 8
+                    del g
+                ya, yb = run_chained(xs[0]).float(), run_per_factor(xs[0]).float()
+                rel = float((ya - yb).norm() / yb.norm())
+            chains.append({"chain": name, "patterns": [list(p_) for p_ in pats], "dtype": "fp16",
+                           "layout": "bs_first", "ms_chained": round(res["chained"], 5),
+                           "ms_per_factor": round(res["per_factor"], 5),
+                           "speedup": round(res["per_factor"] / res["chained"], 3),
+                           "rel_diff_between_the_two": rel})
+            del layer, xs
+        kb.check_device()
+
     if rank != 0:
         return
 
@@ -521,7 +573,7 @@ def run_ours(args, rank, world, local_rank):
         "roofline": roofline_of(per[dom], cs[dom]),
         "roofline_hbm": roofline_of(per[dom_hbm], cs[dom_hbm]) if dom_hbm is not None else None,
         "ffma_peak_tflops": round(ffma_peak, 2), "fp32_ffma_only": fp32_exact,
-        "cpu_baseline": cpu, "ksvit_b": ksvit, "per_pattern": per,
+        "cpu_baseline": cpu, "ksvit_b": ksvit, "chains": chains, "per_pattern": per,
     }
     print(json.dumps(line), flush=True)
 

@@ -135,10 +135,19 @@ struct Problem {
   int in_dtype, out_dtype;
   int bs_last;
   float alpha;
+  // Chains only.  out_regroup_d > 0: store the output regrouped by the blocks of the next factor
+  // (c = out_regroup_c, d = out_regroup_d): feature (i2*c + k)*d + l goes to (i2*d + l)*c + k.
+  // in_regrouped: the input already has that order for this factor's own (c, d).
+  int out_regroup_d = 0, out_regroup_c = 0;
+  int in_regrouped = 0;
 };
 
 // host-side error plumbing (defined in ksmm_cu.cu)
 int set_error(int status, const char* fmt, ...);
 void count_launch();
+// Device memory of at least `bytes` from a per-device scratch that is grown on demand (never
+// during a stream capture) and shared by all calls on that device: calls that use it on
+// different streams of one device must not overlap.
+int acquire_layout_scratch(size_t bytes, cudaStream_t stream, void** out);
 
 }  // namespace ksmm

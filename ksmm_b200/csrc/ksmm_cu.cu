@@ -163,6 +163,34 @@ struct ConvScratch {
 static std::mutex g_conv_mu;
 static ConvScratch g_conv[64];
 
+// Per-device scratch of the layout-conversion and regrouping paths (see common.cuh).
+int acquire_layout_scratch(size_t bytes, cudaStream_t stream, void** out) {
+  int dev = 0;
+  KSMM_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return set_error(KSMM_ERR_UNSUPPORTED, "device ordinal %d", dev);
+  std::lock_guard<std::mutex> g(g_conv_mu);
+  ConvScratch& sc = g_conv[dev];
+  if (sc.cap < bytes) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(stream, &cs);
+    if (cs != cudaStreamCaptureStatusNone)
+      return set_error(KSMM_ERR_WORKSPACE,
+                       "the layout-conversion scratch must grow to %zu bytes, which cannot happen "
+                       "inside a stream capture: make one call outside the capture first",
+                       bytes);
+    if (sc.ptr) {
+      KSMM_CUDA_OK(cudaStreamSynchronize(stream));
+      KSMM_CUDA_OK(cudaFree(sc.ptr));
+      sc.ptr = nullptr;
+      sc.cap = 0;
+    }
+    KSMM_CUDA_OK(cudaMalloc(&sc.ptr, bytes));
+    sc.cap = bytes;
+  }
+  *out = sc.ptr;
+  return KSMM_OK;
+}
+
 static bool conversion_applies(const Problem& p) {
   if (p.bs_last || p.d == 1) return false;
   if (reinterpret_cast<uintptr_t>(p.w) % 16 != 0) return false;
@@ -191,32 +219,9 @@ static int forward_via_transpose(const Problem& p, cudaStream_t stream) {
   const int64_t n_in = static_cast<int64_t>(p.a) * p.c * p.d, n_out = static_cast<int64_t>(p.a) * p.b * p.d;
   const size_t in_bytes = align_up(static_cast<size_t>(n_in) * p.batch * es, 256);
   const size_t out_bytes = align_up(static_cast<size_t>(n_out) * p.batch * os, 256);
-  int dev = 0;
-  KSMM_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return set_error(KSMM_ERR_UNSUPPORTED, "device ordinal %d", dev);
   void* base = nullptr;
-  {
-    std::lock_guard<std::mutex> g(g_conv_mu);
-    ConvScratch& sc = g_conv[dev];
-    if (sc.cap < in_bytes + out_bytes) {
-      cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
-      cudaStreamIsCapturing(stream, &cs);
-      if (cs != cudaStreamCaptureStatusNone)
-        return set_error(KSMM_ERR_WORKSPACE,
-                         "the layout-conversion scratch must grow to %zu bytes, which cannot happen "
-                         "inside a stream capture: make one call outside the capture first",
-                         in_bytes + out_bytes);
-      if (sc.ptr) {
-        KSMM_CUDA_OK(cudaStreamSynchronize(stream));
-        KSMM_CUDA_OK(cudaFree(sc.ptr));
-        sc.ptr = nullptr;
-        sc.cap = 0;
-      }
-      KSMM_CUDA_OK(cudaMalloc(&sc.ptr, in_bytes + out_bytes));
-      sc.cap = in_bytes + out_bytes;
-    }
-    base = sc.ptr;
-  }
+  int stq = acquire_layout_scratch(in_bytes + out_bytes, stream, &base);
+  if (stq != KSMM_OK) return stq;
   void* xt = base;
   void* yt = static_cast<char*>(base) + in_bytes;
   int st = launch_transpose(p.in, xt, p.batch, n_in, es, stream);  // (batch, in) -> (in, batch)
@@ -420,6 +425,7 @@ int ksmm_cu_chain_forward(const void* input, const void* const* values, void* ou
                      workspace_bytes);
   const size_t half = nfactors == 2 ? need : need / 2;
   const void* cur = input;
+  bool cur_regrouped = false;  // the intermediate in `cur` is regrouped by the blocks of factor f
   for (int f = 0; f < nfactors; ++f) {
     const int32_t* q = patterns + 4 * f;
     const bool last = (f + 1 == nfactors);
@@ -428,9 +434,39 @@ int ksmm_cu_chain_forward(const void* input, const void* const* values, void* ou
     p.in = cur; p.w = values[f]; p.out = dst; p.bias = last ? bias : nullptr;
     p.batch = batch; p.a = q[0]; p.b = q[1]; p.c = q[2]; p.d = q[3];
     p.in_dtype = dtype; p.out_dtype = dtype; p.bs_last = bs_last; p.alpha = 1.f;
-    int st = dispatch(p, KSMM_ALGO_AUTO, -1, static_cast<cudaStream_t>(stream));
+    // Layout fusion of consecutive batch-first factors: when the next factor has d = 2 or 4 and
+    // this one can store its output regrouped by the next factor's blocks, the intermediate is
+    // written in that order and the next factor runs the kernel without the transposer stage
+    // (and without a regrouping pass).
+    bool next_regrouped = false;
+    if (!last && !bs_last) {
+      const int32_t* r = patterns + 4 * (f + 1);
+      Problem nx = p;
+      nx.in = dst; nx.out = dst; nx.w = values[f + 1]; nx.bias = nullptr;
+      nx.a = r[0]; nx.b = r[1]; nx.c = r[2]; nx.d = r[3];
+      p.out_regroup_c = r[2];
+      p.out_regroup_d = r[3];
+      Choice ch;
+      const bool pinned = lookup_choice(p, &ch) || lookup_choice(nx, &ch);  // a tuned choice wins
+      if (!pinned && !cur_regrouped && (r[3] == 2 || r[3] == 4) && tc_can_regroup_output(p) &&
+          tc_config_supported(nx, 1, true) && tc_default_config(nx) >= 0) {
+        next_regrouped = true;
+      } else {
+        p.out_regroup_c = p.out_regroup_d = 0;
+      }
+    }
+    int st;
+    if (cur_regrouped) {
+      p.in_regrouped = 1;
+      st = tc_launch(p, 1, static_cast<cudaStream_t>(stream));
+    } else if (next_regrouped) {
+      st = tc_launch(p, -1, static_cast<cudaStream_t>(stream));
+    } else {
+      st = dispatch(p, KSMM_ALGO_AUTO, -1, static_cast<cudaStream_t>(stream));
+    }
     if (st != KSMM_OK) return st;
     cur = dst;
+    cur_regrouped = next_regrouped;
   }
   return KSMM_OK;
 }

@@ -260,6 +260,7 @@ __global__ void __launch_bounds__(kThreadsF, 1)
     KSMM_TRACE_DECL;
     const bool tron = (warp == 2 || warp == 6) && lane == 0;
     const int trole = on_w ? 3 : 2;
+    (void)tron; (void)trole;
     for (uint32_t row = row_begin; row < row_end && ok; ++row) {
       for (int qc = 0; qc < nchunks; ++qc) {
         int got = 1;

@@ -66,6 +66,7 @@ struct Params {
   const void* bias;
   int out_dtype;
   int* status;
+  int rg_d, rg_c;  // batch-first, 16-bit: store regrouped for the next factor's (c, d); 0 = natural order
   int ablate;  // diagnostic: bit0 skip TMA loads, bit1 skip MMAs, bit2 skip epilogue work
 };
 
@@ -331,7 +332,29 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
           }
           const uint32_t rowaddr = stg + lane * 128;
-          if constexpr (OS == 2) {
+          if (!BS_LAST && OS == 2 && P.rg_d != 0) {
+            // regrouped store: element e of the 64 goes to (e % d2) * (64 / d2) + e / d2; the tile is
+            // not swizzled (its TMA box rows are 64 / d2 elements wide)
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                if (P.rg_d == 4) {
+                  const int l2 = ch >> 1, t = (ch & 1) * 4 + e;
+                  w[e] = pack2(__uint_as_float(r[(2 * t) * 4 + l2]), __uint_as_float(r[(2 * t + 1) * 4 + l2]),
+                               P.out_dtype);
+                } else {
+                  const int l2 = ch >> 2, t = (ch & 3) * 4 + e;
+                  w[e] = pack2(__uint_as_float(r[(2 * t) * 2 + l2]), __uint_as_float(r[(2 * t + 1) * 2 + l2]),
+                               P.out_dtype);
+                }
+              }
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowaddr + ch * 16),
+                           "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                           : "memory");
+            }
+          } else if constexpr (OS == 2) {
 #pragma unroll
             for (int ch = 0; ch < 8; ++ch) {
               uint32_t w[4];
@@ -360,6 +383,10 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (lane == 0) {
             if constexpr (BS_LAST) {
               tma_store_4d(&tmY, stg, n0 + cbi * C::CB, l, j0 + q * 32, i);
+            } else if (P.rg_d != 0) {
+              // output seen as (k2, l2, i2, n): the tile starts at feature m0 = i*b + j0 + 64*cbi
+              const int m0 = i * P.b + j0 + cbi * C::CB, seg = P.rg_c * P.rg_d;
+              tma_store_4d(&tmY, stg, (m0 % seg) / P.rg_d, 0, m0 / seg, n0 + q * 32);
             } else {
               tma_store_3d(&tmY, stg, j0 + cbi * C::CB, i, n0 + q * 32);
             }
@@ -508,6 +535,8 @@ static int launch_one(const Problem& p, cudaStream_t stream) {
   P.alpha = p.alpha;
   P.bias = p.bias;
   P.out_dtype = p.out_dtype;
+  P.rg_d = (!BS_LAST && OS == 2) ? p.out_regroup_d : 0;
+  P.rg_c = p.out_regroup_c;
   P.status = status_word();
   {
     static const int ablate = [] { const char* e = getenv("KSMM_TC_ABLATE"); return e ? atoi(e) : 0; }();
@@ -534,10 +563,19 @@ static int launch_one(const Problem& p, cudaStream_t stream) {
     const uint64_t xs[3] = {1, c, a * c};
     const uint32_t xb[3] = {static_cast<uint32_t>(KC), 1, 128};
     if ((st = encode_map(&tmX, p.in_dtype, 3, p.in, xd, xs, xb)) != KSMM_OK) return st;
-    const uint64_t yd[3] = {b, a, B};
-    const uint64_t ys[3] = {1, b, a * b};
-    const uint32_t yb[3] = {static_cast<uint32_t>(C::CB), 1, 32};
-    if ((st = encode_map(&tmY, p.out_dtype, 3, p.out, yd, ys, yb)) != KSMM_OK) return st;
+    if (p.out_regroup_d > 0 && OS == 2) {
+      // regrouped output (k2, l2, i2, n): a staging tile of 64 features is d2 runs of 64 / d2
+      const uint64_t c2 = p.out_regroup_c, d2 = p.out_regroup_d;
+      const uint64_t yd[4] = {c2, d2, a * b / (c2 * d2), B};
+      const uint64_t ys[4] = {1, c2, c2 * d2, a * b};
+      const uint32_t yb[4] = {static_cast<uint32_t>(C::CB / d2), static_cast<uint32_t>(d2), 1, 32};
+      if ((st = encode_map(&tmY, p.out_dtype, 4, p.out, yd, ys, yb, false)) != KSMM_OK) return st;
+    } else {
+      const uint64_t yd[3] = {b, a, B};
+      const uint64_t ys[3] = {1, b, a * b};
+      const uint32_t yb[3] = {static_cast<uint32_t>(C::CB), 1, 32};
+      if ((st = encode_map(&tmY, p.out_dtype, 3, p.out, yd, ys, yb)) != KSMM_OK) return st;
+    }
     P.tiles_n = static_cast<int>((B + 127) / 128);
     P.tiles_j = static_cast<int>((b + NT - 1) / NT);
   }
@@ -609,7 +647,9 @@ int tc_num_configs() { return tc::kNumConfigs; }
 bool tc_config_supported(const Problem& p, int config, bool check_pointers) {
   if (config < 0 || config >= tc::kNumConfigs) return false;
   if (p.in_dtype == KSMM_F32) return config == 0 && tc_f32x3_supported(p, check_pointers);
-  if (!p.bs_last && p.d != 1) return config == 0 && tc_bsfirst_d_supported(p, check_pointers);
+  if (!p.bs_last && p.d != 1)
+    return config == 0 ? tc_bsfirst_d_supported(p, check_pointers)
+                       : (config == 1 && tc_bsfirst_dp_supported(p, check_pointers));
   if (config == 4 && p.in_dtype == KSMM_F8E4M3) return false;
   const int es = dtype_size(p.in_dtype), os = dtype_size(p.out_dtype);
   if (p.in_dtype == KSMM_F16 || p.in_dtype == KSMM_BF16) {
@@ -635,6 +675,16 @@ bool tc_config_supported(const Problem& p, int config, bool check_pointers) {
   return true;
 }
 
+bool tc_can_regroup_output(const Problem& p) {
+  // the 16-bit batch-first d = 1 kernel, whole 64-feature staging tiles that stay inside one
+  // block row of the next factor
+  if (p.bs_last || p.d != 1 || (p.in_dtype != KSMM_F16 && p.in_dtype != KSMM_BF16)) return false;
+  if (p.out_dtype != p.in_dtype || p.b % 64 != 0) return false;
+  const int d2 = p.out_regroup_d, c2 = p.out_regroup_c;
+  if ((d2 != 2 && d2 != 4) || c2 <= 0 || (c2 * d2) % 64 != 0 || c2 % 8 != 0) return false;
+  return (static_cast<int64_t>(p.a) * p.b) % (static_cast<int64_t>(c2) * d2) == 0 && tc_default_config(p) >= 0;
+}
+
 int tc_default_config(const Problem& p) {
   if (!tc_config_supported(p, 0, true)) return -1;
   // tiny blocks are bandwidth problems that the FFMA family tiles more tightly
@@ -642,6 +692,10 @@ int tc_default_config(const Problem& p) {
   // fp32 on the tensor cores: the accumulator truncates once per k step of 8, so the default
   // stops at c = 1024 (relative error about 2e-6 at c = 768); longer sums take the FFMA family
   if (p.in_dtype == KSMM_F32) return p.c <= 1024 ? 0 : -1;
+  // batch-first, d = 2 or 4: the in-kernel split (configuration 0).  Configuration 1 (regrouping pass,
+  // then the kernel without the transposer stage) measured slower for a single factor (94 us
+  // against 85 us for (1,768,192,4) fp16); chains use its kernel when the previous factor can
+  // store the intermediate regrouped for free.
   if (!p.bs_last && p.d != 1) return 0;
   if (p.bs_last) return p.batch >= 256 * 148 / 2 || p.batch >= 4096 ? 0 : 1;
   return p.b > 128 ? 0 : (p.b > 64 ? 1 : 4);
@@ -656,7 +710,9 @@ int tc_launch(const Problem& p, int config, cudaStream_t stream) {
                      p.a, p.b, p.c, p.d, static_cast<long long>(p.batch), p.in_dtype, p.bs_last);
   const bool last = p.bs_last != 0;
   if (p.in_dtype == KSMM_F32) return tc_f32x3_launch(p, stream);
-  if (!last && p.d != 1) return tc_bsfirst_d_launch(p, stream);
+  if (!last && p.d != 1) return config == 1 ? tc_bsfirst_dp_launch(p, stream) : tc_bsfirst_d_launch(p, stream);
+  if (p.out_regroup_d > 0 && !tc_can_regroup_output(p))
+    return set_error(KSMM_ERR_UNSUPPORTED, "this factor cannot store a regrouped output");
   if (p.in_dtype == KSMM_F8E4M3) {
     if (p.out_dtype == KSMM_F32)
       return last ? tc::launch_cfg<true, 1, 4>(p, config, stream)

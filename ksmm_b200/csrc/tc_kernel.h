@@ -13,6 +13,9 @@ bool tc_config_supported(const Problem& p, int config, bool check_pointers);
 // heuristic default configuration, or -1 if the family cannot run `p`
 int tc_default_config(const Problem& p);
 int tc_launch(const Problem& p, int config, cudaStream_t stream);
+// true if `p` (with out_regroup_c / out_regroup_d set) can store its output regrouped by the
+// blocks of the next factor of a chain
+bool tc_can_regroup_output(const Problem& p);
 // Synchronises `stream` and reports a device-side timeout recorded by any
 // earlier launch of this family on the current device (then clears it).
 int tc_check_device(cudaStream_t stream);
@@ -20,6 +23,11 @@ int tc_check_device(cudaStream_t stream);
 // batch-first factors with d = 2 or 4 (tc_bsfirst_d.cu); a single configuration
 bool tc_bsfirst_d_supported(const Problem& p, bool check_pointers);
 int tc_bsfirst_d_launch(const Problem& p, cudaStream_t stream);
+
+// batch-first factors with d = 2 or 4 through a regrouping pass and a kernel without the
+// transposer stage (tc_bsfirst_dp.cu); configuration 1 of such problems
+bool tc_bsfirst_dp_supported(const Problem& p, bool check_pointers);
+int tc_bsfirst_dp_launch(const Problem& p, cudaStream_t stream);
 
 // fp32 factors as three tf32 products per term (tc_f32x3.cu); a single configuration
 bool tc_f32x3_supported(const Problem& p, bool check_pointers);
