@@ -67,7 +67,6 @@ struct Params {
   int out_dtype;
   int* status;
   int rg_d, rg_c;  // batch-first, 16-bit: store regrouped for the next factor's (c, d); 0 = natural order
-  int ablate;  // diagnostic: bit0 skip TMA loads, bit1 skip MMAs, bit2 skip epilogue work
 };
 
 // WRES = true  ("weight-stationary"): the CTA's weight tile (all NWC k chunks of
@@ -306,7 +305,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (BS_LAST && P.bias != nullptr && q * 32 + lane < row_limit)
         bias_row = bias_at(P.bias, (static_cast<int64_t>(i) * P.b + j0 + q * 32 + lane) * d + l,
                            P.out_dtype);
-      if (warp_active && !(P.ablate & 4)) {
+      if (warp_active) {
 #pragma unroll 1
         for (int cbi = grp; cbi < NT / C::CB; cbi += kEpilogueWarps / 4) {
           if (cbi * C::CB >= col_limit) break;
@@ -538,10 +537,6 @@ static int launch_one(const Problem& p, cudaStream_t stream) {
   P.rg_d = (!BS_LAST && OS == 2) ? p.out_regroup_d : 0;
   P.rg_c = p.out_regroup_c;
   P.status = status_word();
-  {
-    static const int ablate = [] { const char* e = getenv("KSMM_TC_ABLATE"); return e ? atoi(e) : 0; }();
-    P.ablate = ablate;
-  }
   if (!P.status) return set_error(KSMM_ERR_CUDA, "cannot resolve the device status word");
   const uint32_t fmt = p.in_dtype == KSMM_BF16 ? 1u : 0u;  // f16 / e4m3 = 0, bf16 = 1
   uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) |
