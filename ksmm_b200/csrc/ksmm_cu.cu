@@ -5,6 +5,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <algorithm>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -291,9 +292,13 @@ __global__ void __launch_bounds__(256) ffma_probe_kernel(float* sink, int iters,
 struct HostPathState {
   std::mutex mu;
   int device = -1;
-  cudaStream_t stream = nullptr;
-  void* buf[4] = {nullptr, nullptr, nullptr, nullptr};  // input, output, weights, workspace
-  size_t cap[4] = {0, 0, 0, 0};
+  cudaStream_t stream = nullptr;                   // compute (and everything, for small batches)
+  cudaStream_t s_in = nullptr, s_out = nullptr;    // copy streams of the pipelined path
+  cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_cmp[2] = {nullptr, nullptr},
+              ev_out[2] = {nullptr, nullptr}, ev_w = nullptr;
+  // input A, output A, weights, workspace, input B, output B
+  void* buf[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  size_t cap[6] = {0, 0, 0, 0, 0, 0};
 };
 static HostPathState g_host;
 
@@ -504,23 +509,30 @@ int ksmm_cu_chain_forward_host(const void* host_input, const void* const* host_v
   std::lock_guard<std::mutex> g(g_host.mu);
   KSMM_CUDA_OK(cudaSetDevice(device));
   if (g_host.device != device) {
-    // buffers belong to one device at a time; moving devices drops them
-    for (int q = 0; q < 4; ++q) {
+    // buffers, streams and events belong to one device at a time; moving devices drops them
+    for (int q = 0; q < 6; ++q) {
       if (g_host.buf[q]) cudaFree(g_host.buf[q]);
       g_host.buf[q] = nullptr;
       g_host.cap[q] = 0;
     }
-    if (g_host.stream) cudaStreamDestroy(g_host.stream);
-    g_host.stream = nullptr;
-    KSMM_CUDA_OK(cudaStreamCreateWithFlags(&g_host.stream, cudaStreamNonBlocking));
+    for (cudaStream_t* sp : {&g_host.stream, &g_host.s_in, &g_host.s_out}) {
+      if (*sp) cudaStreamDestroy(*sp);
+      *sp = nullptr;
+      KSMM_CUDA_OK(cudaStreamCreateWithFlags(sp, cudaStreamNonBlocking));
+    }
+    for (cudaEvent_t* ep : {&g_host.ev_in[0], &g_host.ev_in[1], &g_host.ev_cmp[0], &g_host.ev_cmp[1],
+                            &g_host.ev_out[0], &g_host.ev_out[1], &g_host.ev_w}) {
+      if (*ep) cudaEventDestroy(*ep);
+      *ep = nullptr;
+      KSMM_CUDA_OK(cudaEventCreateWithFlags(ep, cudaEventDisableTiming));
+    }
     g_host.device = device;
   }
   const size_t es = dtype_size(dtype);
   const int32_t* p0 = patterns;
   const int32_t* pl = patterns + 4 * (nfactors - 1);
-  const size_t in_bytes = static_cast<size_t>(p0[0]) * p0[2] * p0[3] * batch * es;
+  const size_t in_feats = static_cast<size_t>(p0[0]) * p0[2] * p0[3];
   const size_t out_feats = static_cast<size_t>(pl[0]) * pl[1] * pl[3];
-  const size_t out_bytes = out_feats * batch * es;
   std::vector<size_t> woff(nfactors + 1, 0);
   for (int f = 0; f < nfactors; ++f) {
     const int32_t* q = patterns + 4 * f;
@@ -528,34 +540,92 @@ int ksmm_cu_chain_forward_host(const void* host_input, const void* const* host_v
   }
   const size_t bias_off = woff[nfactors];
   const size_t w_bytes = bias_off + (host_bias ? align_up(out_feats * es, 256) : 0);
-  const size_t ws_bytes = ksmm_cu_chain_workspace_bytes(nfactors, patterns, batch, dtype);
+
+  // The batch is cut into slices of `slice` entries that move through a three-stage pipeline
+  // (host->device copy, chain, device->host copy) on three streams with two buffers per
+  // direction, so that both directions of the link are busy at the same time.
+  int64_t slice = batch;
+  if (batch >= 16384) slice = ((batch + 7) / 8 + 255) / 256 * 256;
+  else if (batch >= 8192) slice = ((batch + 3) / 4 + 255) / 256 * 256;
+  const int nslices = static_cast<int>((batch + slice - 1) / slice);
+  const size_t ws_bytes = ksmm_cu_chain_workspace_bytes(nfactors, patterns, slice, dtype);
   int st;
-  if ((st = host_reserve(0, in_bytes)) != KSMM_OK) return st;
-  if ((st = host_reserve(1, out_bytes)) != KSMM_OK) return st;
+  if ((st = host_reserve(0, in_feats * slice * es)) != KSMM_OK) return st;
+  if ((st = host_reserve(1, out_feats * slice * es)) != KSMM_OK) return st;
   if ((st = host_reserve(2, w_bytes)) != KSMM_OK) return st;
   if ((st = host_reserve(3, ws_bytes)) != KSMM_OK) return st;
-  cudaStream_t s = g_host.stream;
-  KSMM_CUDA_OK(cudaMemcpyAsync(g_host.buf[0], host_input, in_bytes, cudaMemcpyHostToDevice, s));
+  if (nslices > 1) {
+    if ((st = host_reserve(4, in_feats * slice * es)) != KSMM_OK) return st;
+    if ((st = host_reserve(5, out_feats * slice * es)) != KSMM_OK) return st;
+  }
+  cudaStream_t sc = g_host.stream, si = nslices > 1 ? g_host.s_in : sc, so = nslices > 1 ? g_host.s_out : sc;
   std::vector<const void*> dvals(nfactors);
   for (int f = 0; f < nfactors; ++f) {
     const int32_t* q = patterns + 4 * f;
     char* dst = static_cast<char*>(g_host.buf[2]) + woff[f];
     KSMM_CUDA_OK(cudaMemcpyAsync(dst, host_values[f],
                                  static_cast<size_t>(q[0]) * q[1] * q[2] * q[3] * es,
-                                 cudaMemcpyHostToDevice, s));
+                                 cudaMemcpyHostToDevice, si));
     dvals[f] = dst;
   }
   const void* dbias = nullptr;
   if (host_bias) {
     char* dst = static_cast<char*>(g_host.buf[2]) + bias_off;
-    KSMM_CUDA_OK(cudaMemcpyAsync(dst, host_bias, out_feats * es, cudaMemcpyHostToDevice, s));
+    KSMM_CUDA_OK(cudaMemcpyAsync(dst, host_bias, out_feats * es, cudaMemcpyHostToDevice, si));
     dbias = dst;
   }
-  st = ksmm_cu_chain_forward(g_host.buf[0], dvals.data(), g_host.buf[1], dbias, g_host.buf[3],
-                             g_host.cap[3], batch, nfactors, patterns, dtype, bs_last, s);
-  if (st != KSMM_OK) return st;
-  KSMM_CUDA_OK(cudaMemcpyAsync(host_output, g_host.buf[1], out_bytes, cudaMemcpyDeviceToHost, s));
-  KSMM_CUDA_OK(cudaStreamSynchronize(s));
+  if (nslices > 1) {
+    KSMM_CUDA_OK(cudaEventRecord(g_host.ev_w, si));
+    KSMM_CUDA_OK(cudaStreamWaitEvent(sc, g_host.ev_w, 0));
+  }
+  const char* hin = static_cast<const char*>(host_input);
+  char* hout = static_cast<char*>(host_output);
+  for (int k = 0; k < nslices; ++k) {
+    const int64_t n0 = static_cast<int64_t>(k) * slice;
+    const int64_t cn = std::min<int64_t>(slice, batch - n0);
+    const int sl = k & 1;
+    void* din = g_host.buf[sl ? 4 : 0];
+    void* dout = g_host.buf[sl ? 5 : 1];
+    // host -> device, once the chain of slice k - 2 has read this input buffer
+    if (k >= 2) KSMM_CUDA_OK(cudaStreamWaitEvent(si, g_host.ev_cmp[sl], 0));
+    if (bs_last) {
+      // (features, batch) row-major: a slice is a column block
+      KSMM_CUDA_OK(cudaMemcpy2DAsync(din, cn * es, hin + n0 * es, batch * es, cn * es, in_feats,
+                                     cudaMemcpyHostToDevice, si));
+    } else {
+      KSMM_CUDA_OK(cudaMemcpyAsync(din, hin + n0 * in_feats * es, cn * in_feats * es,
+                                   cudaMemcpyHostToDevice, si));
+    }
+    if (nslices > 1) {
+      KSMM_CUDA_OK(cudaEventRecord(g_host.ev_in[sl], si));
+      KSMM_CUDA_OK(cudaStreamWaitEvent(sc, g_host.ev_in[sl], 0));
+      // the output buffer is free once slice k - 2 has left it
+      if (k >= 2) KSMM_CUDA_OK(cudaStreamWaitEvent(sc, g_host.ev_out[sl], 0));
+    }
+    st = ksmm_cu_chain_forward(din, dvals.data(), dout, dbias, g_host.buf[3], g_host.cap[3], cn,
+                               nfactors, patterns, dtype, bs_last, sc);
+    if (st != KSMM_OK) {
+      cudaDeviceSynchronize();
+      return st;
+    }
+    if (nslices > 1) {
+      KSMM_CUDA_OK(cudaEventRecord(g_host.ev_cmp[sl], sc));
+      KSMM_CUDA_OK(cudaStreamWaitEvent(so, g_host.ev_cmp[sl], 0));
+    }
+    if (bs_last) {
+      KSMM_CUDA_OK(cudaMemcpy2DAsync(hout + n0 * es, batch * es, dout, cn * es, cn * es, out_feats,
+                                     cudaMemcpyDeviceToHost, so));
+    } else {
+      KSMM_CUDA_OK(cudaMemcpyAsync(hout + n0 * out_feats * es, dout, cn * out_feats * es,
+                                   cudaMemcpyDeviceToHost, so));
+    }
+    if (nslices > 1) KSMM_CUDA_OK(cudaEventRecord(g_host.ev_out[sl], so));
+  }
+  KSMM_CUDA_OK(cudaStreamSynchronize(so));
+  if (nslices > 1) {
+    KSMM_CUDA_OK(cudaStreamSynchronize(sc));
+    KSMM_CUDA_OK(cudaStreamSynchronize(si));
+  }
   return KSMM_OK;
 }
 

@@ -457,8 +457,8 @@ def test_chain_forward_host_buffers():
     pats = [(2, 8, 4, 2), (4, 6, 4, 2)]
     rng = np.random.RandomState(21)
     ws = make_weights(pats, rng)
-    for bs_last in (1, 0):
-        batch = 50
+    # 50: one slice; 8500: four slices through the copy / compute / copy pipeline, ragged last slice
+    for bs_last, batch in ((1, 50), (0, 50), (1, 8500), (0, 8500)):
         x = rng.standard_normal((16, batch) if bs_last else (batch, 16)).astype(np.float32)
         bias = rng.standard_normal(48).astype(np.float32)
         wk = [ko.abcd_to_kernel_format(w) for w in ws]
