@@ -70,6 +70,14 @@ typedef enum {
 } ksmm_algo_t;
 
 /* Full description of one factor multiplication. */
+/* Element-wise function fused into the epilogue (the reference has none: its
+ * callers apply activations as separate PyTorch kernels). */
+typedef enum {
+  KSMM_ACT_NONE = 0,
+  KSMM_ACT_GELU = 1,   /* 0.5 x (1 + erf(x / sqrt 2)), torch.nn.functional.gelu's default */
+  KSMM_ACT_RELU = 2
+} ksmm_activation_t;
+
 typedef struct {
   const void* input;
   const void* values;     /* kernel-format weights, (a*d*c, b) row-major       */
@@ -82,7 +90,8 @@ typedef struct {
   int32_t bs_last;        /* 1 = batch-last, 0 = batch-first                   */
   int32_t algo;           /* ksmm_algo_t                                       */
   int32_t config;         /* tile configuration index inside the family, -1 = auto */
-  float alpha;            /* output = alpha * (K x) + bias; fp8: s_x * s_w     */
+  float alpha;            /* output = act(alpha * (K x) + bias); fp8: s_x * s_w */
+  int32_t activation;     /* ksmm_activation_t applied last in the epilogue    */
 } ksmm_forward_desc_t;
 
 /* Library version: major*10000 + minor*100 + patch. */
@@ -129,6 +138,13 @@ KSMM_API int ksmm_cu_chain_forward(const void* input, const void* const* values,
                           const void* bias, void* workspace, size_t workspace_bytes,
                           int64_t batch, int nfactors, const int32_t* patterns,
                           int dtype, int bs_last, void* stream);
+/* Same call with an element-wise activation (ksmm_activation_t) applied after the bias in the
+ * last factor's epilogue; no reference counterpart (the reference's callers run the activation
+ * as a separate PyTorch kernel). */
+KSMM_API int ksmm_cu_chain_forward_act(const void* input, const void* const* values, void* output,
+                              const void* bias, void* workspace, size_t workspace_bytes,
+                              int64_t batch, int nfactors, const int32_t* patterns,
+                              int dtype, int bs_last, int activation, void* stream);
 
 /*
  * ksmm_cu_chain_forward without any allocation: the intermediate activations

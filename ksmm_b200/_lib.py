@@ -23,11 +23,13 @@ KSMM_ERR_NO_DEVICE = 6
 
 KSMM_F32, KSMM_F16, KSMM_BF16, KSMM_F8E4M3 = 0, 1, 2, 3
 KSMM_ALGO_AUTO, KSMM_ALGO_SIMT, KSMM_ALGO_TC = 0, 1, 2
+KSMM_ACT_NONE, KSMM_ACT_GELU, KSMM_ACT_RELU = 0, 1, 2
+ACTIVATIONS = {None: KSMM_ACT_NONE, "none": KSMM_ACT_NONE, "gelu": KSMM_ACT_GELU, "relu": KSMM_ACT_RELU}
 STATIC_SCRATCH_BYTES = 40 * 1024 * 1024  # KSMM_CU_STATIC_SCRATCH_BYTES
 
 EXPORTS = (
     "ksmm_cu_version", "ksmm_cu_last_error", "ksmm_cu_status_string", "ksmm_cu_forward",
-    "ksmm_cu_forward_ex", "ksmm_cu_chain_workspace_bytes", "ksmm_cu_chain_forward",
+    "ksmm_cu_forward_ex", "ksmm_cu_chain_workspace_bytes", "ksmm_cu_chain_forward", "ksmm_cu_chain_forward_act",
     "ksmm_cu_chain_forward_static", "ksmm_cu_chain_forward_host", "ksmm_cu_num_configs", "ksmm_cu_config_supported",
     "ksmm_cu_tune", "ksmm_cu_set_choice", "ksmm_cu_get_choice", "ksmm_cu_default_choice",
     "ksmm_cu_check_device",
@@ -43,6 +45,7 @@ class ForwardDesc(ctypes.Structure):
         ("a", ctypes.c_int32), ("b", ctypes.c_int32), ("c", ctypes.c_int32), ("d", ctypes.c_int32),
         ("in_dtype", ctypes.c_int32), ("out_dtype", ctypes.c_int32), ("bs_last", ctypes.c_int32),
         ("algo", ctypes.c_int32), ("config", ctypes.c_int32), ("alpha", ctypes.c_float),
+        ("activation", ctypes.c_int32),
     ]
 
 
@@ -79,6 +82,9 @@ def load():
     lib.ksmm_cu_chain_forward.restype = i32
     lib.ksmm_cu_chain_forward.argtypes = [vp, ctypes.POINTER(vp), vp, vp, vp, ctypes.c_size_t, i64,
                                           i32, ctypes.POINTER(ctypes.c_int32), i32, i32, vp]
+    lib.ksmm_cu_chain_forward_act.restype = i32
+    lib.ksmm_cu_chain_forward_act.argtypes = [vp, ctypes.POINTER(vp), vp, vp, vp, ctypes.c_size_t, i64,
+                                              i32, ctypes.POINTER(ctypes.c_int32), i32, i32, i32, vp]
     lib.ksmm_cu_chain_forward_static.restype = i32
     lib.ksmm_cu_chain_forward_static.argtypes = [vp, ctypes.POINTER(vp), vp, vp, i64, i32,
                                                  ctypes.POINTER(ctypes.c_int32), i32, i32, vp]

@@ -140,7 +140,27 @@ struct Problem {
   // in_regrouped: the input already has that order for this factor's own (c, d).
   int out_regroup_d = 0, out_regroup_c = 0;
   int in_regrouped = 0;
+  int activation = 0;  // ksmm_activation_t, applied after alpha and bias
 };
+
+// element-wise epilogue function (ksmm_activation_t)
+// erf by the rational approximation 7.1.26 of Abramowitz and Stegun (absolute error below
+// 1.5e-7, i.e. fp32 rounding level for a GELU): one reciprocal, one exponential, six FMAs.
+__device__ __forceinline__ float fast_erf(float x) {
+  const float ax = fabsf(x);
+  const float t = __frcp_rn(fmaf(0.3275911f, ax, 1.f));
+  float p = fmaf(1.061405429f, t, -1.453152027f);
+  p = fmaf(p, t, 1.421413741f);
+  p = fmaf(p, t, -0.284496736f);
+  p = fmaf(p, t, 0.254829592f);
+  const float r = 1.f - p * t * __expf(-ax * ax);
+  return copysignf(r, x);
+}
+__device__ __forceinline__ float apply_activation(float v, int act) {
+  if (act == 1) return 0.5f * v * (1.f + fast_erf(v * 0.70710678118654752f));
+  if (act == 2) return fmaxf(v, 0.f);
+  return v;
+}
 
 // host-side error plumbing (defined in ksmm_cu.cu)
 int set_error(int status, const char* fmt, ...);

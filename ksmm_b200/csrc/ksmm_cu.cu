@@ -56,7 +56,7 @@ int launch_transpose(const void* in, void* out, int64_t rows, int64_t cols, int 
                      cudaStream_t stream);
 static constexpr int kFfmaTmaWide = 6, kFfmaTmaNarrow = 7, kFfmaTmaFirst = 8, kNumFfmaConfigs = 9;
 
-static int simt_launch(const Problem& p, int config, cudaStream_t stream) {
+static int simt_launch_raw(const Problem& p, int config, cudaStream_t stream) {
   if (config < 0) {
     if (ffma_tma_supported(p, true) && p.b >= 48)
       config = kFfmaTmaNarrow;  // 64 x 128 tiles, four CTAs per SM: fastest in every measured case
@@ -109,6 +109,34 @@ struct Choice {
 static std::mutex g_choice_mu;
 static std::map<ChoiceKey, Choice> g_choices;
 
+// The FFMA family has no activation in its epilogues: an element-wise pass over the output
+// follows the kernel (the tensor-core kernels apply it in their epilogue).
+template <typename T>
+__global__ void __launch_bounds__(256) activation_kernel(T* data, int64_t n, int act) {
+  for (int64_t q = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; q < n;
+       q += static_cast<int64_t>(gridDim.x) * 256)
+    data[q] = ElemTraits<T>::from_float(apply_activation(ElemTraits<T>::to_float(data[q]), act));
+}
+
+static int simt_launch(const Problem& p, int config, cudaStream_t stream) {
+  int st = simt_launch_raw(p, config, stream);
+  if (st != KSMM_OK || p.activation == 0) return st;
+  const int64_t n = static_cast<int64_t>(p.a) * p.b * p.d * p.batch;
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>((n + 255) / 256, 148 * 16));
+  if (p.out_dtype == KSMM_F32)
+    activation_kernel<float><<<grid, 256, 0, stream>>>(static_cast<float*>(p.out), n, p.activation);
+  else if (p.out_dtype == KSMM_F16)
+    activation_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<__half*>(p.out), n, p.activation);
+  else
+    activation_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(p.out), n,
+                                                               p.activation);
+  count_launch();
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess)
+    return set_error(KSMM_ERR_CUDA, "activation kernel launch failed: %s", cudaGetErrorString(err));
+  return KSMM_OK;
+}
+
 static ChoiceKey key_of(const Problem& p) {
   return ChoiceKey(p.batch, p.a, p.b, p.c, p.d, p.in_dtype, p.out_dtype, p.bs_last);
 }
@@ -136,6 +164,8 @@ static int check_problem(const Problem& p) {
     return set_error(KSMM_ERR_BAD_ARGUMENT, "unsupported output dtype %d", p.out_dtype);
   if (p.bs_last != 0 && p.bs_last != 1)
     return set_error(KSMM_ERR_BAD_ARGUMENT, "bs_last must be 0 or 1");
+  if (p.activation < 0 || p.activation > 2)
+    return set_error(KSMM_ERR_BAD_ARGUMENT, "unknown activation %d", p.activation);
   return KSMM_OK;
 }
 
@@ -263,6 +293,7 @@ static Problem problem_of(const ksmm_forward_desc_t& dsc) {
   p.out_dtype = dsc.out_dtype;
   p.bs_last = dsc.bs_last;
   p.alpha = dsc.alpha;
+  p.activation = dsc.activation;
   return p;
 }
 
@@ -411,6 +442,16 @@ int ksmm_cu_chain_forward(const void* input, const void* const* values, void* ou
                           const void* bias, void* workspace, size_t workspace_bytes,
                           int64_t batch, int nfactors, const int32_t* patterns, int dtype,
                           int bs_last, void* stream) {
+  return ksmm_cu_chain_forward_act(input, values, output, bias, workspace, workspace_bytes, batch,
+                                   nfactors, patterns, dtype, bs_last, KSMM_ACT_NONE, stream);
+}
+
+int ksmm_cu_chain_forward_act(const void* input, const void* const* values, void* output,
+                              const void* bias, void* workspace, size_t workspace_bytes,
+                              int64_t batch, int nfactors, const int32_t* patterns, int dtype,
+                              int bs_last, int activation, void* stream) {
+  if (activation < 0 || activation > 2)
+    return set_error(KSMM_ERR_BAD_ARGUMENT, "unknown activation %d", activation);
   if (nfactors <= 0 || !patterns || !values)
     return set_error(KSMM_ERR_BAD_ARGUMENT, "chain needs at least one factor");
   if (dtype == KSMM_F8E4M3)
@@ -439,6 +480,7 @@ int ksmm_cu_chain_forward(const void* input, const void* const* values, void* ou
     p.in = cur; p.w = values[f]; p.out = dst; p.bias = last ? bias : nullptr;
     p.batch = batch; p.a = q[0]; p.b = q[1]; p.c = q[2]; p.d = q[3];
     p.in_dtype = dtype; p.out_dtype = dtype; p.bs_last = bs_last; p.alpha = 1.f;
+    p.activation = last ? activation : 0;
     // Layout fusion of consecutive batch-first factors: when the next factor has d = 2 or 4 and
     // this one can store its output regrouped by the next factor's blocks, the intermediate is
     // written in that order and the next factor runs the kernel without the transposer stage

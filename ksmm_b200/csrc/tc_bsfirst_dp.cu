@@ -46,6 +46,7 @@ struct ParamsP {
   float alpha;
   const void* bias;
   int out_dtype;
+  int act;  // ksmm_activation_t
   int* status;
 };
 
@@ -197,7 +198,7 @@ __global__ void __launch_bounds__(kThreadsP, 1)
     const int q = warp & 3;
     const int grp = ew >> 2;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
-    const bool plain = (P.alpha == 1.f) && (P.bias == nullptr);
+    const bool plain = (P.alpha == 1.f) && (P.bias == nullptr) && (P.act == 0);
     const uint32_t stg = stg0 + ew * C::STG_WARP_BYTES;
     constexpr int JB = 64 / D;  // j values in one 64-element output box
     uint32_t ut = 0, sti = 0;
@@ -251,7 +252,7 @@ __global__ void __launch_bounds__(kThreadsP, 1)
               if (P.bias != nullptr && j0 + jj0 + jj < P.b)
                 bv = bias_at(P.bias, (static_cast<int64_t>(i) * P.b + j0 + jj0 + jj) * D + l,
                              P.out_dtype);
-              r[l][jj] = __float_as_uint(fmaf(P.alpha, __uint_as_float(r[l][jj]), bv));
+              r[l][jj] = __float_as_uint(apply_activation(fmaf(P.alpha, __uint_as_float(r[l][jj]), bv), P.act));
             }
         }
         // the staging tile about to be written must have been read by its last store
@@ -356,6 +357,7 @@ static int launch_p(const Problem& p, const void* regrouped, cudaStream_t stream
   P.alpha = p.alpha;
   P.bias = p.bias;
   P.out_dtype = p.out_dtype;
+  P.act = p.activation;
   P.status = status_word();
   if (!P.status) return set_error(KSMM_ERR_CUDA, "cannot resolve the device status word");
   const uint32_t fmt = p.in_dtype == KSMM_BF16 ? 1u : 0u;

@@ -69,6 +69,7 @@ struct ParamsF {
   float alpha;
   const float* bias;
   float* out;  // batch-last: the epilogue stores straight from registers
+  int act;     // ksmm_activation_t
   int* status;
 };
 
@@ -298,7 +299,7 @@ __global__ void __launch_bounds__(kThreadsF, 1)
     const int q = warp & 3;
     const int grp = ew >> 2;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
-    const bool plain = (P.alpha == 1.f) && (P.bias == nullptr);
+    const bool plain = (P.alpha == 1.f) && (P.bias == nullptr) && (P.act == 0);
     const uint32_t stg = stg0 + ew * C::STG_WARP_BYTES;
     uint32_t ut = 0;
     for (uint32_t row = row_begin; row < row_end; ++row, ++ut) {
@@ -343,7 +344,7 @@ __global__ void __launch_bounds__(kThreadsF, 1)
                                         : static_cast<int64_t>(blk) * P.b + j;
               bv = P.bias[f];
             }
-            r[jj] = __float_as_uint(fmaf(P.alpha, __uint_as_float(r[jj]), bv));
+            r[jj] = __float_as_uint(apply_activation(fmaf(P.alpha, __uint_as_float(r[jj]), bv), P.act));
           }
         }
         if constexpr (C::DIRECT) {
@@ -472,6 +473,7 @@ static int launch_f(const Problem& p, cudaStream_t stream) {
   P.alpha = p.alpha;
   P.bias = static_cast<const float*>(p.bias);
   P.out = static_cast<float*>(p.out);
+  P.act = p.activation;
   P.status = status_word();
   if (!P.status) return set_error(KSMM_ERR_CUDA, "cannot resolve the device status word");
   // fp32 accumulate, tf32 operands, weights MN-major, batch-last input MN-major, M = 128

@@ -66,6 +66,7 @@ struct Params {
   const void* bias;
   int out_dtype;
   int* status;
+  int act;         // ksmm_activation_t
   int rg_d, rg_c;  // batch-first, 16-bit: store regrouped for the next factor's (c, d); 0 = natural order
 };
 
@@ -277,7 +278,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int q = warp & 3;
     const int grp = ew >> 2;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
-    const bool plain = (P.alpha == 1.f) && (P.bias == nullptr);
+    const bool plain = (P.alpha == 1.f) && (P.bias == nullptr) && (P.act == 0);
     const uint32_t stg = stg0 + ew * C::STG_WARP_BYTES;
     uint32_t ut = 0;
     KSMM_TRACE_DECL;
@@ -327,7 +328,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                          ? bias_at(P.bias, static_cast<int64_t>(i) * P.b + j0 + col, P.out_dtype)
                          : 0.f;
               }
-              r[e] = __float_as_uint(fmaf(P.alpha, __uint_as_float(r[e]), bv));
+              r[e] = __float_as_uint(apply_activation(fmaf(P.alpha, __uint_as_float(r[e]), bv), P.act));
             }
           }
           const uint32_t rowaddr = stg + lane * 128;
@@ -534,6 +535,7 @@ static int launch_one(const Problem& p, cudaStream_t stream) {
   P.alpha = p.alpha;
   P.bias = p.bias;
   P.out_dtype = p.out_dtype;
+  P.act = p.activation;
   P.rg_d = (!BS_LAST && OS == 2) ? p.out_regroup_d : 0;
   P.rg_c = p.out_regroup_c;
   P.status = status_word();

@@ -60,8 +60,13 @@ class KSLinear(nn.Module):
 
     def __init__(self, patterns, weights=None, bias=True, algo="kernel",
                  dtype: torch.dtype = torch.float16, bs_last: bool = False, vsize: int = 4,
-                 device: str = "cuda", fuse_chain: bool = True):
+                 device: str = "cuda", fuse_chain: bool = True, activation=None):
         super().__init__()
+        # `activation` (None, "gelu", "relu") is an addition to the reference's signature: it is applied
+        # after the bias inside the last factor's epilogue instead of as a separate kernel
+        if activation not in (None, "gelu", "relu"):
+            raise ValueError(f"activation={activation!r}: expected None, 'gelu' or 'relu'")
+        self.activation = activation
         if algo != "kernel":
             raise NotImplementedError(
                 f"algo={algo!r}: this library implements the reference's algo='kernel' only")
@@ -123,15 +128,20 @@ class KSLinear(nn.Module):
                 last = idx + 1 == self.num_mat
                 y = _k.forward_fp8(xq, wq, self.bs_last, *p, sx, sw, out_dtype=torch.bfloat16,
                                    bias=bias if last else None)
+            if self.activation == "gelu":
+                y = torch.nn.functional.gelu(y)
+            elif self.activation == "relu":
+                y = torch.relu(y)
             return y
         if self.fuse_chain or self.num_mat == 1:
             ws = self._ensure_workspace(x) if self.num_mat > 1 else None
             return _k.chain_forward(x, list(self.factors), self.patterns, self.bs_last, bias=bias,
-                                    workspace=ws)
+                                    workspace=ws, activation=self.activation)
         y = x
         for idx, (p, f) in enumerate(zip(self.patterns, self.factors)):
             last = idx + 1 == self.num_mat
-            y = _k.forward_ex(y, f, self.bs_last, *p, bias=bias if last else None)
+            y = _k.forward_ex(y, f, self.bs_last, *p, bias=bias if last else None,
+                              activation=self.activation if last else None)
         return y
 
     def _ensure_workspace(self, x):

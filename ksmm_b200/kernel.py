@@ -74,7 +74,7 @@ def _check_inputs(input, factor, bs_last, a, b, c, d):
 
 
 def forward_ex(input, factor, bs_last, a, b, c, d, *, out_dtype=None, alpha=1.0, bias=None,
-               algo=_lib.KSMM_ALGO_AUTO, config=-1, out=None):
+               algo=_lib.KSMM_ALGO_AUTO, config=-1, out=None, activation=None):
     """One factor with every option of ``ksmm_cu_forward_ex``."""
     lib = _lib.load()
     bs_last = int(bool(bs_last))
@@ -95,7 +95,7 @@ def forward_ex(input, factor, bs_last, a, b, c, d, *, out_dtype=None, alpha=1.0,
         input=input.data_ptr(), values=factor.data_ptr(), output=out.data_ptr(),
         bias=bias.data_ptr() if bias is not None else None, batch=batch, a=a, b=b, c=c, d=d,
         in_dtype=dtype_code(input.dtype), out_dtype=dtype_code(out_dtype), bs_last=bs_last,
-        algo=algo, config=config, alpha=float(alpha))
+        algo=algo, config=config, alpha=float(alpha), activation=_lib.ACTIVATIONS[activation])
     with torch.cuda.device(input.device):
         _lib.check(lib.ksmm_cu_forward_ex(ctypes.byref(desc), _stream_ptr(input.device)))
     return out
@@ -110,7 +110,7 @@ def default_choice(pattern, batch, dtype, bs_last, out_dtype=None):
     out_dtype = dtype if out_dtype is None else out_dtype
     desc = ForwardDesc(input=256, values=256, output=256, bias=None, batch=int(batch), a=a, b=b, c=c,
                        d=d, in_dtype=dtype_code(dtype), out_dtype=dtype_code(out_dtype),
-                       bs_last=int(bool(bs_last)), algo=0, config=-1, alpha=1.0)
+                       bs_last=int(bool(bs_last)), algo=0, config=-1, alpha=1.0, activation=0)
     algo, cfg, conv = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
     _lib.check(lib.ksmm_cu_default_choice(ctypes.byref(desc), ctypes.byref(algo), ctypes.byref(cfg),
                                           ctypes.byref(conv)))
@@ -135,12 +135,13 @@ def forward(input, factor, bs_last, a, b, c, d, dtype, vsize=4):
     return Kernel.forward(input, factor, bool(bs_last), a, b, c, d, dtype, vsize)
 
 
-def chain_forward(input, factors, patterns, bs_last, bias=None, workspace=None, out=None):
-    """All factors of one KSLinear in one library call (``ksmm_cu_chain_forward``).
+def chain_forward(input, factors, patterns, bs_last, bias=None, workspace=None, out=None,
+                  activation=None):
+    """All factors of one KSLinear in one library call (``ksmm_cu_chain_forward_act``).
 
     ``factors[f]`` is the kernel-format (a*d*c, b) weight of ``patterns[f]``;
     ``patterns[0]`` is applied first.  ``bias`` (out features, output dtype)
-    is fused into the last factor.
+    and ``activation`` (None, "gelu" or "relu") are fused into the last factor.
     """
     lib = _lib.load()
     bs_last = int(bool(bs_last))
@@ -170,11 +171,11 @@ def chain_forward(input, factors, patterns, bs_last, bias=None, workspace=None, 
         raise ValueError("bias must hold out_size elements of the input dtype")
     vals = (ctypes.c_void_p * nf)(*[w.data_ptr() for w in factors])
     with torch.cuda.device(input.device):
-        _lib.check(lib.ksmm_cu_chain_forward(
+        _lib.check(lib.ksmm_cu_chain_forward_act(
             input.data_ptr(), vals, out.data_ptr(), bias.data_ptr() if bias is not None else None,
             workspace.data_ptr() if workspace is not None else None,
             workspace.numel() * workspace.element_size() if workspace is not None else 0,
-            batch, nf, pat, code, bs_last, _stream_ptr(input.device)))
+            batch, nf, pat, code, bs_last, _lib.ACTIVATIONS[activation], _stream_ptr(input.device)))
     return out
 
 

@@ -35,20 +35,29 @@ def posemb_sincos_2d(h, w, dim, temperature=10000.0):
 
 
 class KSFeedForward(nn.Module):
-    def __init__(self, dim, dtype, device, dense=False):
+    def __init__(self, dim, dtype, device, dense=False, fuse_gelu=False):
         super().__init__()
         self.norm = nn.LayerNorm(dim)
+        self.dense = dense
+        self.fuse_gelu = fuse_gelu and not dense
         if dense:  # same shapes with nn.Linear, for an accuracy / speed comparison
             self.fc1 = nn.Linear(dim, 4 * dim)
             self.fc2 = nn.Linear(4 * dim, dim)
         else:
+            # fuse_gelu: the GELU runs in the epilogue of fc1's last factor instead of as a separate
+            # PyTorch kernel (model/vit.py:416-431).  Off by default: that factor is (1,768,192,4), whose
+            # four accumulators fill TMEM, so its epilogue cannot overlap the MMAs and the erf
+            # arithmetic (measured) costs more there than the separate element-wise kernel.
             self.fc1 = KSLinear(FC1_PATTERNS, bias=True, algo="kernel", dtype=dtype, bs_last=False,
-                                device=device)
+                                device=device, activation="gelu" if self.fuse_gelu else None)
             self.fc2 = KSLinear(FC2_PATTERNS, bias=True, algo="kernel", dtype=dtype, bs_last=False,
                                 device=device)
 
     def forward(self, x):
-        return self.fc2(F.gelu(self.fc1(self.norm(x))))
+        h = self.fc1(self.norm(x))
+        if not self.fuse_gelu:
+            h = F.gelu(h)
+        return self.fc2(h)
 
 
 class Attention(nn.Module):
@@ -68,14 +77,14 @@ class Attention(nn.Module):
 
 class KSViTB(nn.Module):
     def __init__(self, dtype=torch.float16, device="cuda", depth=12, dim=768, num_classes=1000,
-                 dense_mlp=False):
+                 dense_mlp=False, fuse_gelu=False):
         super().__init__()
         self.patch = 16
         patch_dim = 3 * 16 * 16
         self.embed = nn.Sequential(nn.LayerNorm(patch_dim), nn.Linear(patch_dim, dim), nn.LayerNorm(dim))
         self.register_buffer("pos", posemb_sincos_2d(14, 14, dim), persistent=False)
         self.layers = nn.ModuleList(
-            [nn.ModuleList([Attention(dim), KSFeedForward(dim, dtype, device, dense_mlp)])
+            [nn.ModuleList([Attention(dim), KSFeedForward(dim, dtype, device, dense_mlp, fuse_gelu)])
              for _ in range(depth)])
         self.norm = nn.LayerNorm(dim)
         self.head = nn.Linear(dim, num_classes)

@@ -452,6 +452,48 @@ def test_chain_layout_fusion_batch_first(dtype):
     kb.check_device()
 
 
+def _act_ref(y, act):
+    if act == "gelu":
+        erf = np.vectorize(math.erf)
+        return 0.5 * y * (1.0 + erf(y / math.sqrt(2.0)))
+    return np.maximum(y, 0.0)
+
+
+@pytest.mark.parametrize("act", ["gelu", "relu"])
+def test_activation_in_the_epilogue(act):
+    """act(alpha * K x + bias) on every kernel path: tensor kernels apply it in their epilogue, the
+    FFMA family through an element-wise pass after the kernel."""
+    cases = [((2, 96, 48, 1), torch.float16, True, _lib.KSMM_ALGO_TC), ((2, 96, 48, 1), torch.float16, False, _lib.KSMM_ALGO_TC),
+             ((1, 128, 32, 4), torch.bfloat16, False, _lib.KSMM_ALGO_TC),       # interleaved batch-first kernel
+             ((2, 96, 48, 1), torch.float32, True, _lib.KSMM_ALGO_TC), ((2, 96, 48, 1), torch.float32, False, _lib.KSMM_ALGO_TC),
+             ((2, 72, 48, 2), torch.float32, True, _lib.KSMM_ALGO_SIMT), ((2, 72, 48, 2), torch.float16, False, _lib.KSMM_ALGO_SIMT),
+             ((1, 64, 64, 16), torch.float16, False, _lib.KSMM_ALGO_AUTO)]    # layout-conversion path
+    for ci, (pattern, dtype, bs_last, algo) in enumerate(cases):
+        batch = 96
+        x, w = _inputs(pattern, batch, dtype, bs_last, seed=800 + ci)
+        rng = np.random.RandomState(810 + ci)
+        a, b, c, d = pattern
+        bias = torch.from_numpy(rng.standard_normal(a * b * d).astype(np.float32)).to(dtype)
+        y = _run(x, w, pattern, bs_last, algo=algo, bias=bias.to(DEV), alpha=0.5, activation=act)
+        ref = 0.5 * _oracle(x, w, bs_last)
+        bf = bias.float().numpy()
+        ref = _act_ref(ref + (bf[:, None] if bs_last else bf[None, :]), act)
+        tol = 1e-5 if dtype == torch.float32 else 1e-2
+        assert ko.rel_fro_error(y, ref) < tol, (pattern, dtype, bs_last, algo, act)
+    # a chain: the activation follows the last factor only
+    pats = [(4, 192, 192, 1), (1, 768, 192, 4)]
+    rng = np.random.RandomState(820)
+    ws = make_weights(pats, rng)
+    x = torch.from_numpy(rng.standard_normal((136, 768)).astype(np.float32)).half()
+    wt = [torch.from_numpy(v).half() for v in ws]
+    layer = kb.KSLinear(pats, weights=wt, bias=False, algo="kernel", dtype=torch.float16, bs_last=False,
+                        device=DEV, activation=act)
+    y = layer(x.to(DEV)).float().cpu().numpy()
+    ref = _act_ref(ko.chain_apply(x.float().numpy(), [v.float().numpy() for v in wt], False), act)
+    assert ko.rel_fro_error(y, ref) < 1e-2
+    kb.check_device()
+
+
 def test_chain_forward_host_buffers():
     lib = _lib.load()
     pats = [(2, 8, 4, 2), (4, 6, 4, 2)]
