@@ -244,16 +244,40 @@ __global__ void __launch_bounds__(kThreadsP, 1)
           released = true;
         }
         if (!plain) {
-#pragma unroll
-          for (int l = 0; l < D; ++l)
-#pragma unroll
-            for (int jj = 0; jj < JB; ++jj) {
-              float bv = 0.f;
-              if (P.bias != nullptr && j0 + jj0 + jj < P.b)
-                bv = bias_at(P.bias, (static_cast<int64_t>(i) * P.b + j0 + jj0 + jj) * D + l,
-                             P.out_dtype);
-              r[l][jj] = __float_as_uint(apply_activation(fmaf(P.alpha, __uint_as_float(r[l][jj]), bv), P.act));
+          // bias of the 64 output elements (jj, l) of this tile: one coalesced 4-byte load per lane
+          // (elements 2 lane and 2 lane + 1), then broadcast by shuffle
+          uint32_t bpair = 0;
+          if (P.bias != nullptr) {
+            const int64_t e0 = (static_cast<int64_t>(i) * P.b + j0 + jj0) * D + 2 * lane;
+            if (j0 + jj0 + (2 * lane) / D < P.b) {
+              const uint16_t* bp = static_cast<const uint16_t*>(P.bias) + e0;
+              bpair = (reinterpret_cast<uintptr_t>(bp) & 3) == 0
+                          ? *reinterpret_cast<const uint32_t*>(bp)
+                          : (static_cast<uint32_t>(bp[0]) | (static_cast<uint32_t>(bp[1]) << 16));
             }
+          }
+#pragma unroll
+          for (int jj = 0; jj < JB; ++jj)
+#pragma unroll
+            for (int l = 0; l < D; ++l) {
+              const int e = jj * D + l;
+              const uint32_t pr = __shfl_sync(0xffffffffu, bpair, e >> 1);
+              const uint16_t hv = static_cast<uint16_t>((e & 1) ? (pr >> 16) : (pr & 0xffffu));
+              const float bv = P.out_dtype == KSMM_BF16 ? __uint_as_float(static_cast<uint32_t>(hv) << 16)
+                                                        : __half2float(__ushort_as_half(hv));
+              r[l][jj] = __float_as_uint(fmaf(P.alpha, __uint_as_float(r[l][jj]), bv));
+            }
+          if (P.act == KSMM_ACT_GELU) {
+#pragma unroll
+            for (int l = 0; l < D; ++l)
+#pragma unroll
+              for (int jj = 0; jj < JB; ++jj) r[l][jj] = __float_as_uint(apply_activation(__uint_as_float(r[l][jj]), 1));
+          } else if (P.act == KSMM_ACT_RELU) {
+#pragma unroll
+            for (int l = 0; l < D; ++l)
+#pragma unroll
+              for (int jj = 0; jj < JB; ++jj) r[l][jj] = __float_as_uint(fmaxf(__uint_as_float(r[l][jj]), 0.f));
+          }
         }
         // the staging tile about to be written must have been read by its last store
         if (lane == 0) bulk_wait_read<STGN - 1>();

@@ -334,17 +334,24 @@ __global__ void __launch_bounds__(kThreadsF, 1)
         for (int jj = 0; jj < 32; ++jj)
           r[jj] = __float_as_uint(__uint_as_float(r[jj]) + __uint_as_float(rs[jj]));
         if (!plain) {
+          // bias of this tile's 32 columns: lane t loads the one of column jj0 + t, shuffles broadcast
+          float bl = 0.f;
+          if (P.bias != nullptr && j0 + jj0 + lane < P.b) {
+            const int j = j0 + jj0 + lane;
+            // output feature: batch-last (i*b + j)*d + l with blk = i*d + l; batch-first i*b + j
+            const int64_t f = BS_LAST ? (static_cast<int64_t>(blk / P.d) * P.b + j) * P.d + blk % P.d
+                                      : static_cast<int64_t>(blk) * P.b + j;
+            bl = P.bias[f];
+          }
 #pragma unroll
-          for (int jj = 0; jj < 32; ++jj) {
-            float bv = 0.f;
-            const int j = j0 + jj0 + jj;
-            if (P.bias != nullptr && j < P.b) {
-              // output feature: batch-last (i*b + j)*d + l with blk = i*d + l; batch-first i*b + j
-              const int64_t f = BS_LAST ? (static_cast<int64_t>(blk / P.d) * P.b + j) * P.d + blk % P.d
-                                        : static_cast<int64_t>(blk) * P.b + j;
-              bv = P.bias[f];
-            }
-            r[jj] = __float_as_uint(apply_activation(fmaf(P.alpha, __uint_as_float(r[jj]), bv), P.act));
+          for (int jj = 0; jj < 32; ++jj)
+            r[jj] = __float_as_uint(fmaf(P.alpha, __uint_as_float(r[jj]), __shfl_sync(0xffffffffu, bl, jj)));
+          if (P.act == KSMM_ACT_GELU) {
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) r[jj] = __float_as_uint(apply_activation(__uint_as_float(r[jj]), 1));
+          } else if (P.act == KSMM_ACT_RELU) {
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) r[jj] = __float_as_uint(fmaxf(__uint_as_float(r[jj]), 0.f));
           }
         }
         if constexpr (C::DIRECT) {

@@ -319,16 +319,46 @@ __global__ void __launch_bounds__(kThreads, 1)
           tmem_ld_wait();
           if (tron) KSMM_TRACE(trole, 23);
           if (!plain) {
+            // batch-first: the bias of the tile's columns comes through one coalesced load per lane
+            // and shuffles (16-bit: columns 2 lane, 2 lane + 1; fp32: column lane);
+            // batch-last: one value per accumulator row
+            uint32_t braw = 0;
+            if (!BS_LAST && P.bias != nullptr) {
+              const int col = cbi * C::CB + (OS == 2 ? 2 * lane : lane);
+              if (col < col_limit) {
+                const int64_t e0 = static_cast<int64_t>(i) * P.b + j0 + col;
+                if constexpr (OS == 2) {
+                  // (col_limit is even for 16-bit outputs: b * 2 bytes is a multiple of 16)
+                  const uint16_t* bp = static_cast<const uint16_t*>(P.bias) + e0;
+                  braw = (reinterpret_cast<uintptr_t>(bp) & 3) == 0
+                             ? *reinterpret_cast<const uint32_t*>(bp)
+                             : (static_cast<uint32_t>(bp[0]) | (static_cast<uint32_t>(bp[1]) << 16));
+                } else {
+                  braw = static_cast<const uint32_t*>(P.bias)[e0];
+                }
+              }
+            }
 #pragma unroll
             for (int e = 0; e < C::CB; ++e) {
               float bv = bias_row;
-              if (!BS_LAST && P.bias != nullptr) {
-                const int col = cbi * C::CB + e;
-                bv = col < col_limit
-                         ? bias_at(P.bias, static_cast<int64_t>(i) * P.b + j0 + col, P.out_dtype)
-                         : 0.f;
+              if (!BS_LAST) {
+                if constexpr (OS == 2) {
+                  const uint32_t pr = __shfl_sync(0xffffffffu, braw, e >> 1);
+                  const uint16_t hv = static_cast<uint16_t>((e & 1) ? (pr >> 16) : (pr & 0xffffu));
+                  bv = P.out_dtype == KSMM_BF16 ? __uint_as_float(static_cast<uint32_t>(hv) << 16)
+                                                : __half2float(__ushort_as_half(hv));
+                } else {
+                  bv = __uint_as_float(__shfl_sync(0xffffffffu, braw, e));
+                }
               }
-              r[e] = __float_as_uint(apply_activation(fmaf(P.alpha, __uint_as_float(r[e]), bv), P.act));
+              r[e] = __float_as_uint(fmaf(P.alpha, __uint_as_float(r[e]), bv));
+            }
+            if (P.act == KSMM_ACT_GELU) {
+#pragma unroll
+              for (int e = 0; e < C::CB; ++e) r[e] = __float_as_uint(apply_activation(__uint_as_float(r[e]), 1));
+            } else if (P.act == KSMM_ACT_RELU) {
+#pragma unroll
+              for (int e = 0; e < C::CB; ++e) r[e] = __float_as_uint(fmaxf(__uint_as_float(r[e]), 0.f));
             }
           }
           const uint32_t rowaddr = stg + lane * 128;

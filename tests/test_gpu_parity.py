@@ -494,6 +494,23 @@ def test_activation_in_the_epilogue(act):
     kb.check_device()
 
 
+def test_standalone_driver_writes_the_reference_row(tmp_path):
+    """ksmm_cli: the stand-alone driver with the reference's sparse_mm flags times the library on one
+    pattern, checks 1 % of the batch on the CPU and appends `batch a b c d ... ms std mse`."""
+    import subprocess
+    exe = os.path.join(os.path.dirname(_lib.LIB_PATH), "ksmm_cli")
+    assert os.path.exists(exe), "ksmm_cli is built next to libksmm_cu.so by `make -C ksmm_b200/csrc`"
+    for kernel, pat in (("kernel_bs_last_float", "2,64,32,2"), ("kernel_bs_first_half", "1,128,64,4"),
+                        ("kernel_bs_last_bf16", "4,64,64,1")):
+        out = tmp_path / (kernel + ".out")
+        res = subprocess.run([exe, "-n", kernel, "-p", pat, "-b", "2048", "-r", "5", "-o", str(out)],
+                             capture_output=True, text=True, cwd=str(tmp_path), timeout=300)
+        assert res.returncode == 0, res.stdout + res.stderr
+        row = out.read_text().split()
+        assert row[:5] == ["2048"] + pat.split(",") and len(row) == 14
+        assert float(row[11]) > 0 and float(row[13]) < 1e-2
+
+
 def test_chain_forward_host_buffers():
     lib = _lib.load()
     pats = [(2, 8, 4, 2), (4, 6, 4, 2)]
