@@ -492,6 +492,50 @@ def run_ours(args, rank, world, local_rank):
                            "fc1=[(4,192,192,1),(1,768,192,4)], fc2=[(1,192,768,4),(4,192,192,1)], batch-first; "
                            "attention / LayerNorm / GELU are stock PyTorch; forward captured in a CUDA graph"}
 
+    # ---- fp8-e4m3 and bf16 factors (per-tensor scale, fp32 accumulate) --------------------------
+    lowp = None
+    if not args.no_vit and not args.only:
+        lowp = []
+        for pat in ((4, 192, 192, 1), (1, 768, 192, 4), (1, 192, 768, 4)):
+            for nb in (BATCH, 4096):
+                a_, b_, c_, d_ = pat
+                gen = torch.Generator(device=dev).manual_seed(5)
+                x32 = torch.randn((a_ * c_ * d_, nb), device=dev, generator=gen)
+                w32 = kb.generate_factor(a_, b_, c_, d_, "kernel", None, torch.float32, dev)
+                ref = kb.forward_ex(x32, w32, True, a_, b_, c_, d_, algo=_lib.KSMM_ALGO_SIMT).float()
+                xq, sx = kb.quantize_e4m3(x32)
+                wq, sw = kb.quantize_e4m3(w32)
+                xb, wb = x32.bfloat16(), w32.bfloat16()
+                yq = torch.empty((a_ * b_ * d_, nb), device=dev, dtype=torch.bfloat16)
+                yb = torch.empty_like(yq)
+
+                def t_of(fn):
+                    fn()
+                    torch.cuda.synchronize()
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g):
+                        for _ in range(20):
+                            fn()
+                    g.replay()
+                    torch.cuda.synchronize()
+                    t0_, t1_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    t0_.record()
+                    g.replay()
+                    t1_.record()
+                    torch.cuda.synchronize()
+                    del g
+                    return t0_.elapsed_time(t1_) / 20
+
+                ms8 = t_of(lambda: kb.forward_fp8(xq, wq, True, a_, b_, c_, d_, sx, sw, out=yq))
+                ms16 = t_of(lambda: kb.forward_ex(xb, wb, True, a_, b_, c_, d_, out=yb))
+                e8 = float((yq.float() - ref).norm() / ref.norm())
+                e16 = float((yb.float() - ref).norm() / ref.norm())
+                lowp.append({"pattern": list(pat), "batch": nb, "layout": "bs_last",
+                             "fp8_e4m3_ms": round(ms8, 5), "fp8_rel_err_vs_fp32": round(e8, 5),
+                             "bf16_ms": round(ms16, 5), "bf16_rel_err_vs_fp32": round(e16, 5)})
+                del x32, w32, ref, xq, wq, xb, wb, yq, yb
+        kb.check_device()
+
     # ---- chains: one chained call (layout-fused intermediates) against per-factor calls ------------
     chains = None
     if not args.no_vit and not args.only:
@@ -573,7 +617,7 @@ def run_ours(args, rank, world, local_rank):
         "roofline": roofline_of(per[dom], cs[dom]),
         "roofline_hbm": roofline_of(per[dom_hbm], cs[dom_hbm]) if dom_hbm is not None else None,
         "ffma_peak_tflops": round(ffma_peak, 2), "fp32_ffma_only": fp32_exact,
-        "cpu_baseline": cpu, "ksvit_b": ksvit, "chains": chains, "per_pattern": per,
+        "cpu_baseline": cpu, "ksvit_b": ksvit, "chains": chains, "fp8_bf16": lowp, "per_pattern": per,
     }
     print(json.dumps(line), flush=True)
 
