@@ -31,8 +31,6 @@
 // tensor-pipe work.
 #include <cuda.h>
 
-#include <cstdlib>
-
 #include "tc_host.h"
 #include "tc_kernel.h"
 #include "tc_ptx.cuh"

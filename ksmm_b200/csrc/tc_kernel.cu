@@ -2,12 +2,14 @@
 // fp8-e4m3 inputs with fp32 accumulation.
 //
 // One factor with pattern (a,b,c,d) is a*d independent (b x c) blocks, each
-// contracted with a (c x batch) slice of the input.  A work item is one input
-// tile of one block together with g of the 128 x NT output tiles computed from
-// it; when the whole input tile fits in shared memory it is fetched once per
-// item and only the weights stream.  A persistent CTA (one per SM) walks items
-// bid, bid + grid, ... so that the CTAs running at any moment work on
-// neighbouring tiles and share their operands in L2.
+// contracted with a (c x batch) slice of the input.  The output is cut into
+// tiles of 128 accumulator rows x NT columns.  A persistent CTA (one per SM) keeps
+// one j tile (CTA index modulo the number of j tiles) and walks a contiguous range
+// of rows (row = block x batch tile); CTAs that differ only in the j tile walk the
+// same rows at the same time and share the input tile in L2.  Two flavours per tile
+// configuration: weight-stationary (all k chunks of the CTA's weight tile stay in
+// shared memory, only the input streams through the ring) when the weight tile
+// fits, else streaming (a ring stage holds one k chunk of both operands).
 //
 //   batch-last : D[j (128 rows), n (NT cols)] = W_blk[j,k] * X_blk[k,n]
 //                A = weights tile, MN-major, straight from the reference's
@@ -21,12 +23,15 @@
 // In both layouts the contiguous dimension of the output is the TMEM column
 // dimension, so each epilogue thread owns a run of consecutive output
 // elements: it converts them, writes 16-byte chunks into a 128-byte-swizzled
-// staging tile, and one thread issues a TMA store of the tile.
+// staging tile, and one thread issues a TMA store of the tile.  The epilogue
+// applies alpha, the bias (one coalesced load per tile, broadcast by shuffles) and
+// an optional activation; in a chain it can store a batch-first 16-bit output
+// regrouped by the blocks of the next factor (see tc_bsfirst_dp.cu).
 //
 // Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM allocator and
 // single-thread MMA issuer, warps 2..9 = epilogue (TMEM lane quarter = warp
 // index mod 4; each warp converts and stores its own 32-row sub-tiles, so the
-// epilogue has no block-level barrier).  Input chunk slots and the weight ring
+// epilogue has no block-level barrier).  Ring stages and the resident weight tile
 // are guarded by full/empty mbarriers; the accumulator is double-buffered in
 // TMEM (2 x NT columns) so the epilogue of one tile overlaps the MMAs of the next.
 //
@@ -41,7 +46,6 @@
 // (src/ksmm_cu/src/template_kernels_fp8.cuh:22-370).
 #include <cuda.h>
 
-#include <cstdlib>
 #include <mutex>
 
 #include "tc_kernel.h"
