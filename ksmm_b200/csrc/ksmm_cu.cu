@@ -489,7 +489,10 @@ int ksmm_cu_chain_forward_act(const void* input, const void* const* values, void
     if (!last && !bs_last) {
       const int32_t* r = patterns + 4 * (f + 1);
       Problem nx = p;
-      nx.in = dst; nx.out = dst; nx.w = values[f + 1]; nx.bias = nullptr;
+      // the next factor reads this factor's destination and writes its own one
+      nx.in = dst;
+      nx.out = (f + 2 == nfactors) ? output : static_cast<char*>(workspace) + ((f + 1) & 1) * half;
+      nx.w = values[f + 1]; nx.bias = nullptr;
       nx.a = r[0]; nx.b = r[1]; nx.c = r[2]; nx.d = r[3];
       p.out_regroup_c = r[2];
       p.out_regroup_d = r[3];
