@@ -494,6 +494,37 @@ def test_activation_in_the_epilogue(act):
     kb.check_device()
 
 
+GRID = [16, 48, 64, 96, 128, 192, 384, 768]
+
+
+@pytest.mark.parametrize("bs_last", [True, False])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_synthetic_pattern_grid_through_the_default_dispatch(dtype, bs_last):
+    """The synthetic patterns of the benchmark specification: b, c in {16, ..., 768} with a and d chosen
+    so that a*c*d is 768 or 3072, both layouts, whatever kernel the default dispatch picks
+    (tensor-core kernels, layout conversion, FFMA kernels), at a batch that the tensor-core
+    kernels accept (96) and one that sends fp32 batch-last to the FFMA family (40)."""
+    rng = np.random.RandomState(900)
+    for c in GRID:
+        for b in GRID:
+            total = 3072 if (GRID.index(b) + GRID.index(c)) % 2 else 768
+            if total % c:
+                continue
+            rest = total // c                      # a * d
+            d = 4 if rest % 4 == 0 and (GRID.index(b) % 2 == 0) else (2 if rest % 2 == 0 and GRID.index(c) % 3 == 0 else 1)
+            a = rest // d
+            pattern = (a, b, c, d)
+            for batch in (96, 40):
+                shape = (a * c * d, batch) if bs_last else (batch, a * c * d)
+                x = torch.from_numpy(rng.standard_normal(shape).astype(np.float32)).to(dtype)
+                w = torch.from_numpy(make_weights([pattern], rng)[0]).to(dtype)
+                y = _run(x, w, pattern, bs_last)
+                assert not np.isnan(y).any(), (pattern, batch)
+                err = ko.rel_fro_error(y, _oracle(x, w, bs_last))
+                assert err < TOL[dtype], (pattern, batch, err)
+    kb.check_device()
+
+
 def test_standalone_driver_writes_the_reference_row(tmp_path):
     """ksmm_cli: the stand-alone driver with the reference's sparse_mm flags times the library on one
     pattern, checks 1 % of the batch on the CPU and appends `batch a b c d ... ms std mse`."""
