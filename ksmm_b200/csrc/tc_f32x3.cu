@@ -30,17 +30,38 @@
 // descriptor layout type 1 on the MMA side).  The batch-first input rows hold
 // consecutive k: K-major, plain 128-byte swizzle.  Two groups of four
 // "splitter" warps only add the lo tiles, element by element at the same
-// offsets (16-byte loads and stores).  One shared-memory stage holds
-// [X hi | X lo | W hi | W lo]; the lo weights follow the hi weights directly, so the
-// two together are one operand of 2 NJ rows.
+// offsets (16-byte loads and stores).  The lo weights follow the hi weights
+// directly, so the two together are one operand of 2 NJ rows.
+//
+// Three forms, chosen by the launcher:
+//  * j tile of 128 columns: both operands from shared memory, one stage holds
+//    [X hi | X lo | W hi | W lo].  The accumulators (2 buffers x 2 x 128 columns)
+//    fill the tensor memory.
+//  * j tile of 96 or 64 columns (TS): the input operand is read from tensor
+//    memory.  The input splitters read the raw tile (one accumulator row = one
+//    thread, through the swizzle) and write hi and lo with tcgen05.st into one of
+//    two operand buffers of 64 columns behind the accumulators; a stage is
+//    [X raw | W hi | W lo].  This removes the lo tile of the input and the tensor
+//    core's reads of the input operand from the shared-memory pipe, the unit
+//    that bounds the first form.
+//  * the same with resident weights (WR; batch-last, 96 columns, c <= 192): the
+//    hi and lo weights of the CTA's j tile stay in shared memory for all batch
+//    tiles of a block (loaded and split once per block, after the MMAs of the
+//    previous block have completed), a stage is the raw input tile alone, and
+//    the four weight warps join the epilogue as a third column group, so that
+//    each of the twelve warps stores 32 of the 96 columns.  On short blocks the
+//    epilogue's stores, not the main loop, set the time per tile.
 //
 // Warp roles (576 threads): warp 0 TMA producer, warp 1 TMEM owner and MMA
 // issuer, warps 2..5 input splitters, warps 6..9 weight splitters, warps
-// 10..17 epilogue (TMEM lane quarter = warp index mod 4).  Accumulator rows
+// 10..17 epilogue (TMEM lane quarter = warp index mod 4, which also fixes the
+// accumulator rows an input splitter can write).  Accumulator rows
 // are batch entries, columns are j.  A CTA keeps one j tile and walks a
 // contiguous range of (block, batch tile) pairs.  Per chunk of 32 k there are three
 // hand-offs: TMA -> splitters (one barrier for both tiles), splitters -> MMA
-// thread (eight warp arrivals), MMA commit -> producer.  Waits are bounded and
+// thread (one arrival per splitter warp), MMA commit -> producer; an operand
+// buffer in tensor memory is free again when the commit of the chunk two
+// iterations back has arrived.  Waits are bounded and
 // report through the status word as in tc_kernel.cu.
 //
 // Shapes: b a multiple of 32 and, batch-last, a batch that is a multiple of 32 (the tiles are
@@ -84,51 +105,77 @@ __device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint6
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// same MMA with the A operand (128 rows x 8 k, one 32-bit column per k) read from tensor memory
+__device__ __forceinline__ void umma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ uint32_t lo_part(uint32_t v) {
   return __float_as_uint(__uint_as_float(v) - __uint_as_float(v & 0xFFFFE000u));
 }
 
-// ST stages of [X hi | X lo | W hi | W lo].
-template <bool BS_LAST, int NJ_, int ST_>
+// ST stages of [X hi | X lo | W hi | W lo]; with TS the input operand lives in tensor memory and a
+// stage is [X raw | W hi | W lo].
+// With WR (needs TS and c <= 32 kMaxResident) the hi and lo weights of the CTA's j tile stay in shared
+// memory for all batch tiles of a block, and a stage is the raw input tile alone.
+constexpr int kMaxResident = 6;  // chunks of 32 k
+
+template <bool BS_LAST, int NJ_, int ST_, bool TS_, bool DIRECT_, bool WR_>
 struct CfgF {
   static constexpr int NJ = NJ_;                    // j columns per accumulator (64, 96 or 128)
   static constexpr int ST = ST_;
+  static constexpr bool TS = TS_;
+  static constexpr bool WR = WR_;
+  static_assert(!WR || (TS && BS_LAST && DIRECT_),
+                "resident weights come with the tensor-memory input operand and direct stores");
   static constexpr int XT_BYTES = kKC * 128 * 4;    // 32 k x 128 batch entries (either order)
   static constexpr int WT_BYTES = kKC * NJ * 4;     // 32 k x NJ columns
-  static constexpr int W_OFF = 2 * XT_BYTES;
-  static constexpr int STAGE_BYTES = 2 * XT_BYTES + 2 * WT_BYTES;
+  static constexpr int W_OFF = TS ? XT_BYTES : 2 * XT_BYTES;
+  static constexpr int STAGE_BYTES = WR ? XT_BYTES : W_OFF + 2 * WT_BYTES;
+  static constexpr int WRES_BYTES = WR ? kMaxResident * 2 * WT_BYTES : 0;
   static constexpr int STG_WARP_BYTES = 32 * 128;   // 32 rows of 32 fp32
   // batch-last can do without staging: a warp's 32 lanes hold 32 consecutive batch entries of
   // one output row, so a plain store already writes a whole 128-byte line
-  static constexpr bool DIRECT = BS_LAST && NJ_ > 64;  // (narrow tiles measured faster through TMA stores)
+  static constexpr bool DIRECT = BS_LAST && DIRECT_;
   static constexpr int STG_BYTES = DIRECT ? 0 : kEpilogueWarps * STG_WARP_BYTES;
   // barriers per stage: tiles landed, lo tiles written, stage free; tmem full/empty
-  static constexpr int NBAR = 3 * ST + 4;
+  // + weights landed, weights split (resident weights only)
+  static constexpr int NBAR = 3 * ST + 6;
   static constexpr int BAR_BYTES = 512;
-  static constexpr int SMEM_BYTES = STG_BYTES + ST * STAGE_BYTES + BAR_BYTES + 1024;
+  static constexpr int SMEM_BYTES = STG_BYTES + WRES_BYTES + ST * STAGE_BYTES + BAR_BYTES + 1024;
   static constexpr int NBUF = 2;
   static constexpr int BUF_COLS = 2 * NJ;  // leading accumulator | small-terms accumulator
+  // TS: two operand buffers of [hi: 32 k | lo: 32 k] columns behind the accumulators
+  static constexpr int A_COL0 = NBUF * BUF_COLS;
+  static constexpr int A_BUF_COLS = 2 * kKC;
+  static constexpr int USED_COLS = A_COL0 + (TS ? 2 * A_BUF_COLS : 0);
   // allocations are powers of two
-  static constexpr int TMEM_COLS = NBUF * BUF_COLS <= 128 ? 128 : (NBUF * BUF_COLS <= 256 ? 256 : 512);
+  static constexpr int TMEM_COLS = USED_COLS <= 128 ? 128 : (USED_COLS <= 256 ? 256 : 512);
+  static_assert(USED_COLS <= 512, "tensor memory budget");
   static_assert(NJ == 64 || NJ == 96 || NJ == 128, "j tile");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
   static_assert(SMEM_BYTES > 116 * 1024, "one CTA per SM, so that the TMEM allocation never waits");
   static_assert(8 * NBAR + 16 <= BAR_BYTES, "barrier area");
 };
 
-template <bool BS_LAST, int NJ_, int ST_>
+template <bool BS_LAST, int NJ_, int ST_, bool TS_, bool DIRECT_, bool WR_>
 __global__ void __launch_bounds__(kThreadsF, 1)
     ksmm_tc_f32x3_kernel(const __grid_constant__ CUtensorMap tmX,
                          const __grid_constant__ CUtensorMap tmW,
                          const __grid_constant__ CUtensorMap tmY, const ParamsF P) {
-  using C = CfgF<BS_LAST, NJ_, ST_>;
+  using C = CfgF<BS_LAST, NJ_, ST_, TS_, DIRECT_, WR_>;
   constexpr int ST = C::ST;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t sm0 = (raw + 1023u) & ~1023u;
   uint8_t* sm_gen = smem_raw + (sm0 - raw);
   const uint32_t stg0 = sm0;                     // epilogue staging tiles
-  const uint32_t stage0 = stg0 + C::STG_BYTES;   // operand stages
+  const uint32_t wres0 = stg0 + C::STG_BYTES;    // resident weights: per chunk [hi | lo]
+  const uint32_t stage0 = wres0 + C::WRES_BYTES;  // operand stages
   const uint32_t bar0 = stage0 + ST * C::STAGE_BYTES;
   uint8_t* bar_gen = sm_gen + (bar0 - sm0);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };             // TMA: X hi and W hi landed
@@ -136,6 +183,8 @@ __global__ void __launch_bounds__(kThreadsF, 1)
   auto free_bar = [&](int s) { return bar0 + 8u * (2 * ST + s); };  // MMA commit: stage consumed
   auto tfull_bar = [&](int q) { return bar0 + 8u * (3 * ST + q); };
   auto tempty_bar = [&](int q) { return bar0 + 8u * (3 * ST + 2 + q); };
+  auto wfull_bar = [&]() { return bar0 + 8u * (3 * ST + 4); };   // TMA: a block's hi weights landed
+  auto wsplit_bar = [&]() { return bar0 + 8u * (3 * ST + 5); };  // weight splitters: lo weights written
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * C::NBAR);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 8 * C::NBAR + 4);
 
@@ -144,13 +193,15 @@ __global__ void __launch_bounds__(kThreadsF, 1)
   if (threadIdx.x == 0) {
     for (int s = 0; s < ST; ++s) {
       mbar_init(full_bar(s), 1);
-      mbar_init(split_bar(s), 8);  // four input-splitter and four weight-splitter warps
+      mbar_init(split_bar(s), C::WR ? 4 : 8);  // four input-splitter (and four weight-splitter) warps
       mbar_init(free_bar(s), 1);
     }
     for (int q = 0; q < 2; ++q) {
       mbar_init(tfull_bar(q), 1);
-      mbar_init(tempty_bar(q), kEpilogueWarps);
+      mbar_init(tempty_bar(q), kEpilogueWarps + (C::WR ? 4 : 0));
     }
+    mbar_init(wfull_bar(), 1);
+    mbar_init(wsplit_bar(), 4);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -173,18 +224,34 @@ __global__ void __launch_bounds__(kThreadsF, 1)
   if (warp == 0) {
     // ===================== TMA producer =====================
     if (lane == 0) {
-      uint32_t si = 0, sph = 0;
+      uint32_t si = 0, sph = 0, last_si = 0, last_ph = 0;
+      int cur_blk = -1;
+      (void)last_si; (void)last_ph; (void)cur_blk;
       bool ok = true;
       KSMM_TRACE_DECL;
       for (uint32_t row = row_begin; row < row_end && ok; ++row) {
         const int blk = static_cast<int>(row / P.tiles_n);  // batch-last: (i, l); batch-first: i
         const int n0 = static_cast<int>(row % P.tiles_n) * 128;
+        if constexpr (C::WR) {
+          if (blk != cur_blk) {
+            // new block: once every MMA issued so far has completed (the commit of the last stage
+            // covers them all), its weights replace the resident ones
+            if (cur_blk >= 0 && !mbar_wait<64>(free_bar(last_si), last_ph, abort_flag, P.status, 39)) {
+              ok = false;
+              break;
+            }
+            mbar_expect_tx(wfull_bar(), static_cast<uint32_t>(nchunks) * C::WT_BYTES);
+            for (int qc = 0; qc < nchunks; ++qc)
+              tma_load_4d(wres0 + qc * 2 * C::WT_BYTES, &tmW, wfull_bar(), 0, qc * kKC, j0 / 32, blk);
+            cur_blk = blk;
+          }
+        }
         for (int qc = 0; qc < nchunks; ++qc) {
           KSMM_TRACE(0, 1);
           if (!mbar_wait<64>(free_bar(si), sph ^ 1u, abort_flag, P.status, 31)) { ok = false; break; }
           KSMM_TRACE(0, 2);
           const uint32_t sb = stage0 + si * C::STAGE_BYTES;
-          mbar_expect_tx(full_bar(si), C::XT_BYTES + C::WT_BYTES);
+          mbar_expect_tx(full_bar(si), C::XT_BYTES + (C::WR ? 0 : C::WT_BYTES));
           if constexpr (BS_LAST) {
             // (n % 32, k, n / 32, l, i): four atoms of 32 batch entries x 32 k rows
             tma_load_5d(sb, &tmX, full_bar(si), 0, qc * kKC, n0 / 32, blk % P.d, blk / P.d);
@@ -192,8 +259,10 @@ __global__ void __launch_bounds__(kThreadsF, 1)
             tma_load_3d(sb, &tmX, full_bar(si), qc * kKC, blk, n0);
           }
           // (j % 32, k, j / 32, block): NJ / 32 atoms of 32 columns x 32 k rows
-          tma_load_4d(sb + C::W_OFF, &tmW, full_bar(si), 0, qc * kKC, j0 / 32, blk);
+          if constexpr (!C::WR) tma_load_4d(sb + C::W_OFF, &tmW, full_bar(si), 0, qc * kKC, j0 / 32, blk);
           KSMM_TRACE(0, 3);
+          last_si = si;
+          last_ph = sph;
           if (++si == ST) { si = 0; sph ^= 1u; }
         }
       }
@@ -202,7 +271,9 @@ __global__ void __launch_bounds__(kThreadsF, 1)
   } else if (warp == 1) {
     // ===================== MMA issuer =====================
     if (lane == 0) {
-      uint32_t si = 0, sph = 0, ut = 0;
+      uint32_t si = 0, sph = 0, ut = 0, ab = 0, wph = 0;
+      int cur_blk = -1;
+      (void)wph; (void)cur_blk;
       bool ok = true;
       KSMM_TRACE_DECL;
       for (uint32_t row = row_begin; row < row_end && ok; ++row, ++ut) {
@@ -210,6 +281,15 @@ __global__ void __launch_bounds__(kThreadsF, 1)
         KSMM_TRACE(1, 10);
         if (!mbar_wait<0>(tempty_bar(buf), bph ^ 1u, abort_flag, P.status, 33)) { ok = false; break; }
         KSMM_TRACE(1, 11);
+        if constexpr (C::WR) {
+          const int blk = static_cast<int>(row / P.tiles_n);
+          if (blk != cur_blk) {
+            // the block's weights, hi and lo, are in place
+            if (!mbar_wait<0>(wsplit_bar(), wph, abort_flag, P.status, 38)) { ok = false; break; }
+            wph ^= 1u;
+            cur_blk = blk;
+          }
+        }
         tc_fence_after();
         const uint32_t dcol = tmem_base + buf * C::BUF_COLS, dsmall = dcol + C::NJ;
         for (int qc = 0; qc < nchunks; ++qc) {
@@ -217,9 +297,19 @@ __global__ void __launch_bounds__(kThreadsF, 1)
           if (!mbar_wait<0>(split_bar(si), sph, abort_flag, P.status, 35)) { ok = false; break; }
           KSMM_TRACE(1, 13);
           tc_fence_after();
-          const uint32_t xb = stage0 + si * C::STAGE_BYTES, wb = xb + C::W_OFF;
+          const uint32_t xb = stage0 + si * C::STAGE_BYTES;
+          const uint32_t wb = C::WR ? wres0 + qc * 2 * C::WT_BYTES : xb + C::W_OFF;
 #pragma unroll
           for (int ks = 0; ks < kKC / 8; ++ks) {
+            // weights: MN-major, the NJ / 32 hi atoms and then the NJ / 32 lo atoms
+            const uint64_t wst = make_desc(wb + ks * 1024, 4096, 512, 1);
+            const uint32_t acc = (qc | ks) != 0 ? 1u : 0u;
+            if constexpr (C::TS) {
+              const uint32_t ahi = tmem_base + C::A_COL0 + ab * C::A_BUF_COLS + ks * 8;
+              umma_tf32_ts(dcol, ahi, wst, P.idesc2, acc);
+              umma_tf32_ts(dsmall, ahi + kKC, wst, P.idesc, 1u);
+              continue;
+            }
             uint64_t xhi, xlo;
             if constexpr (BS_LAST) {
               // MN-major, 32-byte atoms: 4 KB between the atoms of 32 batch entries, 512 bytes
@@ -231,9 +321,6 @@ __global__ void __launch_bounds__(kThreadsF, 1)
               xhi = make_desc(xb + ks * 32, 16, 1024, 2);
               xlo = make_desc(xb + C::XT_BYTES + ks * 32, 16, 1024, 2);
             }
-            // weights: MN-major, the NJ / 32 hi atoms and then the NJ / 32 lo atoms
-            const uint64_t wst = make_desc(wb + ks * 1024, 4096, 512, 1);
-            const uint32_t acc = (qc | ks) != 0 ? 1u : 0u;
             // hi(x) * [hi(w) | lo(w)]: the leading accumulator and, next to it, the small one
             umma_tf32(dcol, xhi, wst, P.idesc2, acc);
             // lo(x) * hi(w): only the first NJ rows of the same operand
@@ -241,6 +328,7 @@ __global__ void __launch_bounds__(kThreadsF, 1)
           }
           KSMM_TRACE(1, 19);
           umma_commit(free_bar(si));
+          ab ^= 1u;
           if (++si == ST) { si = 0; sph ^= 1u; }
         }
         if (!ok) break;
@@ -248,7 +336,7 @@ __global__ void __launch_bounds__(kThreadsF, 1)
       }
     }
     __syncwarp();
-  } else if (warp < 10) {
+  } else if (warp < (C::WR ? 6 : 10)) {
     // ===================== splitters =====================
     // warps 2..5: lo tile of the input, warps 6..9: lo tile of the weights; same offsets as the
     // hi tile, so the swizzle does not matter here
@@ -257,9 +345,12 @@ __global__ void __launch_bounds__(kThreadsF, 1)
     const uint32_t off0 = on_w ? C::W_OFF : 0u;
     const uint32_t tile_bytes = on_w ? C::WT_BYTES : C::XT_BYTES;
     uint32_t si = 0, sph = 0;
+    // TS: the operand buffer written in iteration t is read by the MMAs of iteration t and was
+    // last read by those of iteration t - 2, whose commit is the free barrier of stage (t - 2) % ST
+    uint32_t iter = 0, s2 = 0, ph2 = 0;
     bool ok = true;
     KSMM_TRACE_DECL;
-    const bool tron = (warp == 2 || warp == 6) && lane == 0;
+    const bool tron = warp == 2 && lane == 0;
     const int trole = on_w ? 3 : 2;
     (void)tron; (void)trole;
     for (uint32_t row = row_begin; row < row_end && ok; ++row) {
@@ -272,6 +363,52 @@ __global__ void __launch_bounds__(kThreadsF, 1)
         if (tron) KSMM_TRACE(trole, 33);
         const uint32_t hb = stage0 + si * C::STAGE_BYTES + off0, lb = hb + tile_bytes;
         const int npieces = static_cast<int>(tile_bytes / 16);
+        if (C::TS && !on_w) {
+          // thread = accumulator row tr (a warp reaches the TMEM lanes of its index mod 4 only):
+          // its 32 k values go to tensor memory, as they are and as lo
+          const int tr = (warp & 3) * 32 + lane;
+          if (iter >= 2) {
+            if (lane == 0) got = mbar_wait<32>(free_bar(s2), ph2, abort_flag, P.status, 37) ? 1 : 0;
+            got = __shfl_sync(0xffffffffu, got, 0);
+            if (!got) { ok = false; break; }
+            if (++s2 == ST) { s2 = 0; ph2 ^= 1u; }
+          }
+          uint32_t v[kKC];
+          if constexpr (BS_LAST) {
+            // atom tr / 32 (32 batch entries x 32 k rows of 128 bytes), 32-byte piece p at p ^ (k % 4)
+            const uint32_t ab0 = hb + (tr >> 5) * 4096 + (lane & 7) * 4;
+#pragma unroll
+            for (int k = 0; k < kKC; ++k)
+              asm volatile("ld.shared.b32 %0, [%1];"
+                           : "=r"(v[k])
+                           : "r"(ab0 + k * 128 + ((((lane >> 3) ^ (k & 3))) << 5))
+                           : "memory");
+          } else {
+            // row tr of 32 k (128 bytes), 16-byte chunk q at q ^ (row % 8)
+            const uint32_t rb = hb + tr * 128;
+#pragma unroll
+            for (int ch = 0; ch < kKC / 4; ++ch)
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(v[4 * ch]), "=r"(v[4 * ch + 1]), "=r"(v[4 * ch + 2]), "=r"(v[4 * ch + 3])
+                           : "r"(rb + ((ch ^ (tr & 7)) << 4))
+                           : "memory");
+          }
+          tc_fence_after();
+          const uint32_t ta = tmem_base + (static_cast<uint32_t>(tr & ~31) << 16) + C::A_COL0 +
+                              (iter & 1u) * C::A_BUF_COLS;
+          tmem_st32(ta, v);
+#pragma unroll
+          for (int k = 0; k < kKC; ++k) v[k] = lo_part(v[k]);
+          tmem_st32(ta + kKC, v);
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(split_bar(si));
+          if (tron) KSMM_TRACE(trole, 34);
+          ++iter;
+          if (++si == ST) { si = 0; sph ^= 1u; }
+          continue;
+        }
 #pragma unroll 4
         for (int pc = tt; pc < npieces; pc += 128) {
           uint32_t v[4];
@@ -293,36 +430,74 @@ __global__ void __launch_bounds__(kThreadsF, 1)
     __syncwarp();
   } else {
     // ===================== epilogue =====================
-    // A warp owns 32 accumulator rows (batch entries) and every other group of
-    // 32 columns (j); one staging tile of 32 x 32 fp32 per TMA store.
-    const int ew = warp - 10;
+    // A warp owns 32 accumulator rows (batch entries) and every NG-th group of
+    // 32 columns (j); one staging tile of 32 x 32 fp32 per TMA store.  With resident weights the
+    // four weight warps are a third group: they split a block's weights when the CTA reaches
+    // it and store accumulator columns the rest of the time.
+    constexpr int NG = C::WR ? 3 : 2;
+    const bool helper = warp < 10;
+    const int ew = helper ? 0 : warp - 10;  // (helpers store directly and have no staging tile)
     const int q = warp & 3;
-    const int grp = ew >> 2;
+    const int grp = helper ? 2 : ew >> 2;
+    uint32_t wph = 0;
+    int cur_blk = -1;
+    (void)wph; (void)cur_blk;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     const bool plain = (P.alpha == 1.f) && (P.bias == nullptr) && (P.act == 0);
     const uint32_t stg = stg0 + ew * C::STG_WARP_BYTES;
     uint32_t ut = 0;
+    KSMM_TRACE_DECL;
+    const bool etr = warp == 10 && lane == 0;
+    (void)etr;
     for (uint32_t row = row_begin; row < row_end; ++row, ++ut) {
       const int blk = static_cast<int>(row / P.tiles_n);
       const int n0 = static_cast<int>(row % P.tiles_n) * 128;
       const uint32_t buf = ut % C::NBUF, bph = (ut / C::NBUF) & 1u;
       int got = 1;
+      if constexpr (C::WR) {
+        if (helper && blk != cur_blk) {
+          // lo tiles of all chunks of the block's weights
+          cur_blk = blk;
+          if (lane == 0) got = mbar_wait<32>(wfull_bar(), wph, abort_flag, P.status, 41) ? 1 : 0;
+          got = __shfl_sync(0xffffffffu, got, 0);
+          if (!got) break;
+          wph ^= 1u;
+          constexpr int kPieces = C::WT_BYTES / 16;
+          for (int pc = (warp - 6) * 32 + lane; pc < nchunks * kPieces; pc += 128) {
+            const uint32_t hb = wres0 + (pc / kPieces) * 2 * C::WT_BYTES + (pc % kPieces) * 16;
+            uint32_t v[4];
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+                         : "r"(hb)
+                         : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(hb + C::WT_BYTES),
+                         "r"(lo_part(v[0])), "r"(lo_part(v[1])), "r"(lo_part(v[2])), "r"(lo_part(v[3]))
+                         : "memory");
+          }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(wsplit_bar());
+        }
+      }
+      if (etr) KSMM_TRACE(3, 50);
       if (lane == 0) got = mbar_wait<128>(tfull_bar(buf), bph, abort_flag, P.status, 40) ? 1 : 0;
       got = __shfl_sync(0xffffffffu, got, 0);
       if (!got) break;
+      if (etr) KSMM_TRACE(3, 51);
       tc_fence_after();
       const bool warp_active = n0 + q * 32 < P.batch;
       int jlim = P.b - j0;
       if (jlim > C::NJ) jlim = C::NJ;
-      const int n_it = warp_active ? ((jlim + 31) / 32 - grp + 1) / 2 : 0;
+      const int n_it = warp_active ? ((jlim + 31) / 32 - grp + NG - 1) / NG : 0;
       bool released = false;
 #pragma unroll 1
       for (int it = 0; it < n_it; ++it) {
-        const int jj0 = (grp + 2 * it) * 32;
+        const int jj0 = (grp + NG * it) * 32;
         uint32_t r[32], rs[32];
         tmem_ld32(tmem_base + lane_addr + buf * C::BUF_COLS + jj0, r);
         tmem_ld32(tmem_base + lane_addr + buf * C::BUF_COLS + C::NJ + jj0, rs);
         tmem_ld_wait();
+        if (etr) KSMM_TRACE(3, 52);
         if (it == n_it - 1) {
           // the accumulator is in registers: the MMA warp may overwrite it
           tc_fence_before();
@@ -366,6 +541,7 @@ __global__ void __launch_bounds__(kThreadsF, 1)
             for (int jj = 0; jj < 32; ++jj)
               if (j0 + jj0 + jj < P.b) dst[jj * jstride] = __uint_as_float(r[jj]);
           }
+          if (etr) KSMM_TRACE(3, 53);
         } else {
           if (lane == 0) bulk_wait_read<0>();  // the previous store has read the staging tile
           __syncwarp();
@@ -417,10 +593,10 @@ __global__ void __launch_bounds__(kThreadsF, 1)
   }
 }
 
-template <bool BS_LAST, int NJ_, int ST_>
+template <bool BS_LAST, int NJ_, int ST_, bool TS_, bool DIRECT_ = false, bool WR_ = false>
 static int launch_f(const Problem& p, cudaStream_t stream) {
-  using C = CfgF<BS_LAST, NJ_, ST_>;
-  auto kern = ksmm_tc_f32x3_kernel<BS_LAST, NJ_, ST_>;
+  using C = CfgF<BS_LAST, NJ_, ST_, TS_, DIRECT_, WR_>;
+  auto kern = ksmm_tc_f32x3_kernel<BS_LAST, NJ_, ST_, TS_, DIRECT_, WR_>;
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -483,8 +659,9 @@ static int launch_f(const Problem& p, cudaStream_t stream) {
   P.act = p.activation;
   P.status = status_word();
   if (!P.status) return set_error(KSMM_ERR_CUDA, "cannot resolve the device status word");
-  // fp32 accumulate, tf32 operands, weights MN-major, batch-last input MN-major, M = 128
-  const uint32_t common = (1u << 4) | (2u << 7) | (2u << 10) | (BS_LAST ? (1u << 15) : 0u) | (1u << 16) |
+  // fp32 accumulate, tf32 operands, weights MN-major, batch-last input MN-major when it is read
+  // from shared memory (an operand in tensor memory is K-major), M = 128
+  const uint32_t common = (1u << 4) | (2u << 7) | (2u << 10) | ((BS_LAST && !C::TS) ? (1u << 15) : 0u) | (1u << 16) |
                           (static_cast<uint32_t>(128 >> 4) << 24);
   P.idesc = common | (static_cast<uint32_t>(C::NJ >> 3) << 17);
   P.idesc2 = common | (static_cast<uint32_t>(2 * C::NJ >> 3) << 17);
@@ -527,22 +704,30 @@ bool tc_f32x3_supported(const Problem& p, bool check_pointers) {
 }
 
 int tc_f32x3_launch(const Problem& p, cudaStream_t stream) {
-  // <batch-last, j tile, stages>.  The j tile
-  // is the one with the least padded work: a tile costs about 0.4 (input side) + 0.6 * NJ / 128.
-  int nj = 128;
+  // <batch-last, j tile, stages, input operand in tensor memory, direct stores, resident weights>.
+  // The j tile is the one with the least padded work.  Relative cost of a tile: 1 for 128 columns
+  // (input operand from shared memory), 0.675 and 0.55 for 96 and 64 columns (input operand in
+  // tensor memory); short blocks (batch-last, c <= 32 kMaxResident) have 96 columns with resident
+  // weights (the weights of the j tile stay in shared memory and twelve warps store the
+  // accumulator) at 0.6 against 0.45 for 64 columns.
+  const bool can_wr = p.bs_last && p.c <= 32 * tc::kMaxResident;
+  int nj = 96;
   double best = 1e30;
   for (int cand : {128, 96, 64}) {
-    const double cost = ((p.b + cand - 1) / cand) * (0.4 + 0.6 * cand / 128.0);
+    const double tile = cand == 128 ? 1.0 : (cand == 96 && can_wr ? 0.6 : (cand == 96 ? 0.675 : (can_wr ? 0.45 : 0.55)));
+    const double cost = ((p.b + cand - 1) / cand) * tile;
     if (cost < best - 1e-9) { best = cost; nj = cand; }
   }
   if (p.bs_last) {
-    if (nj == 128) return tc::launch_f<true, 128, 3>(p, stream);
-    if (nj == 96) return tc::launch_f<true, 96, 4>(p, stream);
-    return tc::launch_f<true, 64, 4>(p, stream);
+    if (nj == 128) return tc::launch_f<true, 128, 3, false, true, false>(p, stream);
+    if (nj == 96)
+      return can_wr ? tc::launch_f<true, 96, 5, true, true, true>(p, stream)
+                    : tc::launch_f<true, 96, 5, true, true, false>(p, stream);
+    return tc::launch_f<true, 64, 6, true, false, false>(p, stream);
   }
-  if (nj == 128) return tc::launch_f<false, 128, 3>(p, stream);
-  if (nj == 96) return tc::launch_f<false, 96, 3>(p, stream);
-  return tc::launch_f<false, 64, 4>(p, stream);
+  if (nj == 128) return tc::launch_f<false, 128, 3, false, false, false>(p, stream);
+  if (nj == 96) return tc::launch_f<false, 96, 4, true, false, false>(p, stream);
+  return tc::launch_f<false, 64, 6, true, false, false>(p, stream);
 }
 
 }  // namespace ksmm

@@ -239,7 +239,8 @@ def test_batch_first_layout_conversion_path(dtype):
 
 
 F32_TC_LAST = [(1, 64, 64, 1), (2, 128, 32, 4), (1, 768, 192, 4), (6, 64, 64, 1), (3, 96, 80, 2),
-               (1, 160, 72, 4), (1, 64, 64, 16), (1, 192, 768, 2), (2, 32, 200, 3), (2, 96, 40, 2)]
+               (1, 160, 72, 4), (1, 64, 64, 16), (1, 192, 768, 2), (2, 32, 200, 3), (2, 96, 40, 2),
+               (1, 128, 224, 2)]   # the last one takes the 128-column tile (operands from shared memory)
 F32_TC_FIRST = [(1, 64, 64, 1), (4, 192, 192, 1), (3, 96, 80, 1), (2, 64, 48, 1), (6, 64, 64, 1),
                 (1, 224, 100, 1), (1, 768, 192, 1), (2, 96, 40, 1)]
 
@@ -257,6 +258,20 @@ def test_tc_family_fp32_split_into_three_tf32_products(bs_last):
             assert not np.isnan(y).any(), (pattern, batch)
             err = ko.rel_fro_error(y, _oracle(x, w, bs_last))
             assert err < 3e-6, (pattern, batch, err)
+    kb.check_device()
+
+
+def test_tc_family_fp32_resident_weights_across_block_changes():
+    """Batch-last fp32 with short blocks keeps a block's weights in shared memory; with more
+    (block, batch tile) pairs than CTAs, CTAs walk over block boundaries and reload them."""
+    for pi, (pattern, batch) in enumerate([((8, 96, 32, 1), 5120), ((2, 192, 96, 3), 9600)]):
+        x, w = _inputs(pattern, batch, torch.float32, True, seed=650 + pi)
+        rng = np.random.RandomState(660 + pi)
+        a, b, c, d = pattern
+        bias = torch.from_numpy(rng.standard_normal(a * b * d).astype(np.float32))
+        y = _run(x, w, pattern, True, algo=_lib.KSMM_ALGO_TC, config=0, bias=bias.to(DEV), alpha=0.5)
+        ref = 0.5 * _oracle(x, w, True) + bias.numpy()[:, None]
+        assert ko.rel_fro_error(y, ref) < 3e-6, pattern
     kb.check_device()
 
 
