@@ -486,6 +486,11 @@ __global__ void __launch_bounds__(kThreadsF, 1)
       if (etr) KSMM_TRACE(3, 51);
       tc_fence_after();
       const bool warp_active = n0 + q * 32 < P.batch;
+      // direct stores: row (i*b + j0)*d + l of the output, this lane's batch entry
+      const int64_t n_row = static_cast<int64_t>(n0) + q * 32 + lane;
+      const int64_t jstride = static_cast<int64_t>(P.d) * P.batch;
+      float* row_out = P.out + ((static_cast<int64_t>(blk / P.d) * P.b + j0) * P.d + blk % P.d) * P.batch + n_row;
+      (void)n_row; (void)jstride; (void)row_out;
       int jlim = P.b - j0;
       if (jlim > C::NJ) jlim = C::NJ;
       const int n_it = warp_active ? ((jlim + 31) / 32 - grp + NG - 1) / NG : 0;
@@ -532,14 +537,21 @@ __global__ void __launch_bounds__(kThreadsF, 1)
         if constexpr (C::DIRECT) {
           // lane = batch entry n, register jj = output row (i*b + j)*d + l: every store instruction
           // of the warp writes 32 consecutive floats of one row
-          const int64_t n = static_cast<int64_t>(n0) + q * 32 + lane;
-          if (n < P.batch) {
-            const int i = blk / P.d, l = blk % P.d;
-            float* dst = P.out + ((static_cast<int64_t>(i) * P.b + j0 + jj0) * P.d + l) * P.batch + n;
-            const int64_t jstride = static_cast<int64_t>(P.d) * P.batch;
+          if (n_row < P.batch) {
+            // few instructions per store: the warps of the epilogue run one dependent stream each,
+            // and on short blocks their instruction count sets the time per tile
+            float* dst = row_out + jj0 * jstride;
+            if (j0 + jj0 + 32 <= P.b) {
 #pragma unroll
-            for (int jj = 0; jj < 32; ++jj)
-              if (j0 + jj0 + jj < P.b) dst[jj * jstride] = __uint_as_float(r[jj]);
+              for (int jj = 0; jj < 32; ++jj) {
+                *dst = __uint_as_float(r[jj]);
+                dst += jstride;
+              }
+            } else {
+#pragma unroll
+              for (int jj = 0; jj < 32; ++jj)
+                if (j0 + jj0 + jj < P.b) dst[jj * jstride] = __uint_as_float(r[jj]);
+            }
           }
           if (etr) KSMM_TRACE(3, 53);
         } else {
