@@ -16,7 +16,7 @@
 // of their own (their truncation is 2^-11 times smaller) and are added to the
 // leading one in the epilogue, which leaves c / 8 truncating additions on the
 // leading accumulator.  Relative Frobenius error against an fp64 oracle: about
-// 3e-7 for c <= 192 and 2e-6 for c = 768, inside the 1e-5 of the reference's own
+// 5e-7 to 8e-7 for c <= 192 and 2e-6 for c = 768, inside the 1e-5 of the reference's own
 // fp32 check (src/ksmm_cu/src/template_sparse_mm.cu:873-880); the default
 // dispatch uses this kernel up to c = 1024.  The exact FFMA kernels stay
 // available as KSMM_ALGO_SIMT.

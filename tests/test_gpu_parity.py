@@ -249,7 +249,7 @@ F32_TC_FIRST = [(1, 64, 64, 1), (4, 192, 192, 1), (3, 96, 80, 1), (2, 64, 48, 1)
 def test_tc_family_fp32_split_into_three_tf32_products(bs_last):
     """fp32 factors on the tensor cores (hi*hi + lo*hi + hi*lo in tf32, fp32 accumulate).  The
     specification's fp32 tolerance is 1e-5; the three-term split has to stay near fp32 rounding
-    (a single tf32 product would sit at about 5e-4), so the test asks for 3e-6 (measured: 3e-7
+    (a single tf32 product would sit at about 5e-4), so the test asks for 3e-6 (measured: 5e-7 to 8e-7
     for c <= 192, 2e-6 for c = 768, where the truncating accumulator shows)."""
     for pi, pattern in enumerate(F32_TC_LAST if bs_last else F32_TC_FIRST):
         for batch in ((32, 160, 544) if bs_last else (8, 136, 520)):   # batch-last: multiples of 32
