@@ -199,6 +199,8 @@ KSMM_API int ksmm_cu_chain_forward_host(const void* host_input, const void* cons
  * (dtype, layout, a, b, c, d, batch).
  *
  * ksmm_cu_num_configs: number of tile configurations of a kernel family.
+ *   (fp32 in the tensor-core family: 0 = output tile chosen by a cost rule,
+ *   1, 2, 3 = output tiles of 128, 96, 64 columns.)
  * ksmm_cu_config_supported: 1 if (algo, config) can run this problem.
  * ksmm_cu_tune: times every supported candidate on the given buffers (which
  *   must be valid for the problem; output is overwritten), stores the winner

@@ -715,7 +715,7 @@ bool tc_f32x3_supported(const Problem& p, bool check_pointers) {
   return true;
 }
 
-int tc_f32x3_launch(const Problem& p, cudaStream_t stream) {
+int tc_f32x3_launch(const Problem& p, int config, cudaStream_t stream) {
   // <batch-last, j tile, stages, input operand in tensor memory, direct stores, resident weights>.
   // The j tile is the one with the least padded work.  Relative cost of a tile: 1 for 128 columns
   // (input operand from shared memory), 0.675 and 0.55 for 96 and 64 columns (input operand in
@@ -730,6 +730,9 @@ int tc_f32x3_launch(const Problem& p, cudaStream_t stream) {
     const double cost = ((p.b + cand - 1) / cand) * tile;
     if (cost < best - 1e-9) { best = cost; nj = cand; }
   }
+  if (config == 1) nj = 128;
+  if (config == 2) nj = 96;
+  if (config == 3) nj = 64;
   if (p.bs_last) {
     if (nj == 128) return tc::launch_f<true, 128, 3, false, true, false>(p, stream);
     if (nj == 96)

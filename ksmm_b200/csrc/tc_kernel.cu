@@ -677,7 +677,7 @@ int tc_num_configs() { return tc::kNumConfigs; }
 
 bool tc_config_supported(const Problem& p, int config, bool check_pointers) {
   if (config < 0 || config >= tc::kNumConfigs) return false;
-  if (p.in_dtype == KSMM_F32) return config == 0 && tc_f32x3_supported(p, check_pointers);
+  if (p.in_dtype == KSMM_F32) return config >= 0 && config <= 3 && tc_f32x3_supported(p, check_pointers);
   if (!p.bs_last && p.d != 1)
     return config == 0 ? tc_bsfirst_d_supported(p, check_pointers)
                        : (config == 1 && tc_bsfirst_dp_supported(p, check_pointers));
@@ -740,7 +740,7 @@ int tc_launch(const Problem& p, int config, cudaStream_t stream) {
                      "bs_last %d (alignment or layout rule)",
                      p.a, p.b, p.c, p.d, static_cast<long long>(p.batch), p.in_dtype, p.bs_last);
   const bool last = p.bs_last != 0;
-  if (p.in_dtype == KSMM_F32) return tc_f32x3_launch(p, stream);
+  if (p.in_dtype == KSMM_F32) return tc_f32x3_launch(p, config, stream);
   if (!last && p.d != 1) return config == 1 ? tc_bsfirst_dp_launch(p, stream) : tc_bsfirst_d_launch(p, stream);
   if (p.out_regroup_d > 0 && !tc_can_regroup_output(p))
     return set_error(KSMM_ERR_UNSUPPORTED, "this factor cannot store a regrouped output");

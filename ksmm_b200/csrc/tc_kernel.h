@@ -29,8 +29,9 @@ int tc_bsfirst_d_launch(const Problem& p, cudaStream_t stream);
 bool tc_bsfirst_dp_supported(const Problem& p, bool check_pointers);
 int tc_bsfirst_dp_launch(const Problem& p, cudaStream_t stream);
 
-// fp32 factors as three tf32 products per term (tc_f32x3.cu); a single configuration
+// fp32 factors as three tf32 products per term (tc_f32x3.cu); configuration 0 picks the j tile by
+// a cost rule, 1..3 force 128, 96 and 64 columns (what the tuner compares)
 bool tc_f32x3_supported(const Problem& p, bool check_pointers);
-int tc_f32x3_launch(const Problem& p, cudaStream_t stream);
+int tc_f32x3_launch(const Problem& p, int config, cudaStream_t stream);
 
 }  // namespace ksmm

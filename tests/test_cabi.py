@@ -90,11 +90,12 @@ def test_config_tables():
     F16, F32, F8, BF16 = _lib.KSMM_F16, _lib.KSMM_F32, _lib.KSMM_F8E4M3, _lib.KSMM_BF16
     # the fp32 FFMA family takes anything
     assert sup(_lib.KSMM_ALGO_SIMT, 0, 25088, 1, 449, 514, 3, F32, F32, 0) == 1
-    # tensor-core family: TMA stride rules; fp32 (three tf32 products) has one configuration and
-    # covers batch-last and batch-first d = 1
+    # tensor-core family: TMA stride rules; fp32 (three tf32 products) covers batch-last and
+    # batch-first d = 1; configuration 0 picks the j tile, 1..3 force 128, 96, 64 columns
     assert sup(_lib.KSMM_ALGO_TC, 0, 25088, 1, 768, 192, 4, F16, F16, 1) == 1
     assert sup(_lib.KSMM_ALGO_TC, 0, 25088, 1, 768, 192, 4, F32, F32, 1) == 1
-    assert sup(_lib.KSMM_ALGO_TC, 1, 25088, 1, 768, 192, 4, F32, F32, 1) == 0
+    assert sup(_lib.KSMM_ALGO_TC, 3, 25088, 1, 768, 192, 4, F32, F32, 1) == 1
+    assert sup(_lib.KSMM_ALGO_TC, 4, 25088, 1, 768, 192, 4, F32, F32, 1) == 0
     assert sup(_lib.KSMM_ALGO_TC, 0, 25088, 1, 768, 192, 4, F32, F32, 0) == 0
     assert sup(_lib.KSMM_ALGO_TC, 0, 25088, 4, 192, 192, 1, F32, F32, 0) == 1
     assert sup(_lib.KSMM_ALGO_TC, 0, 25080, 4, 192, 192, 1, F32, F32, 1) == 0   # batch % 32 != 0

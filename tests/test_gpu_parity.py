@@ -261,6 +261,19 @@ def test_tc_family_fp32_split_into_three_tf32_products(bs_last):
     kb.check_device()
 
 
+@pytest.mark.parametrize("config", [1, 2, 3])
+def test_tc_family_fp32_forced_j_tiles(config):
+    """Configurations 1..3 of the fp32 tensor kernel force j tiles of 128, 96 and 64 columns (the
+    tuner's candidates); every form has to give the result of configuration 0."""
+    cases = [((1, 768, 192, 4), True, 544), ((1, 192, 768, 2), True, 160), ((2, 96, 40, 2), True, 96),
+             ((4, 192, 192, 1), False, 136), ((1, 224, 100, 1), False, 520)]
+    for pi, (pattern, bs_last, batch) in enumerate(cases):
+        x, w = _inputs(pattern, batch, torch.float32, bs_last, seed=670 + pi)
+        y = _run(x, w, pattern, bs_last, algo=_lib.KSMM_ALGO_TC, config=config)
+        assert ko.rel_fro_error(y, _oracle(x, w, bs_last)) < 3e-6, (pattern, bs_last, config)
+    kb.check_device()
+
+
 def test_tc_family_fp32_resident_weights_across_block_changes():
     """Batch-last fp32 with short blocks keeps a block's weights in shared memory; with more
     (block, batch tile) pairs than CTAs, CTAs walk over block boundaries and reload them."""

@@ -82,9 +82,9 @@ def test_tuner_table_round_trip(tmp_path):
          "batch": 25088, "family": "tensor", "config": 0, "ms": 0.047},
         {"sm": 100, "dtype": "f32", "out_dtype": "f32", "bs_last": True, "pattern": [1, 768, 192, 4],
          "batch": 25088, "family": "ffma", "config": 7, "ms": 0.57},
-        # an entry the build cannot run (the fp32 tensor kernel has one configuration) is skipped
+        # an entry the build cannot run (the fp32 tensor kernel has configurations 0..3) is skipped
         {"sm": 100, "dtype": "f32", "out_dtype": "f32", "bs_last": True, "pattern": [1, 64, 64, 1],
-         "batch": 64, "family": "tensor", "config": 3, "ms": 1.0},
+         "batch": 64, "family": "tensor", "config": 4, "ms": 1.0},
         {"sm": 90, "dtype": "f16", "out_dtype": "f16", "bs_last": True, "pattern": [1, 64, 64, 1],
          "batch": 64, "family": "tensor", "config": 1, "ms": 1.0}]}
     path = tmp_path / "tuned.json"
