@@ -66,7 +66,8 @@ typedef enum {
 typedef enum {
   KSMM_ALGO_AUTO = 0,   /* cached tuner choice, else heuristic                */
   KSMM_ALGO_SIMT = 1,   /* FFMA register-tiled kernel, any shape/alignment     */
-  KSMM_ALGO_TC = 2      /* tcgen05 + TMEM + TMA kernel (16-bit and fp8 types)  */
+  KSMM_ALGO_TC = 2,     /* tcgen05 + TMEM + TMA kernels (fp32, 16-bit, fp8)    */
+  KSMM_ALGO_CONVERT = 3 /* batch-first, d > 1: transpose, batch-last kernel, transpose */
 } ksmm_algo_t;
 
 /* Full description of one factor multiplication. */
@@ -92,6 +93,9 @@ typedef struct {
   int32_t config;         /* tile configuration index inside the family, -1 = auto */
   float alpha;            /* output = act(alpha * (K x) + bias); fp8: s_x * s_w */
   int32_t activation;     /* ksmm_activation_t applied last in the epilogue    */
+  void* scratch;          /* optional device memory for the paths that need a  */
+  size_t scratch_bytes;   /* second copy of a tensor (ksmm_cu_layout_scratch_bytes); */
+                          /* NULL = a library-owned buffer per (device, stream) */
 } ksmm_forward_desc_t;
 
 /* Library version: major*10000 + minor*100 + patch. */
@@ -126,6 +130,20 @@ KSMM_API int ksmm_cu_forward(const void* input, const void* values, void* output
 KSMM_API int ksmm_cu_forward_ex(const ksmm_forward_desc_t* desc, void* stream);
 
 /*
+ * Device memory (bytes) that ksmm_cu_forward_ex needs beside input, weights
+ * and output for this problem under the current dispatch: non-zero only for
+ * batch-first factors with d > 1 that run through a layout conversion or a
+ * regrouping pass (the reference's kernels index such inputs directly with
+ * strided scalar accesses, template_kernels_half.cuh:402-413, and need none).
+ * A caller that passes that much in desc->scratch keeps the call free of any
+ * allocation; with scratch == NULL the library uses its own buffer for the
+ * (device, stream) pair, grown on demand and released by
+ * ksmm_cu_release_scratch (which synchronises the device first).
+ */
+KSMM_API size_t ksmm_cu_layout_scratch_bytes(const ksmm_forward_desc_t* desc);
+KSMM_API int ksmm_cu_release_scratch(void);
+
+/*
  * A chain of factors: patterns[4*f .. 4*f+3] = (a,b,c,d) of factor f, applied
  * f = 0 first, as KSLinear.forward_bs_{first,last} loops over its factors
  * (interface.py:193-211, 269-291) and post_process adds the bias once
@@ -134,6 +152,12 @@ KSMM_API int ksmm_cu_forward_ex(const ksmm_forward_desc_t* desc, void* stream);
  */
 KSMM_API size_t ksmm_cu_chain_workspace_bytes(int nfactors, const int32_t* patterns,
                                      int64_t batch, int dtype);
+/* Intermediates plus the layout scratch of the factors that need one in the
+ * given layout: with a workspace of this size a chain call never allocates.
+ * (With the smaller size above, such factors use the library-owned buffer of
+ * the calling stream.) */
+KSMM_API size_t ksmm_cu_chain_workspace_bytes_ex(int nfactors, const int32_t* patterns,
+                                        int64_t batch, int dtype, int bs_last);
 KSMM_API int ksmm_cu_chain_forward(const void* input, const void* const* values, void* output,
                           const void* bias, void* workspace, size_t workspace_bytes,
                           int64_t batch, int nfactors, const int32_t* patterns,
@@ -159,10 +183,13 @@ KSMM_API int ksmm_cu_chain_forward_act(const void* input, const void* const* val
  * and forbids allocation after start-up.  Inputs, weights and the output are
  * still the caller's buffers.
  *
- *   - chains whose intermediates exceed the array (see
- *     ksmm_cu_chain_workspace_bytes) are rejected with KSMM_ERR_WORKSPACE; the
- *     default size holds one 38.5 MB intermediate, e.g. the two-factor KS-ViT-B
- *     MLP layers in fp16 or the README layer in fp32 at batch 25088;
+ *   - the array holds the chain's intermediates and, for batch-first factors
+ *     that run through a layout conversion, their transposed input and output
+ *     (ksmm_cu_chain_workspace_bytes_ex gives the total).  A chain that needs
+ *     more is rejected with KSMM_ERR_WORKSPACE before anything is launched;
+ *     the call never falls back to an allocation.  The default size holds one
+ *     38.5 MB intermediate, e.g. the two-factor KS-ViT-B MLP layers in fp16 or
+ *     the batch-last README layer in fp32 at batch 25088;
  *   - the first call on a device resolves the array's device address; make
  *     that call before starting a stream capture;
  *   - all calls on one GPU share the array, and it keeps the previous call's
@@ -212,6 +239,11 @@ KSMM_API int ksmm_cu_chain_forward_host(const void* host_input, const void* cons
  *   configuration (-1 = the family's own default) and whether the call goes
  *   through the layout-conversion path (transpose, batch-last kernel,
  *   transpose).  Pointers in `desc` are only checked for alignment.
+ * KSMM_ALGO_CONVERT (one configuration, 0) is that conversion path as a
+ *   family of its own, so that the tuner can time it against the direct
+ *   kernels and a saved table can name it.  A cached choice is used only when
+ *   it can run on the pointers of the actual call; otherwise the heuristic
+ *   decides, as if nothing were cached.
  */
 KSMM_API int ksmm_cu_num_configs(int algo);
 KSMM_API int ksmm_cu_config_supported(int algo, int config, int64_t batch, int a, int b, int c, int d,
@@ -237,6 +269,22 @@ KSMM_API int ksmm_cu_check_device(void* stream);
 /* Number of kernel launches issued by this library in the calling process
  * since load (all threads); used by the benchmark to report its launch count. */
 KSMM_API uint64_t ksmm_cu_launch_count(void);
+
+/* Number of device allocations (cudaMalloc) the library itself has made in
+ * this process: layout scratch, the staging buffers of the *_host calls, the
+ * FFMA probe.  A caller that must not allocate at call time can assert that
+ * the count does not move across its calls. */
+KSMM_API uint64_t ksmm_cu_alloc_count(void);
+
+/*
+ * Test hook for the timeout path: launches one warp that waits, through the
+ * same bounded wait as the kernels, on a barrier nothing will ever signal, with
+ * a limit of `limit_cycles` SM cycles (at most 4e9).  The wait runs out, the
+ * warp returns, and the next ksmm_cu_check_device reports
+ * KSMM_ERR_DEVICE_TIMEOUT (code 99).  Nothing faults and the context stays
+ * usable.  No counterpart in the reference.
+ */
+KSMM_API int ksmm_cu_debug_wait_probe(int64_t limit_cycles, void* stream);
 
 /* FP32 FFMA throughput probe: runs a register-resident FMA loop on every SM
  * and returns the measured TFLOP/s in *tflops (the fp32 roofline denominator,

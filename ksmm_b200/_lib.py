@@ -22,7 +22,7 @@ KSMM_ERR_DEVICE_TIMEOUT = 5
 KSMM_ERR_NO_DEVICE = 6
 
 KSMM_F32, KSMM_F16, KSMM_BF16, KSMM_F8E4M3 = 0, 1, 2, 3
-KSMM_ALGO_AUTO, KSMM_ALGO_SIMT, KSMM_ALGO_TC = 0, 1, 2
+KSMM_ALGO_AUTO, KSMM_ALGO_SIMT, KSMM_ALGO_TC, KSMM_ALGO_CONVERT = 0, 1, 2, 3
 KSMM_ACT_NONE, KSMM_ACT_GELU, KSMM_ACT_RELU = 0, 1, 2
 ACTIVATIONS = {None: KSMM_ACT_NONE, "none": KSMM_ACT_NONE, "gelu": KSMM_ACT_GELU, "relu": KSMM_ACT_RELU}
 STATIC_SCRATCH_BYTES = 40 * 1024 * 1024  # KSMM_CU_STATIC_SCRATCH_BYTES
@@ -34,6 +34,8 @@ EXPORTS = (
     "ksmm_cu_tune", "ksmm_cu_set_choice", "ksmm_cu_get_choice", "ksmm_cu_default_choice",
     "ksmm_cu_check_device",
     "ksmm_cu_launch_count", "ksmm_cu_measure_ffma_peak",
+    "ksmm_cu_layout_scratch_bytes", "ksmm_cu_release_scratch", "ksmm_cu_chain_workspace_bytes_ex",
+    "ksmm_cu_alloc_count", "ksmm_cu_debug_wait_probe",
 )
 
 
@@ -46,6 +48,7 @@ class ForwardDesc(ctypes.Structure):
         ("in_dtype", ctypes.c_int32), ("out_dtype", ctypes.c_int32), ("bs_last", ctypes.c_int32),
         ("algo", ctypes.c_int32), ("config", ctypes.c_int32), ("alpha", ctypes.c_float),
         ("activation", ctypes.c_int32),
+        ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t),
     ]
 
 
@@ -111,6 +114,14 @@ def load():
     lib.ksmm_cu_launch_count.restype = ctypes.c_uint64
     lib.ksmm_cu_measure_ffma_peak.restype = i32
     lib.ksmm_cu_measure_ffma_peak.argtypes = [ctypes.POINTER(ctypes.c_float), vp]
+    lib.ksmm_cu_layout_scratch_bytes.restype = ctypes.c_size_t
+    lib.ksmm_cu_layout_scratch_bytes.argtypes = [ctypes.POINTER(ForwardDesc)]
+    lib.ksmm_cu_release_scratch.restype = i32
+    lib.ksmm_cu_chain_workspace_bytes_ex.restype = ctypes.c_size_t
+    lib.ksmm_cu_chain_workspace_bytes_ex.argtypes = [i32, ctypes.POINTER(ctypes.c_int32), i64, i32, i32]
+    lib.ksmm_cu_alloc_count.restype = ctypes.c_uint64
+    lib.ksmm_cu_debug_wait_probe.restype = i32
+    lib.ksmm_cu_debug_wait_probe.argtypes = [i64, vp]
     _lib = lib
     return lib
 

@@ -141,6 +141,12 @@ struct Problem {
   int out_regroup_d = 0, out_regroup_c = 0;
   int in_regrouped = 0;
   int activation = 0;  // ksmm_activation_t, applied after alpha and bias
+  // Caller-provided memory for the paths that need a second copy of a tensor (layout conversion,
+  // regrouping).  With scratch == nullptr the library's own per-stream scratch is used, unless
+  // no_alloc is set: then the call fails with KSMM_ERR_WORKSPACE instead of allocating.
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  int no_alloc = 0;
 };
 
 // element-wise epilogue function (ksmm_activation_t)
@@ -165,9 +171,10 @@ __device__ __forceinline__ float apply_activation(float v, int act) {
 // host-side error plumbing (defined in ksmm_cu.cu)
 int set_error(int status, const char* fmt, ...);
 void count_launch();
-// Device memory of at least `bytes` from a per-device scratch that is grown on demand (never
-// during a stream capture) and shared by all calls on that device: calls that use it on
-// different streams of one device must not overlap.
-int acquire_layout_scratch(size_t bytes, cudaStream_t stream, void** out);
+// Device memory of at least `bytes` for the layout-conversion and regrouping paths: the
+// problem's own scratch when it has one, else a library-owned buffer per (device, stream) that
+// grows on demand (never during a stream capture).  Work on one stream is ordered, so calls on
+// different streams never share a buffer.
+int layout_scratch(const Problem& p, size_t bytes, cudaStream_t stream, void** out);
 
 }  // namespace ksmm

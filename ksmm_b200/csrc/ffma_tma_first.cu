@@ -25,6 +25,8 @@
 // d in {1, 2, 4}, b % 4 == 0, c * d % 4 == 0, 16-byte aligned pointers.
 #include <cuda.h>
 
+#include <atomic>
+
 #include "tc_host.h"
 #include "tc_ptx.cuh"
 
@@ -314,7 +316,7 @@ template <int L>
 static int launch(const Problem& p, cudaStream_t stream) {
   using C = Cfg<L>;
   auto kern = ksmm_ffma_tma_first_kernel<L>;
-  static bool attr_set[64] = {false};
+  static std::atomic<bool> attr_set[64];  // zero-initialised; set once per device (a repeated set is harmless)
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {

@@ -19,6 +19,8 @@
 // (src/ksmm_py/layer/kronecker_sparse/template_kernels_float.cuh:301-491).
 #include <cuda.h>
 
+#include <atomic>
+
 #include "tc_host.h"
 #include "tc_ptx.cuh"
 
@@ -177,7 +179,7 @@ template <int WJ>
 static int launch(const Problem& p, cudaStream_t stream) {
   using C = Cfg<WJ>;
   auto kern = ksmm_ffma_tma_kernel<WJ>;
-  static bool attr_set[64] = {false};
+  static std::atomic<bool> attr_set[64];  // zero-initialised; set once per device (a repeated set is harmless)
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {

@@ -21,6 +21,7 @@ namespace ksmm {
 // ---------------------------------------------------------------------------
 static thread_local char g_last_error[512] = "";
 static std::atomic<uint64_t> g_launches{0};
+static std::atomic<uint64_t> g_allocs{0};  // device allocations made by the library itself
 
 int set_error(int status, const char* fmt, ...) {
   va_list ap;
@@ -169,21 +170,14 @@ static int check_problem(const Problem& p) {
   return KSMM_OK;
 }
 
-static int run_family(const Problem& p, int algo, int config, cudaStream_t stream) {
-  if (algo == KSMM_ALGO_SIMT) return simt_launch(p, config, stream);
-  if (algo == KSMM_ALGO_TC) return tc_launch(p, config, stream);
-  return set_error(KSMM_ERR_BAD_ARGUMENT, "unknown kernel family %d", algo);
-}
-
 // ---------------------------------------------------------------------------
 // Layout-conversion path for batch-first factors with d > 1 that no direct
 // kernel covers (e.g. d = 16): transpose the input to batch-last, run the
 // batch-last kernel, transpose the result back.  Three times the minimal HBM
 // traffic, but every access is a full line, which beats the strided
-// register-staged kernel by a wide margin.  The two transposed buffers live in
-// a per-device scratch that is grown on demand (never during a stream capture)
-// and shared by all calls on that device: calls that use this path on
-// different streams of one device must not overlap.
+// register-staged kernel by a wide margin.  The two transposed buffers come from
+// the problem's scratch (chains carve it out of their workspace) or, without
+// one, from a library-owned buffer per (device, stream).
 // ---------------------------------------------------------------------------
 static size_t align_up(size_t v, size_t al) { return (v + al - 1) / al * al; }
 
@@ -192,43 +186,59 @@ struct ConvScratch {
   size_t cap = 0;
 };
 static std::mutex g_conv_mu;
-static ConvScratch g_conv[64];
+static std::map<std::pair<int, cudaStream_t>, ConvScratch> g_conv;
 
-// Per-device scratch of the layout-conversion and regrouping paths (see common.cuh).
-int acquire_layout_scratch(size_t bytes, cudaStream_t stream, void** out) {
+int layout_scratch(const Problem& p, size_t bytes, cudaStream_t stream, void** out) {
+  if (p.scratch != nullptr && p.scratch_bytes >= bytes) {
+    *out = p.scratch;
+    return KSMM_OK;
+  }
+  if (p.no_alloc)
+    return set_error(KSMM_ERR_WORKSPACE,
+                     "this factor needs %zu bytes of layout scratch (%zu given) and the call may not "
+                     "allocate", bytes, p.scratch ? p.scratch_bytes : static_cast<size_t>(0));
   int dev = 0;
   KSMM_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return set_error(KSMM_ERR_UNSUPPORTED, "device ordinal %d", dev);
   std::lock_guard<std::mutex> g(g_conv_mu);
-  ConvScratch& sc = g_conv[dev];
+  ConvScratch& sc = g_conv[std::make_pair(dev, stream)];
   if (sc.cap < bytes) {
     cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
     cudaStreamIsCapturing(stream, &cs);
     if (cs != cudaStreamCaptureStatusNone)
       return set_error(KSMM_ERR_WORKSPACE,
-                       "the layout-conversion scratch must grow to %zu bytes, which cannot happen "
-                       "inside a stream capture: make one call outside the capture first",
+                       "the layout scratch must grow to %zu bytes, which cannot happen inside a "
+                       "stream capture: pass a scratch, or make one call outside the capture first",
                        bytes);
     if (sc.ptr) {
+      // only work on this stream can still be using the old buffer
       KSMM_CUDA_OK(cudaStreamSynchronize(stream));
       KSMM_CUDA_OK(cudaFree(sc.ptr));
       sc.ptr = nullptr;
       sc.cap = 0;
     }
     KSMM_CUDA_OK(cudaMalloc(&sc.ptr, bytes));
+    g_allocs.fetch_add(1, std::memory_order_relaxed);
     sc.cap = bytes;
   }
   *out = sc.ptr;
   return KSMM_OK;
 }
 
+// a batch-first factor with d > 1 whose batch-last twin has a fast kernel
+static bool conversion_possible(const Problem& p) {
+  if (p.bs_last || p.d == 1 || p.in_regrouped || p.out_regroup_d) return false;
+  return p.batch <= 0x7fffffffLL;
+}
+
+// the heuristic: conversion pays when no direct kernel covers the factor and the batch-last
+// kernel is a tensor-core (or TMA-staged FFMA) one
 static bool conversion_applies(const Problem& p) {
-  if (p.bs_last || p.d == 1) return false;
+  if (!conversion_possible(p)) return false;
   if (reinterpret_cast<uintptr_t>(p.w) % 16 != 0) return false;
   if (p.in_dtype == KSMM_F32) {
     Problem q = p;
     q.bs_last = 1;
-    q.in = q.out = reinterpret_cast<void*>(16);  // alignment is that of the scratch (256 bytes)
+    q.in = q.out = reinterpret_cast<void*>(256);  // alignment is that of the scratch (256 bytes)
     // for compute-heavy blocks the batch-last tensor-core kernel pays for the two transposes;
     // small blocks are bandwidth problems that the direct FFMA kernel (d = 2, 4) serves better
     const bool direct = ffma_tma_first_supported(p, true);
@@ -238,20 +248,28 @@ static bool conversion_applies(const Problem& p) {
   }
   Problem q = p;
   q.bs_last = 1;
-  if (tc_config_supported(p, 0, true)) return false;  // the interleaved-block kernel covers it
-  return q.b >= 32 && q.c >= 16 && tc_config_supported(q, 0, false);
+  q.in = q.out = reinterpret_cast<void*>(256);
+  if (tc_config_supported(p, 0, true)) return false;  // a direct batch-first kernel covers it
+  return q.b >= 32 && q.c >= 16 && tc_config_supported(q, 0, true);
+}
+
+static size_t conversion_scratch_bytes(const Problem& p) {
+  const int es = dtype_size(p.in_dtype), os = dtype_size(p.out_dtype);
+  const size_t n_in = static_cast<size_t>(p.a) * p.c * p.d, n_out = static_cast<size_t>(p.a) * p.b * p.d;
+  return align_up(n_in * p.batch * es, 256) + align_up(n_out * p.batch * os, 256);
 }
 
 static int run_family(const Problem& p, int algo, int config, cudaStream_t stream);
 static int dispatch(const Problem& p, int algo, int config, cudaStream_t stream);
 
 static int forward_via_transpose(const Problem& p, cudaStream_t stream) {
+  if (!conversion_possible(p))
+    return set_error(KSMM_ERR_UNSUPPORTED, "the layout-conversion path serves batch-first factors with d > 1");
   const int es = dtype_size(p.in_dtype), os = dtype_size(p.out_dtype);
   const int64_t n_in = static_cast<int64_t>(p.a) * p.c * p.d, n_out = static_cast<int64_t>(p.a) * p.b * p.d;
   const size_t in_bytes = align_up(static_cast<size_t>(n_in) * p.batch * es, 256);
-  const size_t out_bytes = align_up(static_cast<size_t>(n_out) * p.batch * os, 256);
   void* base = nullptr;
-  int stq = acquire_layout_scratch(in_bytes + out_bytes, stream, &base);
+  int stq = layout_scratch(p, conversion_scratch_bytes(p), stream, &base);
   if (stq != KSMM_OK) return stq;
   void* xt = base;
   void* yt = static_cast<char*>(base) + in_bytes;
@@ -261,9 +279,47 @@ static int forward_via_transpose(const Problem& p, cudaStream_t stream) {
   q.in = xt;
   q.out = yt;
   q.bs_last = 1;
-  st = dispatch(q, KSMM_ALGO_AUTO, -1, stream);
+  q.scratch = nullptr;
+  q.scratch_bytes = 0;
+  st = dispatch(q, KSMM_ALGO_AUTO, -1, stream);  // (a batch-last factor never needs scratch)
   if (st != KSMM_OK) return st;
   return launch_transpose(yt, p.out, n_out, p.batch, os, stream);  // (out, batch) -> (batch, out)
+}
+
+static int run_family(const Problem& p, int algo, int config, cudaStream_t stream) {
+  if (algo == KSMM_ALGO_SIMT) return simt_launch(p, config, stream);
+  if (algo == KSMM_ALGO_TC) return tc_launch(p, config, stream);
+  if (algo == KSMM_ALGO_CONVERT) return forward_via_transpose(p, stream);
+  return set_error(KSMM_ERR_BAD_ARGUMENT, "unknown kernel family %d", algo);
+}
+
+// can this (family, configuration) run the problem with the pointers it actually has?
+static bool choice_runnable(const Problem& p, const Choice& ch) {
+  if (ch.algo == KSMM_ALGO_TC) return tc_config_supported(p, ch.config, true);
+  if (ch.algo == KSMM_ALGO_CONVERT) return conversion_possible(p);
+  if (ch.algo != KSMM_ALGO_SIMT) return false;
+  if (ch.config == kFfmaTmaWide || ch.config == kFfmaTmaNarrow) return ffma_tma_supported(p, true);
+  if (ch.config == kFfmaTmaFirst) return ffma_tma_first_supported(p, true);
+  return true;  // the register-staged kernels take any alignment
+}
+
+// What KSMM_ALGO_AUTO runs: a cached choice when it can run on these pointers (a choice tuned
+// on aligned buffers does not bind an unaligned call), else the heuristic.
+static Choice auto_choice(const Problem& p) {
+  Choice ch;
+  if (lookup_choice(p, &ch) && choice_runnable(p, ch)) return ch;
+  const int tc_cfg = tc_default_config(p);
+  if (tc_cfg >= 0) return Choice{KSMM_ALGO_TC, tc_cfg};
+  if (conversion_applies(p)) return Choice{KSMM_ALGO_CONVERT, 0};
+  return Choice{KSMM_ALGO_SIMT, -1};
+}
+
+// layout scratch the given (family, configuration) needs for this problem
+static size_t scratch_need(const Problem& p, const Choice& ch) {
+  if (ch.algo == KSMM_ALGO_CONVERT) return conversion_scratch_bytes(p);
+  if (ch.algo == KSMM_ALGO_TC && !p.bs_last && p.d != 1 && ch.config == 1 && p.in_dtype != KSMM_F32)
+    return tc_bsfirst_dp_scratch_bytes(p);
+  return 0;
 }
 
 static int dispatch(const Problem& p, int algo, int config, cudaStream_t stream) {
@@ -271,12 +327,8 @@ static int dispatch(const Problem& p, int algo, int config, cudaStream_t stream)
   if (st != KSMM_OK) return st;
   if (p.batch == 0) return KSMM_OK;  // empty batch: nothing to write
   if (algo == KSMM_ALGO_AUTO) {
-    Choice ch;
-    if (lookup_choice(p, &ch)) return run_family(p, ch.algo, ch.config, stream);
-    const int tc_cfg = tc_default_config(p);
-    if (tc_cfg >= 0) return tc_launch(p, tc_cfg, stream);
-    if (conversion_applies(p)) return forward_via_transpose(p, stream);
-    return simt_launch(p, -1, stream);
+    const Choice ch = auto_choice(p);
+    return run_family(p, ch.algo, ch.config, stream);
   }
   return run_family(p, algo, config, stream);
 }
@@ -294,6 +346,8 @@ static Problem problem_of(const ksmm_forward_desc_t& dsc) {
   p.bs_last = dsc.bs_last;
   p.alpha = dsc.alpha;
   p.activation = dsc.activation;
+  p.scratch = dsc.scratch;
+  p.scratch_bytes = dsc.scratch_bytes;
   return p;
 }
 
@@ -342,6 +396,7 @@ static int host_reserve(int which, size_t bytes) {
   }
   size_t want = bytes + bytes / 8 + 256;
   KSMM_CUDA_OK(cudaMalloc(&g_host.buf[which], want));
+  g_allocs.fetch_add(1, std::memory_order_relaxed);
   g_host.cap[which] = want;
   return KSMM_OK;
 }
@@ -405,6 +460,39 @@ int ksmm_cu_check_device(void* stream) {
 
 uint64_t ksmm_cu_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
+uint64_t ksmm_cu_alloc_count(void) { return g_allocs.load(std::memory_order_relaxed); }
+
+int ksmm_cu_debug_wait_probe(int64_t limit_cycles, void* stream) {
+  if (limit_cycles < 0 || limit_cycles > 4000000000ll)
+    return set_error(KSMM_ERR_BAD_ARGUMENT, "the probe's limit is 0 .. 4e9 cycles");
+  return tc_wait_probe(limit_cycles, 99, static_cast<cudaStream_t>(stream));
+}
+
+size_t ksmm_cu_layout_scratch_bytes(const ksmm_forward_desc_t* desc) {
+  if (!desc) return 0;
+  Problem p = problem_of(*desc);
+  if (check_problem(p) != KSMM_OK || p.batch == 0) return 0;
+  if (desc->algo == KSMM_ALGO_AUTO) return scratch_need(p, auto_choice(p));
+  return scratch_need(p, Choice{desc->algo, desc->config});
+}
+
+int ksmm_cu_release_scratch(void) {
+  // every stream that used a buffer has to be idle before its memory goes away
+  KSMM_CUDA_OK(cudaDeviceSynchronize());
+  int dev = 0;
+  KSMM_CUDA_OK(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> g(g_conv_mu);
+  for (auto it = g_conv.begin(); it != g_conv.end();) {
+    if (it->first.first == dev) {
+      if (it->second.ptr) cudaFree(it->second.ptr);
+      it = g_conv.erase(it);
+    } else {
+      ++it;
+    }
+  }
+  return KSMM_OK;
+}
+
 int ksmm_cu_forward(const void* input, const void* values, void* output, int64_t batch, int a,
                     int b, int c, int d, int dtype, int bs_last, void* stream) {
   Problem p;
@@ -425,8 +513,8 @@ int ksmm_cu_forward_ex(const ksmm_forward_desc_t* desc, void* stream) {
   return dispatch(problem_of(*desc), desc->algo, desc->config, static_cast<cudaStream_t>(stream));
 }
 
-size_t ksmm_cu_chain_workspace_bytes(int nfactors, const int32_t* patterns, int64_t batch,
-                                     int dtype) {
+// bytes of the intermediate activations of a chain (two alternating buffers from three factors on)
+static size_t chain_intermediate_bytes(int nfactors, const int32_t* patterns, int64_t batch, int dtype) {
   if (nfactors <= 1 || !patterns || batch <= 0) return 0;
   size_t mx = 0;
   for (int f = 0; f + 1 < nfactors; ++f) {
@@ -438,49 +526,37 @@ size_t ksmm_cu_chain_workspace_bytes(int nfactors, const int32_t* patterns, int6
   return nfactors == 2 ? mx : 2 * mx;
 }
 
-int ksmm_cu_chain_forward(const void* input, const void* const* values, void* output,
-                          const void* bias, void* workspace, size_t workspace_bytes,
-                          int64_t batch, int nfactors, const int32_t* patterns, int dtype,
-                          int bs_last, void* stream) {
-  return ksmm_cu_chain_forward_act(input, values, output, bias, workspace, workspace_bytes, batch,
-                                   nfactors, patterns, dtype, bs_last, KSMM_ACT_NONE, stream);
+size_t ksmm_cu_chain_workspace_bytes(int nfactors, const int32_t* patterns, int64_t batch,
+                                     int dtype) {
+  return chain_intermediate_bytes(nfactors, patterns, batch, dtype);
 }
 
-int ksmm_cu_chain_forward_act(const void* input, const void* const* values, void* output,
-                              const void* bias, void* workspace, size_t workspace_bytes,
-                              int64_t batch, int nfactors, const int32_t* patterns, int dtype,
-                              int bs_last, int activation, void* stream) {
-  if (activation < 0 || activation > 2)
-    return set_error(KSMM_ERR_BAD_ARGUMENT, "unknown activation %d", activation);
-  if (nfactors <= 0 || !patterns || !values)
-    return set_error(KSMM_ERR_BAD_ARGUMENT, "chain needs at least one factor");
-  if (dtype == KSMM_F8E4M3)
-    return set_error(KSMM_ERR_UNSUPPORTED, "chains run in fp32, fp16 or bf16");
-  for (int f = 0; f + 1 < nfactors; ++f) {
-    const int32_t* q = patterns + 4 * f;
-    const int32_t* r = patterns + 4 * (f + 1);
-    if (static_cast<int64_t>(q[0]) * q[1] * q[3] != static_cast<int64_t>(r[0]) * r[2] * r[3])
-      return set_error(KSMM_ERR_BAD_ARGUMENT,
-                       "factor %d produces %lld features but factor %d expects %lld", f,
-                       static_cast<long long>(q[0]) * q[1] * q[3], f + 1,
-                       static_cast<long long>(r[0]) * r[2] * r[3]);
-  }
-  const size_t need = ksmm_cu_chain_workspace_bytes(nfactors, patterns, batch, dtype);
-  if (need > 0 && (!workspace || workspace_bytes < need))
-    return set_error(KSMM_ERR_WORKSPACE, "chain workspace: need %zu bytes, got %zu", need,
-                     workspace_bytes);
-  const size_t half = nfactors == 2 ? need : need / 2;
+// One pass over a chain: either plans it (run == false: returns through *scratch_max the largest
+// layout scratch any of its factors needs under the current dispatch) or runs it.
+static int chain_walk(bool run, const void* input, const void* const* values, void* output,
+                      const void* bias, void* workspace, size_t inter_bytes, void* scratch,
+                      size_t scratch_bytes, int no_alloc, int64_t batch, int nfactors,
+                      const int32_t* patterns, int dtype, int bs_last, int activation,
+                      cudaStream_t stream, size_t* scratch_max) {
+  const size_t half = nfactors == 2 ? inter_bytes : inter_bytes / 2;
   const void* cur = input;
   bool cur_regrouped = false;  // the intermediate in `cur` is regrouped by the blocks of factor f
+  char* ws = static_cast<char*>(workspace);
+  // planning needs plausible (aligned) addresses only
+  if (!run) {
+    ws = reinterpret_cast<char*>(static_cast<uintptr_t>(1) << 20);
+    cur = output = ws;
+  }
   for (int f = 0; f < nfactors; ++f) {
     const int32_t* q = patterns + 4 * f;
     const bool last = (f + 1 == nfactors);
-    void* dst = last ? output : static_cast<char*>(workspace) + (f & 1) * half;
+    void* dst = last ? output : ws + (f & 1) * half;
     Problem p;
-    p.in = cur; p.w = values[f]; p.out = dst; p.bias = last ? bias : nullptr;
+    p.in = cur; p.w = run ? values[f] : ws; p.out = dst; p.bias = last ? bias : nullptr;
     p.batch = batch; p.a = q[0]; p.b = q[1]; p.c = q[2]; p.d = q[3];
     p.in_dtype = dtype; p.out_dtype = dtype; p.bs_last = bs_last; p.alpha = 1.f;
     p.activation = last ? activation : 0;
+    p.scratch = scratch; p.scratch_bytes = scratch_bytes; p.no_alloc = no_alloc;
     // Layout fusion of consecutive batch-first factors: when the next factor has d = 2 or 4 and
     // this one can store its output regrouped by the next factor's blocks, the intermediate is
     // written in that order and the next factor runs the kernel without the transposer stage
@@ -491,8 +567,8 @@ int ksmm_cu_chain_forward_act(const void* input, const void* const* values, void
       Problem nx = p;
       // the next factor reads this factor's destination and writes its own one
       nx.in = dst;
-      nx.out = (f + 2 == nfactors) ? output : static_cast<char*>(workspace) + ((f + 1) & 1) * half;
-      nx.w = values[f + 1]; nx.bias = nullptr;
+      nx.out = (f + 2 == nfactors) ? output : ws + ((f + 1) & 1) * half;
+      nx.w = run ? values[f + 1] : ws; nx.bias = nullptr;
       nx.a = r[0]; nx.b = r[1]; nx.c = r[2]; nx.d = r[3];
       p.out_regroup_c = r[2];
       p.out_regroup_d = r[3];
@@ -505,14 +581,20 @@ int ksmm_cu_chain_forward_act(const void* input, const void* const* values, void
         p.out_regroup_c = p.out_regroup_d = 0;
       }
     }
-    int st;
+    int st = KSMM_OK;
     if (cur_regrouped) {
       p.in_regrouped = 1;
-      st = tc_launch(p, 1, static_cast<cudaStream_t>(stream));
+      if (run) st = tc_launch(p, 1, stream);
     } else if (next_regrouped) {
-      st = tc_launch(p, -1, static_cast<cudaStream_t>(stream));
+      if (run) st = tc_launch(p, -1, stream);
+    } else if (run) {
+      st = dispatch(p, KSMM_ALGO_AUTO, -1, stream);
     } else {
-      st = dispatch(p, KSMM_ALGO_AUTO, -1, static_cast<cudaStream_t>(stream));
+      st = check_problem(p);
+      if (st == KSMM_OK && batch > 0) {
+        const size_t need = scratch_need(p, auto_choice(p));
+        if (scratch_max && need > *scratch_max) *scratch_max = need;
+      }
     }
     if (st != KSMM_OK) return st;
     cur = dst;
@@ -521,27 +603,124 @@ int ksmm_cu_chain_forward_act(const void* input, const void* const* values, void
   return KSMM_OK;
 }
 
+static int check_chain(int nfactors, const int32_t* patterns, const void* const* values, int dtype,
+                       int activation) {
+  if (activation < 0 || activation > 2)
+    return set_error(KSMM_ERR_BAD_ARGUMENT, "unknown activation %d", activation);
+  if (nfactors <= 0 || !patterns || !values)
+    return set_error(KSMM_ERR_BAD_ARGUMENT, "chain needs at least one factor");
+  if (dtype == KSMM_F8E4M3)
+    return set_error(KSMM_ERR_UNSUPPORTED, "chains run in fp32, fp16 or bf16");
+  if (dtype < KSMM_F32 || dtype > KSMM_F8E4M3)
+    return set_error(KSMM_ERR_BAD_ARGUMENT, "unknown dtype %d", dtype);
+  for (int f = 0; f < nfactors; ++f) {
+    const int32_t* q = patterns + 4 * f;
+    if (q[0] <= 0 || q[1] <= 0 || q[2] <= 0 || q[3] <= 0)
+      return set_error(KSMM_ERR_BAD_ARGUMENT, "pattern %d (%d,%d,%d,%d) must be positive", f, q[0], q[1],
+                       q[2], q[3]);
+  }
+  for (int f = 0; f + 1 < nfactors; ++f) {
+    const int32_t* q = patterns + 4 * f;
+    const int32_t* r = patterns + 4 * (f + 1);
+    if (static_cast<int64_t>(q[0]) * q[1] * q[3] != static_cast<int64_t>(r[0]) * r[2] * r[3])
+      return set_error(KSMM_ERR_BAD_ARGUMENT,
+                       "factor %d produces %lld features but factor %d expects %lld", f,
+                       static_cast<long long>(q[0]) * q[1] * q[3], f + 1,
+                       static_cast<long long>(r[0]) * r[2] * r[3]);
+  }
+  return KSMM_OK;
+}
+
+size_t ksmm_cu_chain_workspace_bytes_ex(int nfactors, const int32_t* patterns, int64_t batch,
+                                        int dtype, int bs_last) {
+  if (nfactors <= 0 || !patterns || batch <= 0) return 0;
+  const void* dummy = nullptr;
+  if (check_chain(nfactors, patterns, &dummy, dtype, 0) != KSMM_OK) return 0;
+  const size_t inter = chain_intermediate_bytes(nfactors, patterns, batch, dtype);
+  size_t scratch = 0;
+  if (chain_walk(false, nullptr, nullptr, nullptr, nullptr, nullptr, inter, nullptr, 0, 0, batch, nfactors,
+                 patterns, dtype, bs_last ? 1 : 0, 0, nullptr, &scratch) != KSMM_OK)
+    return 0;
+  return inter + scratch;
+}
+
+int ksmm_cu_chain_forward(const void* input, const void* const* values, void* output,
+                          const void* bias, void* workspace, size_t workspace_bytes,
+                          int64_t batch, int nfactors, const int32_t* patterns, int dtype,
+                          int bs_last, void* stream) {
+  return ksmm_cu_chain_forward_act(input, values, output, bias, workspace, workspace_bytes, batch,
+                                   nfactors, patterns, dtype, bs_last, KSMM_ACT_NONE, stream);
+}
+
+// Shared body of the chain entry points.  The workspace holds the intermediates first; whatever
+// follows them is handed to the factors as layout scratch.
+static int chain_forward_impl(const void* input, const void* const* values, void* output,
+                              const void* bias, void* workspace, size_t workspace_bytes, int no_alloc,
+                              int64_t batch, int nfactors, const int32_t* patterns, int dtype,
+                              int bs_last, int activation, cudaStream_t stream) {
+  int st = check_chain(nfactors, patterns, values, dtype, activation);
+  if (st != KSMM_OK) return st;
+  if (bs_last != 0 && bs_last != 1) return set_error(KSMM_ERR_BAD_ARGUMENT, "bs_last must be 0 or 1");
+  if (batch < 0) return set_error(KSMM_ERR_BAD_ARGUMENT, "negative batch");
+  const size_t inter = chain_intermediate_bytes(nfactors, patterns, batch, dtype);
+  if (inter > 0 && (!workspace || workspace_bytes < inter))
+    return set_error(KSMM_ERR_WORKSPACE, "chain workspace: need %zu bytes, got %zu", inter,
+                     workspace_bytes);
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  if (workspace && workspace_bytes > inter) {
+    scratch = static_cast<char*>(workspace) + inter;
+    scratch_bytes = workspace_bytes - inter;
+  }
+  if (no_alloc) {
+    // refuse before the first launch, not half-way through the chain
+    size_t need = 0;
+    st = chain_walk(false, nullptr, nullptr, nullptr, nullptr, nullptr, inter, nullptr, 0, 0, batch,
+                    nfactors, patterns, dtype, bs_last, activation, nullptr, &need);
+    if (st != KSMM_OK) return st;
+    if (need > scratch_bytes)
+      return set_error(KSMM_ERR_WORKSPACE,
+                       "the chain needs %zu bytes of intermediates and %zu bytes of layout scratch; "
+                       "%zu bytes are available and this call may not allocate",
+                       inter, need, workspace_bytes);
+  }
+  return chain_walk(true, input, values, output, bias, workspace, inter, scratch, scratch_bytes, no_alloc,
+                    batch, nfactors, patterns, dtype, bs_last, activation, stream, nullptr);
+}
+
+int ksmm_cu_chain_forward_act(const void* input, const void* const* values, void* output,
+                              const void* bias, void* workspace, size_t workspace_bytes,
+                              int64_t batch, int nfactors, const int32_t* patterns, int dtype,
+                              int bs_last, int activation, void* stream) {
+  return chain_forward_impl(input, values, output, bias, workspace, workspace_bytes, /*no_alloc=*/0, batch,
+                            nfactors, patterns, dtype, bs_last, activation,
+                            static_cast<cudaStream_t>(stream));
+}
+
 int ksmm_cu_chain_forward_static(const void* input, const void* const* values, void* output,
                                  const void* bias, int64_t batch, int nfactors,
                                  const int32_t* patterns, int dtype, int bs_last, void* stream) {
-  if (nfactors <= 0 || !patterns || !values)
-    return set_error(KSMM_ERR_BAD_ARGUMENT, "chain needs at least one factor");
-  const size_t need = ksmm_cu_chain_workspace_bytes(nfactors, patterns, batch, dtype);
+  int st = check_chain(nfactors, patterns, values, dtype, 0);
+  if (st != KSMM_OK) return st;
+  // intermediates and, for batch-first factors that run through a layout conversion, their
+  // transposed copies: all of it has to fit into the array
+  const size_t need = ksmm_cu_chain_workspace_bytes_ex(nfactors, patterns, batch, dtype, bs_last);
   if (need > static_cast<size_t>(KSMM_CU_STATIC_SCRATCH_BYTES))
     return set_error(KSMM_ERR_WORKSPACE,
-                     "chain intermediates need %zu bytes but the built-in scratch holds %zu: use "
+                     "the chain needs %zu bytes of scratch but the built-in scratch holds %zu: use "
                      "ksmm_cu_chain_forward with a caller-provided workspace",
                      need, static_cast<size_t>(KSMM_CU_STATIC_SCRATCH_BYTES));
   void* scratch = nullptr;
   if (need > 0) {
-    int st = static_scratch_address(&scratch);
+    st = static_scratch_address(&scratch);
     if (st != KSMM_OK) return st;
   }
   // every intermediate is fully overwritten by the factor that produces it, so
   // nothing in the scratch has to start at zero
-  return ksmm_cu_chain_forward(input, values, output, bias, scratch,
-                               need > 0 ? static_cast<size_t>(KSMM_CU_STATIC_SCRATCH_BYTES) : 0,
-                               batch, nfactors, patterns, dtype, bs_last, stream);
+  return chain_forward_impl(input, values, output, bias, scratch,
+                            need > 0 ? static_cast<size_t>(KSMM_CU_STATIC_SCRATCH_BYTES) : 0,
+                            /*no_alloc=*/1, batch, nfactors, patterns, dtype, bs_last, KSMM_ACT_NONE,
+                            static_cast<cudaStream_t>(stream));
 }
 
 int ksmm_cu_chain_forward_host(const void* host_input, const void* const* host_values,
@@ -593,7 +772,7 @@ int ksmm_cu_chain_forward_host(const void* host_input, const void* const* host_v
   if (batch >= 16384) slice = ((batch + 7) / 8 + 255) / 256 * 256;
   else if (batch >= 8192) slice = ((batch + 3) / 4 + 255) / 256 * 256;
   const int nslices = static_cast<int>((batch + slice - 1) / slice);
-  const size_t ws_bytes = ksmm_cu_chain_workspace_bytes(nfactors, patterns, slice, dtype);
+  const size_t ws_bytes = ksmm_cu_chain_workspace_bytes_ex(nfactors, patterns, slice, dtype, bs_last);
   int st;
   if ((st = host_reserve(0, in_feats * slice * es)) != KSMM_OK) return st;
   if ((st = host_reserve(1, out_feats * slice * es)) != KSMM_OK) return st;
@@ -677,6 +856,7 @@ int ksmm_cu_chain_forward_host(const void* host_input, const void* const* host_v
 int ksmm_cu_num_configs(int algo) {
   if (algo == KSMM_ALGO_SIMT) return kNumFfmaConfigs;
   if (algo == KSMM_ALGO_TC) return tc_num_configs();
+  if (algo == KSMM_ALGO_CONVERT) return 1;
   return 0;
 }
 
@@ -695,6 +875,7 @@ int ksmm_cu_config_supported(int algo, int config, int64_t batch, int a, int b, 
     return in_dtype == out_dtype;
   }
   if (algo == KSMM_ALGO_TC) return tc_config_supported(p, config, /*check_pointers=*/false);
+  if (algo == KSMM_ALGO_CONVERT) return config == 0 && conversion_possible(p);
   return 0;
 }
 
@@ -712,16 +893,16 @@ int ksmm_cu_tune(const ksmm_forward_desc_t* desc, int nrepeats, void* stream, in
   KSMM_CUDA_OK(cudaEventCreate(&e1));
   float best = -1.f;
   Choice win{KSMM_ALGO_SIMT, simt_default_config_for(p)};
-  const int families[2] = {KSMM_ALGO_TC, KSMM_ALGO_SIMT};
+  // candidates: every configuration of the two kernel families that can run the problem, and
+  // the layout-conversion path (transpose, batch-last kernel, transpose) where it exists
+  const int families[3] = {KSMM_ALGO_TC, KSMM_ALGO_SIMT, KSMM_ALGO_CONVERT};
   for (int fam : families) {
-    const int ncfg = ksmm_cu_num_configs(fam);
+    const int ncfg = fam == KSMM_ALGO_CONVERT ? 1 : ksmm_cu_num_configs(fam);
     for (int cfg = 0; cfg < ncfg; ++cfg) {
-      if (fam == KSMM_ALGO_TC) {
-        if (!tc_config_supported(p, cfg, true)) continue;
-      } else if (!ksmm_cu_config_supported(fam, cfg, p.batch, p.a, p.b, p.c, p.d, p.in_dtype,
-                                           p.out_dtype, p.bs_last)) {
+      if (!choice_runnable(p, Choice{fam, cfg})) continue;
+      if (fam == KSMM_ALGO_SIMT &&
+          !ksmm_cu_config_supported(fam, cfg, p.batch, p.a, p.b, p.c, p.d, p.in_dtype, p.out_dtype, p.bs_last))
         continue;
-      }
       // warm-up (also surfaces launch errors)
       if (run_family(p, fam, cfg, s) != KSMM_OK) continue;
       if (cudaStreamSynchronize(s) != cudaSuccess) {
@@ -761,7 +942,7 @@ int ksmm_cu_tune(const ksmm_forward_desc_t* desc, int nrepeats, void* stream, in
 
 int ksmm_cu_set_choice(int64_t batch, int a, int b, int c, int d, int in_dtype, int out_dtype,
                        int bs_last, int algo, int config) {
-  if (algo != KSMM_ALGO_SIMT && algo != KSMM_ALGO_TC)
+  if (algo != KSMM_ALGO_SIMT && algo != KSMM_ALGO_TC && algo != KSMM_ALGO_CONVERT)
     return set_error(KSMM_ERR_BAD_ARGUMENT, "unknown kernel family %d", algo);
   if (!ksmm_cu_config_supported(algo, config, batch, a, b, c, d, in_dtype, out_dtype, bs_last))
     return set_error(KSMM_ERR_UNSUPPORTED, "configuration (%d,%d) cannot run this problem", algo,
@@ -788,27 +969,17 @@ int ksmm_cu_default_choice(const ksmm_forward_desc_t* desc, int* algo, int* conf
   int st = check_problem(p);
   if (st != KSMM_OK) return st;
   int al = KSMM_ALGO_SIMT, cfg = -1, conv = 0;
-  Choice ch;
-  if (lookup_choice(p, &ch)) {
-    al = ch.algo;
-    cfg = ch.config;
-  } else if (tc_default_config(p) >= 0) {
-    al = KSMM_ALGO_TC;
-    cfg = tc_default_config(p);
-  } else if (conversion_applies(p)) {
-    // the batch-last problem the conversion path dispatches
+  Choice ch = auto_choice(p);
+  if (ch.algo == KSMM_ALGO_CONVERT) {
+    // report the kernel of the batch-last problem that the conversion path dispatches
     conv = 1;
     Problem q = p;
     q.bs_last = 1;
     q.in = q.out = reinterpret_cast<void*>(256);
-    if (lookup_choice(q, &ch)) {
-      al = ch.algo;
-      cfg = ch.config;
-    } else if (tc_default_config(q) >= 0) {
-      al = KSMM_ALGO_TC;
-      cfg = tc_default_config(q);
-    }
+    ch = auto_choice(q);
   }
+  al = ch.algo;
+  cfg = ch.config;
   if (algo) *algo = al;
   if (config) *config = cfg;
   if (via_transpose) *via_transpose = conv;
@@ -823,6 +994,7 @@ int ksmm_cu_measure_ffma_peak(float* tflops, void* stream) {
   KSMM_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   float* sink = nullptr;
   KSMM_CUDA_OK(cudaMalloc(&sink, sizeof(float)));
+  g_allocs.fetch_add(1, std::memory_order_relaxed);
   const int iters = 4096, blocks = sms * 8;
   cudaEvent_t e0, e1;
   cudaEventCreate(&e0);

@@ -31,6 +31,8 @@
 // tensor-pipe work.
 #include <cuda.h>
 
+#include <atomic>
+
 #include "tc_host.h"
 #include "tc_kernel.h"
 #include "tc_ptx.cuh"
@@ -471,7 +473,7 @@ template <int D, int NJ_, int SR, int SW, int SA_, int STGN>
 static int launch_d(const Problem& p, cudaStream_t stream) {
   using C = CfgD<D, NJ_, SR, SW, SA_, STGN>;
   auto kern = ksmm_tc_bsfirst_d_kernel<D, NJ_, SR, SW, SA_, STGN>;
-  static bool attr_set[64] = {false};
+  static std::atomic<bool> attr_set[64];  // zero-initialised; set once per device (a repeated set is harmless)
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {

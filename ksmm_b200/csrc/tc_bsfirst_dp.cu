@@ -28,6 +28,8 @@
 // (src/ksmm_py/layer/kronecker_sparse/template_kernels_half.cuh:107-620).
 #include <cuda.h>
 
+#include <atomic>
+
 #include "tc_host.h"
 #include "tc_kernel.h"
 #include "tc_ptx.cuh"
@@ -337,7 +339,7 @@ template <int D, int NJ_, int ST_, int STGN>
 static int launch_p(const Problem& p, const void* regrouped, cudaStream_t stream) {
   using C = CfgP<D, NJ_, ST_, STGN>;
   auto kern = ksmm_tc_bsfirst_dp_kernel<D, NJ_, ST_, STGN>;
-  static bool attr_set[64] = {false};
+  static std::atomic<bool> attr_set[64];  // zero-initialised; set once per device (a repeated set is harmless)
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
@@ -451,6 +453,12 @@ bool tc_bsfirst_dp_supported(const Problem& p, bool check_pointers) {
          p.a <= 65535;
 }
 
+size_t tc_bsfirst_dp_scratch_bytes(const Problem& p) {
+  if (p.in_regrouped) return 0;
+  const size_t bytes = static_cast<size_t>(p.batch) * p.a * p.c * p.d * 2;
+  return (bytes + 255) / 256 * 256;
+}
+
 int tc_bsfirst_dp_launch(const Problem& p, cudaStream_t stream) {
   if (p.in_regrouped) {
     // a chain's previous factor stored its output in this order already
@@ -458,10 +466,9 @@ int tc_bsfirst_dp_launch(const Problem& p, cudaStream_t stream) {
       return p.b > 64 ? tc::launch_p<4, 128, 3, 1>(p, p.in, stream) : tc::launch_p<4, 64, 4, 1>(p, p.in, stream);
     return p.b > 64 ? tc::launch_p<2, 128, 3, 1>(p, p.in, stream) : tc::launch_p<2, 64, 4, 1>(p, p.in, stream);
   }
-  // 1. regroup the input by block into the per-device scratch
-  const size_t bytes = static_cast<size_t>(p.batch) * p.a * p.c * p.d * 2;
+  // 1. regroup the input by block into the scratch
   void* scratch = nullptr;
-  int st = acquire_layout_scratch((bytes + 255) / 256 * 256, stream, &scratch);
+  int st = layout_scratch(p, tc_bsfirst_dp_scratch_bytes(p), stream, &scratch);
   if (st != KSMM_OK) return st;
   {
     const dim3 grid(static_cast<unsigned>((p.batch + 7) / 8), static_cast<unsigned>(p.a));

@@ -71,6 +71,8 @@
 // (src/ksmm_py/layer/kronecker_sparse/template_kernels_float.cuh:301-491, 51-299).
 #include <cuda.h>
 
+#include <atomic>
+
 #include "tc_host.h"
 #include "tc_kernel.h"
 #include "tc_ptx.cuh"
@@ -609,7 +611,7 @@ template <bool BS_LAST, int NJ_, int ST_, bool TS_, bool DIRECT_ = false, bool W
 static int launch_f(const Problem& p, cudaStream_t stream) {
   using C = CfgF<BS_LAST, NJ_, ST_, TS_, DIRECT_, WR_>;
   auto kern = ksmm_tc_f32x3_kernel<BS_LAST, NJ_, ST_, TS_, DIRECT_, WR_>;
-  static bool attr_set[64] = {false};
+  static std::atomic<bool> attr_set[64];  // zero-initialised; set once per device (a repeated set is harmless)
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {

@@ -46,6 +46,8 @@
 // (src/ksmm_cu/src/template_kernels_fp8.cuh:22-370).
 #include <cuda.h>
 
+#include <atomic>
+
 #include <mutex>
 
 #include "tc_kernel.h"
@@ -518,30 +520,36 @@ static constexpr int kNumConfigs = 5;
 
 int* status_word() {
   // one status word per device, owned by the module image
-  static int* ptrs[64] = {nullptr};
+  static std::atomic<int*> ptrs[64];  // zero-initialised; every thread resolves the same address
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  if (!ptrs[dev]) {
+  int* cached = ptrs[dev].load(std::memory_order_acquire);
+  if (!cached) {
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_tc_status_word) != cudaSuccess) return nullptr;
-    ptrs[dev] = static_cast<int*>(p);
+    cached = static_cast<int*>(p);
+    ptrs[dev].store(cached, std::memory_order_release);
   }
-  return ptrs[dev];
+  return cached;
 }
 
 int num_sms() {
-  static int sms[64] = {0};
+  static std::atomic<int> sms[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
-  if (!sms[dev]) cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
-  return sms[dev];
+  int n = sms[dev].load(std::memory_order_relaxed);
+  if (!n) {
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    sms[dev].store(n, std::memory_order_relaxed);
+  }
+  return n;
 }
 
 template <bool BS_LAST, int ES, int OS, int NT, int KC, bool WRES, int NWC, int SX>
 static int launch_one(const Problem& p, cudaStream_t stream) {
   using C = Cfg<BS_LAST, ES, OS, NT, KC, WRES, NWC, SX>;
   auto kern = ksmm_tc_kernel<BS_LAST, ES, OS, NT, KC, WRES, NWC, SX>;
-  static bool attr_set[64] = {false};
+  static std::atomic<bool> attr_set[64];  // zero-initialised; set once per device (a repeated set is harmless)
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
@@ -765,6 +773,37 @@ extern "C" __attribute__((visibility("default"))) int ksmm_debug_trace_clear() {
   return static_cast<int>(cudaMemcpyToSymbol(tc::g_trace, zeros, sizeof(zeros)));
 }
 #endif
+
+// One warp waits on an mbarrier that nothing ever arrives on, through the same bounded wait as
+// the kernels above but with a caller-chosen limit: the wait runs out, the status word takes
+// `code`, the warp returns.  Lets a test see the whole timeout path (device flag ->
+// tc_check_device -> KSMM_ERR_DEVICE_TIMEOUT) without a faulting or hanging kernel.
+namespace tc {
+__global__ void __launch_bounds__(32) wait_probe_kernel(long long limit_cycles, int code, int* status) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ int abort_flag;
+  const uint32_t b = smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    mbar_init(b, 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncwarp();
+  if (threadIdx.x == 0) mbar_wait<64>(b, 0u, &abort_flag, status, code, limit_cycles);
+  __syncwarp();
+}
+}  // namespace tc
+
+int tc_wait_probe(long long limit_cycles, int code, cudaStream_t stream) {
+  int* w = tc::status_word();
+  if (!w) return set_error(KSMM_ERR_CUDA, "cannot resolve the device status word");
+  tc::wait_probe_kernel<<<1, 32, 0, stream>>>(limit_cycles, code, w);
+  count_launch();
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess)
+    return set_error(KSMM_ERR_CUDA, "wait probe launch failed: %s", cudaGetErrorString(err));
+  return KSMM_OK;
+}
 
 int tc_check_device(cudaStream_t stream) {
   cudaError_t e = cudaStreamSynchronize(stream);

@@ -19,6 +19,9 @@ bool tc_can_regroup_output(const Problem& p);
 // Synchronises `stream` and reports a device-side timeout recorded by any
 // earlier launch of this family on the current device (then clears it).
 int tc_check_device(cudaStream_t stream);
+// Launches one warp whose bounded wait (limit in SM cycles) is certain to run out; the device
+// status word then holds `code`.  Test hook for the timeout path.
+int tc_wait_probe(long long limit_cycles, int code, cudaStream_t stream);
 
 // batch-first factors with d = 2 or 4 (tc_bsfirst_d.cu); a single configuration
 bool tc_bsfirst_d_supported(const Problem& p, bool check_pointers);
@@ -28,6 +31,8 @@ int tc_bsfirst_d_launch(const Problem& p, cudaStream_t stream);
 // transposer stage (tc_bsfirst_dp.cu); configuration 1 of such problems
 bool tc_bsfirst_dp_supported(const Problem& p, bool check_pointers);
 int tc_bsfirst_dp_launch(const Problem& p, cudaStream_t stream);
+// bytes of layout scratch that launch needs (0 when the input is regrouped already)
+size_t tc_bsfirst_dp_scratch_bytes(const Problem& p);
 
 // fp32 factors as three tf32 products per term (tc_f32x3.cu); configuration 0 picks the j tile by
 // a cost rule, 1..3 force 128, 96 and 64 columns (what the tuner compares)

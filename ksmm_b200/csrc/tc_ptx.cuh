@@ -74,7 +74,8 @@ constexpr int kThreads = 64 + kEpilogueThreads;
 // barrier-unit bandwidth from the MMA-issuing thread on the same SM partition.
 template <int SLEEP_NS>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+                                          int* status, int code,
+                                          long long limit_cycles = kWaitLimitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
 #pragma unroll 1
@@ -85,7 +86,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
     }
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitLimitCycles) {
+    if (clock64() - t0 > limit_cycles) {
       *abort_flag = 1;
       atomicCAS(status, 0, code);
       return false;

@@ -59,15 +59,25 @@ torch::Tensor chain_forward(torch::Tensor input, std::vector<torch::Tensor> fact
                             std::vector<std::vector<int64_t>> patterns, int64_t bs_last,
                             c10::optional<torch::Tensor> bias, int64_t activation) {
   check_input(input, "input");
+  TORCH_CHECK(input.dim() == 2, "input is 2-D: (features, batch) batch-last, (batch, features) batch-first");
   TORCH_CHECK(!patterns.empty() && patterns.size() == factors.size(), "one factor per pattern");
   std::vector<int32_t> flat;
   std::vector<const void*> vals;
+  int64_t feats = input.size(bs_last ? 0 : 1);  // features entering the next factor
   for (size_t f = 0; f < patterns.size(); ++f) {
     TORCH_CHECK(patterns[f].size() == 4, "a pattern is (a, b, c, d)");
+    for (int64_t v : patterns[f])
+      TORCH_CHECK(v > 0 && v <= 0x7fffffffLL, "pattern values are positive 32-bit integers, got ", v);
+    const int64_t a = patterns[f][0], b = patterns[f][1], c = patterns[f][2], d = patterns[f][3];
+    TORCH_CHECK(a * c * d == feats, "factor ", f, " expects ", a * c * d, " features but receives ", feats);
     check_input(factors[f], "factor");
+    TORCH_CHECK(factors[f].dim() == 2 && factors[f].size(0) == a * d * c && factors[f].size(1) == b,
+                "factor ", f, " must have shape (a*d*c, b) = (", a * d * c, ", ", b, ")");
     TORCH_CHECK(factors[f].scalar_type() == input.scalar_type(), "factors share the input's type");
+    TORCH_CHECK(factors[f].device() == input.device(), "factors live on the input's device");
     for (int64_t v : patterns[f]) flat.push_back(static_cast<int32_t>(v));
     vals.push_back(factors[f].data_ptr());
+    feats = a * b * d;
   }
   const c10::cuda::CUDAGuard guard(input.device());
   const int64_t batch = input.size(bs_last ? 1 : 0);
@@ -76,14 +86,16 @@ torch::Tensor chain_forward(torch::Tensor input, std::vector<torch::Tensor> fact
   auto out = bs_last ? torch::empty({n_out, batch}, input.options())
                      : torch::empty({batch, n_out}, input.options());
   const int code = dtype_code(input);
-  const size_t need = ksmm_cu_chain_workspace_bytes(static_cast<int>(patterns.size()), flat.data(), batch, code);
+  const size_t need = ksmm_cu_chain_workspace_bytes_ex(static_cast<int>(patterns.size()), flat.data(), batch,
+                                                       code, bs_last ? 1 : 0);
   torch::Tensor ws;
   if (need > 0) ws = torch::empty({static_cast<int64_t>(need)}, input.options().dtype(at::kByte));
   const void* bptr = nullptr;
   if (bias.has_value()) {
     check_input(*bias, "bias");
-    TORCH_CHECK(bias->numel() == n_out && bias->scalar_type() == input.scalar_type(),
-                "bias must hold out_size elements of the input's type");
+    TORCH_CHECK(bias->numel() == n_out && bias->scalar_type() == input.scalar_type() &&
+                    bias->device() == input.device(),
+                "bias must hold out_size elements of the input's type on the input's device");
     bptr = bias->data_ptr();
   }
   check_status(ksmm_cu_chain_forward_act(input.data_ptr(), vals.data(), out.data_ptr(), bptr,

@@ -134,7 +134,7 @@ class KSLinear(nn.Module):
                 y = torch.relu(y)
             return y
         if self.fuse_chain or self.num_mat == 1:
-            ws = self._ensure_workspace(x) if self.num_mat > 1 else None
+            ws = self._ensure_workspace(x)
             return _k.chain_forward(x, list(self.factors), self.patterns, self.bs_last, bias=bias,
                                     workspace=ws, activation=self.activation)
         y = x
@@ -149,11 +149,13 @@ class KSLinear(nn.Module):
         lib = _lib.load()
         batch = x.shape[1] if self.bs_last else x.shape[0]
         flat = [v for p in self.patterns for v in p]
-        need = lib.ksmm_cu_chain_workspace_bytes(self.num_mat, _lib.int32_array(flat), batch,
-                                                 _k.dtype_code(x.dtype))
+        need = lib.ksmm_cu_chain_workspace_bytes_ex(self.num_mat, _lib.int32_array(flat), batch,
+                                                    _k.dtype_code(x.dtype), int(bool(self.bs_last)))
+        if need == 0:
+            return None
         ws = self._workspace
         if ws is None or ws.device != x.device or ws.numel() < need:
-            ws = torch.empty(max(need, 1), dtype=torch.uint8, device=x.device)
+            ws = torch.empty(need, dtype=torch.uint8, device=x.device)
             self._workspace = ws
         return ws
 

@@ -117,6 +117,11 @@ def default_choice(pattern, batch, dtype, bs_last, out_dtype=None):
     return ("tensor" if algo.value == _lib.KSMM_ALGO_TC else "ffma"), cfg.value, bool(conv.value)
 
 
+def alloc_count():
+    """Device allocations made by the library itself since it was loaded."""
+    return int(_lib.load().ksmm_cu_alloc_count())
+
+
 class Kernel:
     """Drop-in for the reference's ``Kernel`` (kernel.py:62-329).  Inference
     only, like the reference (its ``backward`` is a stub, kernel.py:323-329)."""
@@ -164,7 +169,7 @@ def chain_forward(input, factors, patterns, bs_last, bias=None, workspace=None, 
     flat = [int(v) for p in patterns for v in p]
     pat = _lib.int32_array(flat)
     code = dtype_code(input.dtype)
-    need = lib.ksmm_cu_chain_workspace_bytes(nf, pat, batch, code)
+    need = lib.ksmm_cu_chain_workspace_bytes_ex(nf, pat, batch, code, bs_last)
     if need > 0 and (workspace is None or workspace.numel() * workspace.element_size() < need):
         workspace = torch.empty(need, dtype=torch.uint8, device=input.device)
     if bias is not None and (bias.numel() != n_out or bias.dtype != input.dtype):

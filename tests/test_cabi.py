@@ -130,3 +130,51 @@ def test_default_choice_reports_family_and_conversion_path():
     assert kb.default_choice((4, 64, 64, 4), 4096, torch.float32, False)[::2] == ("ffma", False)
     assert kb.default_choice((1, 8, 8, 1), 4096, torch.float32, True)[::2] == ("ffma", False)
     assert kb.default_choice((1, 64, 2048, 1), 4096, torch.float32, True)[0] == "ffma"  # c > 1024
+
+
+def test_layout_scratch_planning():
+    """Which calls need memory beside their operands, and how much: only batch-first factors with
+    d > 1 that run through the layout conversion (two transposed copies).  A chain workspace of the
+    `_ex` size holds that as well, so a chain call given that much never allocates."""
+    lib = _lib.load()
+    F16, F32 = _lib.KSMM_F16, _lib.KSMM_F32
+    batch = 4096
+
+    def desc(pattern, dtype, bs_last, algo=0, config=-1):
+        a, b, c, d = pattern
+        return _lib.ForwardDesc(input=256, values=256, output=256, bias=None, batch=batch, a=a, b=b, c=c, d=d,
+                                in_dtype=dtype, out_dtype=dtype, bs_last=bs_last, algo=algo, config=config,
+                                alpha=1.0, activation=0)
+
+    need = lib.ksmm_cu_layout_scratch_bytes
+    assert need(ctypes.byref(desc((1, 64, 64, 16), F16, 1))) == 0
+    assert need(ctypes.byref(desc((4, 192, 192, 1), F16, 0))) == 0
+    assert need(ctypes.byref(desc((1, 64, 64, 3), F16, 0))) == 2 * 192 * batch * 2
+    assert need(ctypes.byref(desc((1, 768, 192, 4), F32, 0))) == (768 + 3072) * batch * 4
+    # forced families: the conversion path by name; a direct kernel needs nothing
+    assert need(ctypes.byref(desc((1, 64, 64, 4), F16, 0, _lib.KSMM_ALGO_CONVERT, 0))) == 2 * 256 * batch * 2
+    assert need(ctypes.byref(desc((1, 64, 64, 4), F16, 0, _lib.KSMM_ALGO_SIMT, 0))) == 0
+    # chains: intermediates, plus the largest layout scratch of any factor in that layout
+    pats = _lib.int32_array([4, 192, 192, 1, 1, 768, 192, 4])
+    inter = lib.ksmm_cu_chain_workspace_bytes(2, pats, batch, F32)
+    assert inter == 768 * batch * 4
+    assert lib.ksmm_cu_chain_workspace_bytes_ex(2, pats, batch, F32, 1) == inter
+    assert lib.ksmm_cu_chain_workspace_bytes_ex(2, pats, batch, F32, 0) == inter + (768 + 3072) * batch * 4
+    assert lib.ksmm_cu_chain_workspace_bytes_ex(2, pats, batch, F16, 0) == 768 * batch * 2  # direct kernels
+    one = _lib.int32_array([1, 64, 64, 3])
+    assert lib.ksmm_cu_chain_workspace_bytes_ex(1, one, batch, F16, 0) == 2 * 192 * batch * 2
+    assert lib.ksmm_cu_alloc_count() == 0          # planning never allocates (and there is no device here)
+
+
+def test_conversion_family_in_the_choice_cache():
+    lib = _lib.load()
+    assert lib.ksmm_cu_num_configs(_lib.KSMM_ALGO_CONVERT) == 1
+    sup = lib.ksmm_cu_config_supported
+    assert sup(_lib.KSMM_ALGO_CONVERT, 0, 512, 1, 64, 64, 16, _lib.KSMM_F16, _lib.KSMM_F16, 0) == 1
+    assert sup(_lib.KSMM_ALGO_CONVERT, 0, 512, 1, 64, 64, 16, _lib.KSMM_F16, _lib.KSMM_F16, 1) == 0  # batch-last
+    assert sup(_lib.KSMM_ALGO_CONVERT, 0, 512, 16, 64, 64, 1, _lib.KSMM_F16, _lib.KSMM_F16, 0) == 0  # d = 1
+    assert lib.ksmm_cu_set_choice(78, 1, 64, 64, 4, 1, 1, 0, _lib.KSMM_ALGO_CONVERT, 0) == 0
+    algo, cfg = ctypes.c_int(-1), ctypes.c_int(-1)
+    assert lib.ksmm_cu_get_choice(78, 1, 64, 64, 4, 1, 1, 0, ctypes.byref(algo), ctypes.byref(cfg)) == 0
+    assert (algo.value, cfg.value) == (_lib.KSMM_ALGO_CONVERT, 0)
+    assert lib.ksmm_cu_set_choice(78, 1, 64, 64, 4, 1, 1, 1, _lib.KSMM_ALGO_CONVERT, 0) == _lib.KSMM_ERR_UNSUPPORTED
