@@ -44,6 +44,20 @@ TORCH_DT = {"fp32": torch.float32, "fp16": torch.float16}
 ESIZE = {"fp32": 4, "fp16": 2}
 
 
+# (dtype, batch-last, pattern) -> DRAM bytes of one launch under ncu, the summary it comes from and
+# the (family, configuration, via_transpose) that capture ran
+NCU_TRAFFIC = {
+    ("fp32", True, (1, 768, 192, 4)): {"bytes": 331.4e6, "profile": "profiles/tc_f32x3_kernel_fp32.md",
+                                       "choice": ("tensor", 0, False)},
+    ("fp32", True, (1, 192, 768, 4)): {"bytes": 369.7e6, "profile": "profiles/tc_f32x3_kernel_fp32.md",
+                                       "choice": ("tensor", 0, False)},
+    ("fp16", True, (1, 768, 192, 4)): {"bytes": 139.5e6, "profile": "profiles/tc_kernel_fp16_bs_last_1_768_192_4.md",
+                                       "choice": ("tensor", 0, False)},
+    ("fp16", False, (1, 768, 192, 4)): {"bytes": 136.5e6, "profile": "profiles/tc_bsfirst_d_kernel_fp16_1_768_192_4.md",
+                                        "choice": ("tensor", 0, False)},
+}
+
+
 def flops_of(p, batch):
     a, b, c, d = p
     return 2.0 * a * b * c * d * batch
@@ -136,24 +150,31 @@ class ClockSampler:
 # ---------------------------------------------------------------------------
 # the reference's CPU algorithm (torch einsum, all host threads), bounded sample
 # ---------------------------------------------------------------------------
-def cpu_reference_pass(sample_cols, seed=0):
-    """One pass of the fp32 half of the sweep on the host at `sample_cols` batch
-    columns with the reference's einsum algorithm; returns (flops, seconds)."""
+def cpu_reference_pass(sample_cols, seed=0, algos=("einsum",), min_run_time=0.05):
+    """The fp32 half of the sweep on the host at `sample_cols` batch columns with the reference's
+    CPU algorithms (`einsum`, `bmm`), each case timed with torch.utils.benchmark.Timer
+    .blocked_autorange as the reference's own timing script does
+    (src/ksmm_py/benchmark/ksmm_time.py:168-190).  Returns {algo: (flops, seconds)} where seconds
+    is the sum of the per-case medians."""
+    from torch.utils import benchmark as tbench
+
     from oracle import reference_port as rp
     g = torch.Generator().manual_seed(seed)
-    total_fl, total_s = 0.0, 0.0
+    out = {al: [0.0, 0.0] for al in algos}
+    nthreads = torch.get_num_threads()
     for bs_last in (True, False):
         for p in PATTERNS:
             a, b, c, d = p
             w = (torch.rand((a, b, c, d), generator=g) * 2 - 1) / (c ** 0.5)
             shape = (a * c * d, sample_cols) if bs_last else (sample_cols, a * c * d)
             x = torch.randn(shape, generator=g)
-            chain = rp.ChainCPU([p], [w], "einsum", bs_last)
-            t0 = time.perf_counter()
-            chain(x)
-            total_s += time.perf_counter() - t0
-            total_fl += flops_of(p, sample_cols)
-    return total_fl, total_s
+            for al in algos:
+                chain = rp.ChainCPU([p], [w], al, bs_last)
+                m = tbench.Timer(stmt="chain(x)", globals={"chain": chain, "x": x},
+                                 num_threads=nthreads).blocked_autorange(min_run_time=min_run_time)
+                out[al][0] += flops_of(p, sample_cols)
+                out[al][1] += m.median
+    return {al: tuple(v) for al, v in out.items()}
 
 
 def use_all_host_threads():
@@ -165,29 +186,45 @@ def use_all_host_threads():
     torch.set_num_threads(max(1, n))
 
 
+REF_COLS = 3136   # batch columns of the bounded CPU sample (1/8 of the benchmark batch)
+
+
+def reference_sample_text(algos):
+    return (f"fp32 half of the sweep (16 of the 32 cases), first {REF_COLS} of {BATCH} batch columns, "
+            f"reference algo={'/'.join(algos)} restated on torch CPU (oracle/reference_port.py), every "
+            "case timed with torch.utils.benchmark blocked_autorange, all host threads")
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
     use_all_host_threads()
-    cols = 3136
-    for _ in range(args.warmup):
-        cpu_reference_pass(cols)
+    for _ in range(min(args.warmup, 1)):
+        cpu_reference_pass(REF_COLS, min_run_time=0.02)
     fl, secs = 0.0, 0.0
+    # each step is one pass of the bounded sample; einsum is the reference's fastest CPU algorithm
+    # on these patterns and the one the line reports (bmm is timed in the default arm's cpu_baseline)
+    budget = 150.0
+    t_start = time.perf_counter()
+    steps_done = 0
     for _ in range(args.steps):
-        f, s = cpu_reference_pass(cols)
+        f, s_ = cpu_reference_pass(REF_COLS, min_run_time=0.02)["einsum"]
         fl += f
-        secs += s
+        secs += s_
+        steps_done += 1
+        if time.perf_counter() - t_start > budget:
+            break
     val = fl / secs / 1e12
+    cfg = workload_config()
+    cfg["sample"] = reference_sample_text(("einsum",)) + f"; {steps_done} passes timed"
     line = {
         "impl": "reference", "metric": "ksmm_sweep_throughput", "value": val, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": 1e3 * secs / args.steps, "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": 1e3 * secs / steps_done, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(),
+        "config": cfg,
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
-                         "kind": "port",
-                         "sample": f"fp32 half of the sweep (16 cases), first {cols} of {BATCH} batch "
-                                   "columns, reference algo=einsum restated on torch CPU"},
+                         "kind": "port", "sample": cfg["sample"]},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -354,17 +391,21 @@ def run_ours(args, rank, world, local_rank):
                     "bound": "hbm" if t_hbm >= t_fl else cb,
                     "roofline_frac": round(t_roof / (ms * 1e-3), 4)})
 
-    # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) at B = 25088 from the ncu
-    # captures summarised under profiles/: (dtype, batch-last, pattern) -> bytes
-    ncu_traffic = {("fp32", True, (1, 192, 768, 4)): 369.7e6, ("fp32", True, (1, 768, 192, 4)): 331.4e6,
-                   ("fp32", False, (4, 64, 64, 4)): 155.4e6,
-                   ("fp16", True, (1, 768, 192, 4)): 135.2e6, ("fp16", False, (1, 768, 192, 4)): 136.5e6}
+    # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) at B = 25088, copied from the
+    # ncu captures summarised under profiles/ together with the kernel family and configuration
+    # the capture ran.  A figure is reported only while the default dispatch still picks that
+    # kernel; otherwise `traffic` is null (the summary no longer describes what was timed).
+    ncu_traffic = NCU_TRAFFIC
 
     def roofline_of(entry, c):
         ms = entry["ms"]
-        traffic = ncu_traffic.get((c["dtype"], bool(c["bs_last"]), tuple(c["pattern"])))
-        if BATCH != 25088:
-            traffic = None
+        traffic, traffic_src = None, None
+        rec = ncu_traffic.get((c["dtype"], bool(c["bs_last"]), tuple(c["pattern"])))
+        if rec is not None and BATCH == 25088:
+            tdt_ = torch.float32 if c["dtype"] == "fp32" else torch.float16
+            fam_, cfg_, conv_ = kb.default_choice(c["pattern"], BATCH, tdt_, c["bs_last"])
+            if (fam_, cfg_, conv_) == rec["choice"]:
+                traffic, traffic_src = rec["bytes"], rec["profile"]
         if entry["bound"] == "hbm":
             ach, pk, unit = c["bytes"] / (ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s"
             src = f"MEASURED_PEAKS.json ({peaks['source']})"
@@ -383,7 +424,8 @@ def run_ours(args, rank, world, local_rank):
                 src = f"MEASURED_PEAKS.json ({peaks['source']})"
         return {"bound": "tensor" if entry["bound"] == "tensor_tf32x3" else entry["bound"],
                 "achieved": round(ach, 2), "peak": round(pk, 2), "unit": unit,
-                "frac": round(ach / pk, 4), "traffic": traffic, "algorithmic_bytes": c["bytes"],
+                "frac": round(ach / pk, 4), "traffic": traffic, "traffic_source": traffic_src,
+                "algorithmic_bytes": c["bytes"],
                 "kernel": f"{entry['dtype']} {entry['layout']} {tuple(entry['pattern'])} ({entry['kernel']})",
                 "peak_source": src,
                 "share_of_step": round(ms / (elapsed_ms / args.steps), 4)}
@@ -419,11 +461,18 @@ def run_ours(args, rank, world, local_rank):
         d2h = sum(hy.numel() * hy.element_size() for _, _, hy, _, _ in host)
 
         def e2e_step():
+            # every case is enqueued through the asynchronous host-buffer call, then all tickets are
+            # waited for: the upload of case k + 1 overlaps the download of case k
+            tickets = []
             for c, (hx, hw, hy, pat, vals) in zip(cs, host):
                 code = _lib.KSMM_F32 if c["dtype"] == "fp32" else _lib.KSMM_F16
-                _lib.check(lib.ksmm_cu_chain_forward_host(
+                t = ctypes.c_uint64(0)
+                _lib.check(lib.ksmm_cu_chain_forward_host_async(
                     hx.data_ptr(), vals, hy.data_ptr(), None, BATCH, 1, pat, code,
-                    int(c["bs_last"]), local_rank))
+                    int(c["bs_last"]), local_rank, ctypes.byref(t)))
+                tickets.append(t.value)
+            for t in tickets:
+                _lib.check(lib.ksmm_cu_host_wait(t))
 
         e2e_step()  # warm-up: the library allocates its staging buffers here
         e2e_steps = max(1, min(args.steps, 3))
@@ -444,7 +493,10 @@ def run_ours(args, rank, world, local_rank):
         assert torch.equal(host[0][2], chk["y"].cpu()), "host-path result differs from device path"
         e2e = {"value": world * step_flops * e2e_steps / e2e_s / 1e12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": e2e_steps,
-               "api": "ksmm_cu_chain_forward_host (C ABI, pinned host buffers, wall clock)"}
+               "h2d_gbs_per_rank": round(h2d * e2e_steps / e2e_s / 1e9, 1),
+               "d2h_gbs_per_rank": round(d2h * e2e_steps / e2e_s / 1e9, 1),
+               "api": "ksmm_cu_chain_forward_host_async + ksmm_cu_host_wait (C ABI, pinned host buffers, "
+                      "32 calls in flight per step, wall clock)"}
 
     # ---- KS-ViT-B/16 forward (128 images per GPU, fp16): the second half of the headline metric --
     ksvit = None
@@ -595,17 +647,23 @@ def run_ours(args, rank, world, local_rank):
     cpu = None
     if world == 1 and not args.no_cpu:
         use_all_host_threads()
-        cols = 3136
-        cpu_reference_pass(cols)
-        fl, secs, passes = 0.0, 0.0, 0
-        while secs < 10.0 and passes < 40:
-            f, s = cpu_reference_pass(cols)
-            fl, secs, passes = fl + f, secs + s, passes + 1
-        cpu = {"value": fl / secs / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
-               "kind": "port",
-               "sample": f"{passes} passes of the fp32 half of the sweep (16 cases) on the first {cols} "
-                         f"of {BATCH} batch columns, reference algo=einsum restated on torch CPU"}
+        algos = ("einsum", "bmm")
+        acc = {al: [0.0, 0.0] for al in algos}
+        passes, t_start = 0, time.perf_counter()
+        while time.perf_counter() - t_start < 20.0 and passes < 10:
+            for al, (f, s_) in cpu_reference_pass(REF_COLS, seed=passes, algos=algos).items():
+                acc[al][0] += f
+                acc[al][1] += s_
+            passes += 1
+        rates = {al: acc[al][0] / acc[al][1] / 1e12 for al in algos}
+        cpu = {"value": rates["einsum"], "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+               "kind": "port", "einsum_tflops": round(rates["einsum"], 4), "bmm_tflops": round(rates["bmm"], 4),
+               "sample": f"{passes} passes; " + reference_sample_text(algos)}
 
+    # The line ends with what a reader who keeps only its tail needs: the compact per-case table
+    # comes first, the summary objects after it.
+    per_compact = [[q["dtype"], "L" if q["layout"] == "bs_last" else "F", q["pattern"], q["ms"],
+                    q["roofline_frac"], q["bound"], q["kernel"]] for q in per]
     line = {
         "metric": "ksmm_sweep_throughput", "value": value, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps,
@@ -613,11 +671,17 @@ def run_ours(args, rank, world, local_rank):
         "dtype": "f32 (three tf32 tensor-core products per term where the default dispatch picks that "
                  "kernel, else fp32 FFMA) + f16; fp32 accumulate",
         "data": "synthetic",
-        "config": workload_config(), "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
-        "roofline": roofline_of(per[dom], cs[dom]),
-        "roofline_hbm": roofline_of(per[dom_hbm], cs[dom_hbm]) if dom_hbm is not None else None,
+        "config": workload_config(),
+        "per_pattern_columns": ["dtype", "layout (L = batch-last, F = batch-first)", "pattern", "ms",
+                                "fraction of roofline", "bound", "kernel"],
+        "per_pattern": per_compact,
+        "per_pattern_ms_ffma_family": {f"{q['dtype']}:{q['layout']}:{','.join(map(str, q['pattern']))}": q["ms_ffma_family"]
+                                       for q in per if q["ms_ffma_family"] is not None},
         "ffma_peak_tflops": round(ffma_peak, 2), "fp32_ffma_only": fp32_exact,
-        "cpu_baseline": cpu, "ksvit_b": ksvit, "chains": chains, "fp8_bf16": lowp, "per_pattern": per,
+        "fp8_bf16": lowp, "chains": chains, "ksvit_b": ksvit,
+        "roofline_hbm": roofline_of(per[dom_hbm], cs[dom_hbm]) if dom_hbm is not None else None,
+        "cpu_baseline": cpu, "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e,
+        "roofline": roofline_of(per[dom], cs[dom]),
     }
     print(json.dumps(line), flush=True)
 

@@ -217,6 +217,23 @@ KSMM_API int ksmm_cu_chain_forward_host(const void* host_input, const void* cons
                                void* host_output, const void* host_bias,
                                int64_t batch, int nfactors, const int32_t* patterns,
                                int dtype, int bs_last, int device);
+/*
+ * The same call split in two, so that a caller with several inputs keeps both
+ * directions of the host link busy: ..._host_async enqueues the copies and the
+ * chain and returns a ticket at once; ksmm_cu_host_wait blocks until that
+ * call's output is complete in host memory.  Calls are served in order, and
+ * the upload of one call overlaps the download of the one before it (the
+ * standalone driver of the reference copies, launches and copies back one
+ * input at a time: template_sparse_mm.cu:443-457, 800-803).  The host buffers
+ * of a call (input, values, bias, output) must stay valid and untouched until
+ * its ticket has been waited for; pinned (page-locked) buffers are what makes
+ * the copies asynchronous.  A ticket of 0 (empty batch) needs no wait.
+ */
+KSMM_API int ksmm_cu_chain_forward_host_async(const void* host_input, const void* const* host_values,
+                                     void* host_output, const void* host_bias,
+                                     int64_t batch, int nfactors, const int32_t* patterns,
+                                     int dtype, int bs_last, int device, uint64_t* ticket);
+KSMM_API int ksmm_cu_host_wait(uint64_t ticket);
 
 /*
  * Tile-configuration introspection and tuning.  Replaces the offline

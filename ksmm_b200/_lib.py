@@ -36,6 +36,7 @@ EXPORTS = (
     "ksmm_cu_launch_count", "ksmm_cu_measure_ffma_peak",
     "ksmm_cu_layout_scratch_bytes", "ksmm_cu_release_scratch", "ksmm_cu_chain_workspace_bytes_ex",
     "ksmm_cu_alloc_count", "ksmm_cu_debug_wait_probe",
+    "ksmm_cu_chain_forward_host_async", "ksmm_cu_host_wait",
 )
 
 
@@ -94,6 +95,12 @@ def load():
     lib.ksmm_cu_chain_forward_host.restype = i32
     lib.ksmm_cu_chain_forward_host.argtypes = [vp, ctypes.POINTER(vp), vp, vp, i64, i32,
                                                ctypes.POINTER(ctypes.c_int32), i32, i32, i32]
+    lib.ksmm_cu_chain_forward_host_async.restype = i32
+    lib.ksmm_cu_chain_forward_host_async.argtypes = [vp, ctypes.POINTER(vp), vp, vp, i64, i32,
+                                                     ctypes.POINTER(ctypes.c_int32), i32, i32, i32,
+                                                     ctypes.POINTER(ctypes.c_uint64)]
+    lib.ksmm_cu_host_wait.restype = i32
+    lib.ksmm_cu_host_wait.argtypes = [ctypes.c_uint64]
     lib.ksmm_cu_num_configs.restype = i32
     lib.ksmm_cu_num_configs.argtypes = [i32]
     lib.ksmm_cu_config_supported.restype = i32

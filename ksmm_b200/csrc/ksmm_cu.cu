@@ -377,19 +377,26 @@ __global__ void __launch_bounds__(256) ffma_probe_kernel(float* sink, int iters,
 struct HostPathState {
   std::mutex mu;
   int device = -1;
-  cudaStream_t stream = nullptr;                   // compute (and everything, for small batches)
-  cudaStream_t s_in = nullptr, s_out = nullptr;    // copy streams of the pipelined path
-  cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_cmp[2] = {nullptr, nullptr},
-              ev_out[2] = {nullptr, nullptr}, ev_w = nullptr;
-  // input A, output A, weights, workspace, input B, output B
-  void* buf[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
-  size_t cap[6] = {0, 0, 0, 0, 0, 0};
+  cudaStream_t stream = nullptr;                   // chains
+  cudaStream_t s_in = nullptr, s_out = nullptr;    // host->device and device->host copies
+  // indexed by slice parity: input landed, chain done, output copied out
+  cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_cmp[2] = {nullptr, nullptr}, ev_out[2] = {nullptr, nullptr};
+  // indexed by call parity: weights landed, weights no longer read
+  cudaEvent_t ev_w[2] = {nullptr, nullptr}, ev_wfree[2] = {nullptr, nullptr};
+  static constexpr int kTickets = 64;
+  cudaEvent_t ev_call[kTickets] = {};              // end of a call's last device->host copy
+  uint64_t ticket_of[kTickets] = {};               // the call that last recorded the slot (0 = none)
+  uint64_t slices = 0, calls = 0;                  // totals since the device was bound
+  // input A, output A, weights A, workspace, input B, output B, weights B
+  void* buf[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  size_t cap[7] = {0, 0, 0, 0, 0, 0, 0};
 };
 static HostPathState g_host;
 
 static int host_reserve(int which, size_t bytes) {
   if (bytes <= g_host.cap[which]) return KSMM_OK;
   if (g_host.buf[which]) {
+    // (cudaFree waits for the device, so copies and kernels of earlier calls are done with it)
     KSMM_CUDA_OK(cudaFree(g_host.buf[which]));
     g_host.buf[which] = nullptr;
     g_host.cap[which] = 0;
@@ -723,33 +730,47 @@ int ksmm_cu_chain_forward_static(const void* input, const void* const* values, v
                             static_cast<cudaStream_t>(stream));
 }
 
-int ksmm_cu_chain_forward_host(const void* host_input, const void* const* host_values,
-                               void* host_output, const void* host_bias, int64_t batch,
-                               int nfactors, const int32_t* patterns, int dtype, int bs_last,
-                               int device) {
-  if (nfactors <= 0 || !patterns || !host_values || !host_input || !host_output)
-    return set_error(KSMM_ERR_BAD_ARGUMENT, "null argument to the host-memory chain call");
-  if (batch <= 0) return batch == 0 ? KSMM_OK : set_error(KSMM_ERR_BAD_ARGUMENT, "negative batch");
-  std::lock_guard<std::mutex> g(g_host.mu);
+// Enqueues one host-memory chain call on the library's three streams and returns its ticket.
+// Caller holds g_host.mu.
+static int host_submit(const void* host_input, const void* const* host_values, void* host_output,
+                       const void* host_bias, int64_t batch, int nfactors, const int32_t* patterns,
+                       int dtype, int bs_last, int device, uint64_t* ticket) {
   KSMM_CUDA_OK(cudaSetDevice(device));
   if (g_host.device != device) {
     // buffers, streams and events belong to one device at a time; moving devices drops them
-    for (int q = 0; q < 6; ++q) {
-      if (g_host.buf[q]) cudaFree(g_host.buf[q]);
-      g_host.buf[q] = nullptr;
-      g_host.cap[q] = 0;
+    if (g_host.device >= 0) {
+      cudaSetDevice(g_host.device);
+      cudaDeviceSynchronize();
+      for (int q = 0; q < 7; ++q) {
+        if (g_host.buf[q]) cudaFree(g_host.buf[q]);
+        g_host.buf[q] = nullptr;
+        g_host.cap[q] = 0;
+      }
+      KSMM_CUDA_OK(cudaSetDevice(device));
     }
     for (cudaStream_t* sp : {&g_host.stream, &g_host.s_in, &g_host.s_out}) {
       if (*sp) cudaStreamDestroy(*sp);
       *sp = nullptr;
       KSMM_CUDA_OK(cudaStreamCreateWithFlags(sp, cudaStreamNonBlocking));
     }
-    for (cudaEvent_t* ep : {&g_host.ev_in[0], &g_host.ev_in[1], &g_host.ev_cmp[0], &g_host.ev_cmp[1],
-                            &g_host.ev_out[0], &g_host.ev_out[1], &g_host.ev_w}) {
+    auto renew = [](cudaEvent_t* ep) -> cudaError_t {
       if (*ep) cudaEventDestroy(*ep);
       *ep = nullptr;
-      KSMM_CUDA_OK(cudaEventCreateWithFlags(ep, cudaEventDisableTiming));
+      return cudaEventCreateWithFlags(ep, cudaEventDisableTiming);
+    };
+    for (int q = 0; q < 2; ++q) {
+      KSMM_CUDA_OK(renew(&g_host.ev_in[q]));
+      KSMM_CUDA_OK(renew(&g_host.ev_cmp[q]));
+      KSMM_CUDA_OK(renew(&g_host.ev_out[q]));
+      KSMM_CUDA_OK(renew(&g_host.ev_w[q]));
+      KSMM_CUDA_OK(renew(&g_host.ev_wfree[q]));
     }
+    for (int q = 0; q < HostPathState::kTickets; ++q) {
+      KSMM_CUDA_OK(renew(&g_host.ev_call[q]));
+      g_host.ticket_of[q] = 0;
+    }
+    g_host.slices = 0;
+    g_host.calls = 0;
     g_host.device = device;
   }
   const size_t es = dtype_size(dtype);
@@ -767,26 +788,30 @@ int ksmm_cu_chain_forward_host(const void* host_input, const void* const* host_v
 
   // The batch is cut into slices of `slice` entries that move through a three-stage pipeline
   // (host->device copy, chain, device->host copy) on three streams with two buffers per
-  // direction, so that both directions of the link are busy at the same time.
+  // direction, so that both directions of the link are busy at the same time.  The slice
+  // counter runs on across calls: the first copy of one call overlaps the last copies of the
+  // call before it.
   int64_t slice = batch;
   if (batch >= 16384) slice = ((batch + 7) / 8 + 255) / 256 * 256;
   else if (batch >= 8192) slice = ((batch + 3) / 4 + 255) / 256 * 256;
   const int nslices = static_cast<int>((batch + slice - 1) / slice);
   const size_t ws_bytes = ksmm_cu_chain_workspace_bytes_ex(nfactors, patterns, slice, dtype, bs_last);
+  const int cp = static_cast<int>(g_host.calls & 1);   // which weight buffer this call uses
+  const int wslot = cp ? 6 : 2;
   int st;
   if ((st = host_reserve(0, in_feats * slice * es)) != KSMM_OK) return st;
   if ((st = host_reserve(1, out_feats * slice * es)) != KSMM_OK) return st;
-  if ((st = host_reserve(2, w_bytes)) != KSMM_OK) return st;
+  if ((st = host_reserve(wslot, w_bytes)) != KSMM_OK) return st;
   if ((st = host_reserve(3, ws_bytes)) != KSMM_OK) return st;
-  if (nslices > 1) {
-    if ((st = host_reserve(4, in_feats * slice * es)) != KSMM_OK) return st;
-    if ((st = host_reserve(5, out_feats * slice * es)) != KSMM_OK) return st;
-  }
-  cudaStream_t sc = g_host.stream, si = nslices > 1 ? g_host.s_in : sc, so = nslices > 1 ? g_host.s_out : sc;
+  if ((st = host_reserve(4, in_feats * slice * es)) != KSMM_OK) return st;
+  if ((st = host_reserve(5, out_feats * slice * es)) != KSMM_OK) return st;
+  cudaStream_t sc = g_host.stream, si = g_host.s_in, so = g_host.s_out;
+  // weights: wait until the call two back no longer reads this buffer
+  if (g_host.calls >= 2) KSMM_CUDA_OK(cudaStreamWaitEvent(si, g_host.ev_wfree[cp], 0));
   std::vector<const void*> dvals(nfactors);
   for (int f = 0; f < nfactors; ++f) {
     const int32_t* q = patterns + 4 * f;
-    char* dst = static_cast<char*>(g_host.buf[2]) + woff[f];
+    char* dst = static_cast<char*>(g_host.buf[wslot]) + woff[f];
     KSMM_CUDA_OK(cudaMemcpyAsync(dst, host_values[f],
                                  static_cast<size_t>(q[0]) * q[1] * q[2] * q[3] * es,
                                  cudaMemcpyHostToDevice, si));
@@ -794,24 +819,23 @@ int ksmm_cu_chain_forward_host(const void* host_input, const void* const* host_v
   }
   const void* dbias = nullptr;
   if (host_bias) {
-    char* dst = static_cast<char*>(g_host.buf[2]) + bias_off;
+    char* dst = static_cast<char*>(g_host.buf[wslot]) + bias_off;
     KSMM_CUDA_OK(cudaMemcpyAsync(dst, host_bias, out_feats * es, cudaMemcpyHostToDevice, si));
     dbias = dst;
   }
-  if (nslices > 1) {
-    KSMM_CUDA_OK(cudaEventRecord(g_host.ev_w, si));
-    KSMM_CUDA_OK(cudaStreamWaitEvent(sc, g_host.ev_w, 0));
-  }
+  KSMM_CUDA_OK(cudaEventRecord(g_host.ev_w[cp], si));
+  KSMM_CUDA_OK(cudaStreamWaitEvent(sc, g_host.ev_w[cp], 0));
   const char* hin = static_cast<const char*>(host_input);
   char* hout = static_cast<char*>(host_output);
   for (int k = 0; k < nslices; ++k) {
     const int64_t n0 = static_cast<int64_t>(k) * slice;
     const int64_t cn = std::min<int64_t>(slice, batch - n0);
-    const int sl = k & 1;
+    const uint64_t gs = g_host.slices;
+    const int sl = static_cast<int>(gs & 1);
     void* din = g_host.buf[sl ? 4 : 0];
     void* dout = g_host.buf[sl ? 5 : 1];
-    // host -> device, once the chain of slice k - 2 has read this input buffer
-    if (k >= 2) KSMM_CUDA_OK(cudaStreamWaitEvent(si, g_host.ev_cmp[sl], 0));
+    // host -> device, once the chain of the slice two back has read this input buffer
+    if (gs >= 2) KSMM_CUDA_OK(cudaStreamWaitEvent(si, g_host.ev_cmp[sl], 0));
     if (bs_last) {
       // (features, batch) row-major: a slice is a column block
       KSMM_CUDA_OK(cudaMemcpy2DAsync(din, cn * es, hin + n0 * es, batch * es, cn * es, in_feats,
@@ -820,22 +844,18 @@ int ksmm_cu_chain_forward_host(const void* host_input, const void* const* host_v
       KSMM_CUDA_OK(cudaMemcpyAsync(din, hin + n0 * in_feats * es, cn * in_feats * es,
                                    cudaMemcpyHostToDevice, si));
     }
-    if (nslices > 1) {
-      KSMM_CUDA_OK(cudaEventRecord(g_host.ev_in[sl], si));
-      KSMM_CUDA_OK(cudaStreamWaitEvent(sc, g_host.ev_in[sl], 0));
-      // the output buffer is free once slice k - 2 has left it
-      if (k >= 2) KSMM_CUDA_OK(cudaStreamWaitEvent(sc, g_host.ev_out[sl], 0));
-    }
+    KSMM_CUDA_OK(cudaEventRecord(g_host.ev_in[sl], si));
+    KSMM_CUDA_OK(cudaStreamWaitEvent(sc, g_host.ev_in[sl], 0));
+    // the output buffer is free once the slice two back has left it
+    if (gs >= 2) KSMM_CUDA_OK(cudaStreamWaitEvent(sc, g_host.ev_out[sl], 0));
     st = ksmm_cu_chain_forward(din, dvals.data(), dout, dbias, g_host.buf[3], g_host.cap[3], cn,
                                nfactors, patterns, dtype, bs_last, sc);
     if (st != KSMM_OK) {
       cudaDeviceSynchronize();
       return st;
     }
-    if (nslices > 1) {
-      KSMM_CUDA_OK(cudaEventRecord(g_host.ev_cmp[sl], sc));
-      KSMM_CUDA_OK(cudaStreamWaitEvent(so, g_host.ev_cmp[sl], 0));
-    }
+    KSMM_CUDA_OK(cudaEventRecord(g_host.ev_cmp[sl], sc));
+    KSMM_CUDA_OK(cudaStreamWaitEvent(so, g_host.ev_cmp[sl], 0));
     if (bs_last) {
       KSMM_CUDA_OK(cudaMemcpy2DAsync(hout + n0 * es, batch * es, dout, cn * es, cn * es, out_feats,
                                      cudaMemcpyDeviceToHost, so));
@@ -843,14 +863,68 @@ int ksmm_cu_chain_forward_host(const void* host_input, const void* const* host_v
       KSMM_CUDA_OK(cudaMemcpyAsync(hout + n0 * out_feats * es, dout, cn * out_feats * es,
                                    cudaMemcpyDeviceToHost, so));
     }
-    if (nslices > 1) KSMM_CUDA_OK(cudaEventRecord(g_host.ev_out[sl], so));
+    KSMM_CUDA_OK(cudaEventRecord(g_host.ev_out[sl], so));
+    ++g_host.slices;
   }
-  KSMM_CUDA_OK(cudaStreamSynchronize(so));
-  if (nslices > 1) {
-    KSMM_CUDA_OK(cudaStreamSynchronize(sc));
-    KSMM_CUDA_OK(cudaStreamSynchronize(si));
-  }
+  KSMM_CUDA_OK(cudaEventRecord(g_host.ev_wfree[cp], sc));
+  ++g_host.calls;
+  const uint64_t t = g_host.calls;  // tickets start at 1
+  const int slot = static_cast<int>(t % HostPathState::kTickets);
+  // a slot is reused every kTickets calls: whoever recorded it last has long been enqueued, and the
+  // copy stream is ordered, so the new record can only complete later than the old one
+  KSMM_CUDA_OK(cudaEventRecord(g_host.ev_call[slot], so));
+  g_host.ticket_of[slot] = t;
+  *ticket = t;
   return KSMM_OK;
+}
+
+static int host_check_args(const void* host_input, const void* const* host_values, void* host_output,
+                           int64_t batch, int nfactors, const int32_t* patterns, int dtype, int bs_last) {
+  if (nfactors <= 0 || !patterns || !host_values || !host_input || !host_output)
+    return set_error(KSMM_ERR_BAD_ARGUMENT, "null argument to the host-memory chain call");
+  if (batch < 0) return set_error(KSMM_ERR_BAD_ARGUMENT, "negative batch");
+  if (bs_last != 0 && bs_last != 1) return set_error(KSMM_ERR_BAD_ARGUMENT, "bs_last must be 0 or 1");
+  return check_chain(nfactors, patterns, host_values, dtype, 0);
+}
+
+int ksmm_cu_chain_forward_host_async(const void* host_input, const void* const* host_values,
+                                     void* host_output, const void* host_bias, int64_t batch,
+                                     int nfactors, const int32_t* patterns, int dtype, int bs_last,
+                                     int device, uint64_t* ticket) {
+  if (!ticket) return set_error(KSMM_ERR_BAD_ARGUMENT, "null ticket pointer");
+  *ticket = 0;
+  int st = host_check_args(host_input, host_values, host_output, batch, nfactors, patterns, dtype, bs_last);
+  if (st != KSMM_OK) return st;
+  if (batch == 0) return KSMM_OK;  // ticket 0: nothing to wait for
+  std::lock_guard<std::mutex> g(g_host.mu);
+  return host_submit(host_input, host_values, host_output, host_bias, batch, nfactors, patterns, dtype,
+                     bs_last, device, ticket);
+}
+
+int ksmm_cu_host_wait(uint64_t ticket) {
+  if (ticket == 0) return KSMM_OK;
+  cudaEvent_t ev = nullptr;
+  {
+    std::lock_guard<std::mutex> g(g_host.mu);
+    if (ticket > g_host.calls) return set_error(KSMM_ERR_BAD_ARGUMENT, "ticket %llu was never issued",
+                                                static_cast<unsigned long long>(ticket));
+    const int slot = static_cast<int>(ticket % HostPathState::kTickets);
+    // a newer call in the same slot completes after this one (one ordered copy stream)
+    ev = g_host.ev_call[slot];
+  }
+  KSMM_CUDA_OK(cudaEventSynchronize(ev));
+  return KSMM_OK;
+}
+
+int ksmm_cu_chain_forward_host(const void* host_input, const void* const* host_values,
+                               void* host_output, const void* host_bias, int64_t batch,
+                               int nfactors, const int32_t* patterns, int dtype, int bs_last,
+                               int device) {
+  uint64_t ticket = 0;
+  int st = ksmm_cu_chain_forward_host_async(host_input, host_values, host_output, host_bias, batch, nfactors,
+                                            patterns, dtype, bs_last, device, &ticket);
+  if (st != KSMM_OK) return st;
+  return ksmm_cu_host_wait(ticket);
 }
 
 int ksmm_cu_num_configs(int algo) {

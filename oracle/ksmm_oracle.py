@@ -33,7 +33,7 @@ import numpy as np
 
 __all__ = [
     "in_size", "out_size", "abcd_to_kernel_format", "kernel_format_to_abcd",
-    "abcd_to_dense", "factor_apply", "chain_apply", "chain_dense",
+    "abcd_to_dense", "factor_apply", "factor_apply_einsum", "chain_apply", "chain_dense",
     "rel_fro_error", "quantize_e4m3", "e4m3_scale", "flops", "min_bytes",
 ]
 
@@ -88,16 +88,34 @@ def factor_apply(x, w, bs_last, acc_dtype=np.float64):
     """
     a, b, c, d = w.shape
     x = np.asarray(x, dtype=acc_dtype)
-    w = np.asarray(w, dtype=acc_dtype)
+    # Both einsums are one (b x c) @ (c x B) product per block (i, l); written as a batched matmul
+    # over (a, d) so that numpy hands the inner products to BLAS (same sums, same accumulation
+    # type; the literal einsum forms take minutes on the largest patterns of patterns.in).
+    wt = np.ascontiguousarray(np.transpose(np.asarray(w), (0, 3, 1, 2)), dtype=acc_dtype)  # (a, d, b, c)
     if bs_last:
         assert x.shape[0] == a * c * d, (x.shape, w.shape)
         nb = x.shape[1]
-        y = np.einsum("acdn,abcd->abdn", x.reshape(a, c, d, nb), w, optimize=True)
-        return y.reshape(a * b * d, nb)
+        xt = np.transpose(x.reshape(a, c, d, nb), (0, 2, 1, 3))          # (a, d, c, B)
+        y = np.matmul(wt, xt)                                            # (a, d, b, B)
+        return np.ascontiguousarray(np.transpose(y, (0, 2, 1, 3))).reshape(a * b * d, nb)
     assert x.shape[1] == a * c * d, (x.shape, w.shape)
     nb = x.shape[0]
-    y = np.einsum("nacd,abcd->nabd", x.reshape(nb, a, c, d), w, optimize=True)
-    return y.reshape(nb, a * b * d)
+    xt = np.transpose(x.reshape(nb, a, c, d), (1, 3, 2, 0))              # (a, d, c, B)
+    y = np.matmul(wt, xt)                                                # (a, d, b, B)
+    return np.ascontiguousarray(np.transpose(y, (3, 0, 2, 1))).reshape(nb, a * b * d)
+
+
+def factor_apply_einsum(x, w, bs_last, acc_dtype=np.float64):
+    """The same factor written literally as the reference's einsum strings
+    (interface.py:254-264, 332-342); kept to pin :func:`factor_apply` in the tests."""
+    a, b, c, d = w.shape
+    x = np.asarray(x, dtype=acc_dtype)
+    w = np.asarray(w, dtype=acc_dtype)
+    if bs_last:
+        nb = x.shape[1]
+        return np.einsum("acdn,abcd->abdn", x.reshape(a, c, d, nb), w, optimize=True).reshape(a * b * d, nb)
+    nb = x.shape[0]
+    return np.einsum("nacd,abcd->nabd", x.reshape(nb, a, c, d), w, optimize=True).reshape(nb, a * b * d)
 
 
 def chain_apply(x, weights, bs_last, bias=None, acc_dtype=np.float64, round_to=None):

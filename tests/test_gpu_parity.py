@@ -643,3 +643,258 @@ def test_ffma_peak_probe_and_launch_counter():
     _lib.check(lib.ksmm_cu_measure_ffma_peak(ctypes.byref(tf), None))
     assert 20.0 < tf.value < 120.0   # B200: 148 SMs x 128 lanes x 2 flop x ~1.9 GHz ~ 72
     kb.check_device()
+
+
+# ---------------------------------------------------------------------------
+# 7. fp8 / bf16 at the sizes of the benchmark specification; KS-ViT-B against dense factors
+# ---------------------------------------------------------------------------
+def test_fp8_batch_first_on_the_tensor_kernel():
+    """fp8-e4m3 batch-first, d = 1, on the tcgen05 kernel (kind::f8f6f4, K-major input operand):
+    every tile configuration that accepts 8-bit inputs, both output types."""
+    for pi, pattern in enumerate([(4, 192, 192, 1), (1, 768, 192, 1), (16, 64, 64, 1), (3, 48, 80, 1)]):
+        a, b, c, d = pattern
+        for batch in (136, 520):
+            x, w = _inputs(pattern, batch, torch.float32, False, seed=440 + pi)
+            wk = kb.generate_factor(a, b, c, d, "kernel", w, torch.float32, DEV)
+            xq, sx = kb.quantize_e4m3(x.to(DEV))
+            wq, sw = kb.quantize_e4m3(wk)
+            ref_full = _oracle(x, w, False)
+            wq_abcd = ko.kernel_format_to_abcd(wq.float().cpu().numpy(), pattern)
+            ref_q = sx * sw * ko.factor_apply(xq.float().cpu().numpy(), wq_abcd, False)
+            for config in range(4):
+                for out_dtype, tol_q in ((torch.bfloat16, 1e-2), (torch.float32, 1e-5)):
+                    y = kb.forward_fp8(xq, wq, False, a, b, c, d, sx, sw, out_dtype=out_dtype,
+                                       algo=_lib.KSMM_ALGO_TC, config=config).float().cpu().numpy()
+                    assert ko.rel_fro_error(y, ref_q) < tol_q, (pattern, batch, config, out_dtype)
+                    assert ko.rel_fro_error(y, ref_full) < 5e-2, (pattern, batch, config, out_dtype)
+    kb.check_device()
+
+
+@pytest.mark.parametrize("batch", [25088, 4096])
+@pytest.mark.parametrize("pattern", [(4, 192, 192, 1), (1, 768, 192, 4), (1, 192, 768, 4)])
+def test_fp8_and_bf16_at_the_specified_batches_against_the_oracle(pattern, batch):
+    """Per-tensor scale amax / 448, values cast after scaling, fp32 accumulation; the error is
+    measured against the fp64 oracle on the unquantised fp32 inputs (sampled columns): 5e-2 for
+    fp8-e4m3, 1e-2 for bf16.  Batch-last for every pattern, batch-first as well where d = 1."""
+    a, b, c, d = pattern
+    g = torch.Generator(device=DEV).manual_seed(91)
+    x = torch.randn((a * c * d, batch), generator=g, device=DEV)
+    w = (torch.rand((a, b, c, d), generator=g, device=DEV) * 2 - 1) / math.sqrt(c)
+    cols = np.unique(np.concatenate([np.arange(0, 4), np.arange(batch - 4, batch),
+                                     np.random.RandomState(6).randint(0, batch, 56)]))
+    cols_t = torch.from_numpy(cols).to(DEV)
+    ref = ko.factor_apply(x[:, cols_t].cpu().numpy(), w.cpu().numpy(), True)
+    wk32 = kb.generate_factor(a, b, c, d, "kernel", w, torch.float32, DEV)
+    xq, sx = kb.quantize_e4m3(x)
+    wq, sw = kb.quantize_e4m3(wk32)
+    layouts = (True, False) if d == 1 else (True,)
+    for bs_last in layouts:
+        xin = xq if bs_last else xq.t().contiguous()
+        y = kb.forward_fp8(xin, wq, bs_last, a, b, c, d, sx, sw, out_dtype=torch.bfloat16)
+        ys = (y[:, cols_t] if bs_last else y[cols_t].t()).float().cpu().numpy()
+        assert ko.rel_fro_error(ys, ref) < 5e-2, (pattern, batch, bs_last, "fp8")
+    wkb = kb.generate_factor(a, b, c, d, "kernel", w, torch.bfloat16, DEV)
+    xb = x.to(torch.bfloat16)
+    for bs_last in (True, False):
+        xin = xb if bs_last else xb.t().contiguous()
+        y = kb.Kernel.forward(xin, wkb, bs_last, a, b, c, d, torch.bfloat16)
+        ys = (y[:, cols_t] if bs_last else y[cols_t].t()).float().cpu().numpy()
+        assert ko.rel_fro_error(ys, ref) < 1e-2, (pattern, batch, bs_last, "bf16")
+    kb.check_device()
+
+
+def _dense_twin(model):
+    """The same KS-ViT-B with every KSLinear replaced by an nn.Linear holding the dense product of
+    its factors (KSLinear.get_dense_product) and its bias."""
+    import copy
+
+    from ksmm_b200.ksvit import KSFeedForward
+    twin = copy.deepcopy(model)
+    for m in twin.modules():
+        if isinstance(m, KSFeedForward):
+            for name in ("fc1", "fc2"):
+                ks = getattr(m, name)
+                lin = torch.nn.Linear(ks.in_size, ks.out_size, bias=True, device=DEV, dtype=torch.float32)
+                with torch.no_grad():
+                    lin.weight.copy_(ks.get_dense_product())
+                    lin.bias.copy_(ks.bias.float().reshape(-1))
+                setattr(m, name, lin)
+            m.fuse_gelu = False
+    return twin.float()
+
+
+def test_ks_vit_b_block_and_forward_against_dense_factors():
+    """KS-ViT-B/16 in fp16 against the same network in fp32 whose MLP projections are dense
+    matrices built from the same factors: one encoder block at 25088 tokens (128 images) and the
+    12-layer forward at 8 images, relative Frobenius error below 1e-2."""
+    from ksmm_b200.ksvit import KSViTB
+    torch.manual_seed(3)
+    model = KSViTB(dtype=torch.float16, device=DEV).eval()
+    twin = _dense_twin(model).eval()
+    with torch.no_grad():
+        x = torch.randn(128, 196, 768, device=DEV)
+        attn, ff = model.layers[0]
+        attn32, ff32 = twin.layers[0]
+        h16 = attn(x.half()) + x.half()
+        y16 = ff(h16) + h16
+        h32 = attn32(x) + x
+        y32 = ff32(h32) + h32
+        err = (torch.linalg.norm(y16.float() - y32) / torch.linalg.norm(y32)).item()
+        assert err < 1e-2, err
+        # the MLP alone, on identical inputs
+        m16 = ff(h16).float()
+        m32 = ff32(h16.float())
+        err = (torch.linalg.norm(m16 - m32) / torch.linalg.norm(m32)).item()
+        assert err < 1e-2, err
+        img = torch.randn(8, 3, 224, 224, device=DEV)
+        l16 = model(img.half()).float()
+        l32 = twin(img)
+        err = (torch.linalg.norm(l16 - l32) / torch.linalg.norm(l32)).item()
+        assert err < 1e-2, err
+    kb.check_device()
+
+
+# ---------------------------------------------------------------------------
+# 8. robustness of the boundary
+# ---------------------------------------------------------------------------
+def test_bounded_wait_runs_out_and_is_reported():
+    """A wait that nothing will ever satisfy gives up after its limit, the kernel returns, and the
+    host reads KSMM_ERR_DEVICE_TIMEOUT from ksmm_cu_check_device; the context stays usable and the
+    flag is cleared by the read."""
+    lib = _lib.load()
+    kb.check_device()                                           # clean start
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _lib.check(lib.ksmm_cu_debug_wait_probe(2_000_000, stream))  # about one millisecond of SM clock
+    st = lib.ksmm_cu_check_device(stream)
+    assert st == _lib.KSMM_ERR_DEVICE_TIMEOUT
+    assert b"code 99" in lib.ksmm_cu_last_error()
+    assert lib.ksmm_cu_check_device(stream) == _lib.KSMM_OK     # cleared
+    x, w = _inputs((2, 96, 48, 1), 96, torch.float16, True, seed=3)
+    y = _run(x, w, (2, 96, 48, 1), True)                        # the device still works
+    assert ko.rel_fro_error(y, _oracle(x, w, True)) < 1e-2
+    kb.check_device()
+
+
+def test_tuner_times_the_conversion_path_and_unaligned_calls_fall_back():
+    """Tuning a batch-first factor that no direct tensor kernel covers must not pin a slower kernel
+    than the default (the conversion path is a candidate), and a choice tuned on aligned buffers
+    must not make a later call on an unaligned buffer fail."""
+    lib = _lib.load()
+    pattern, batch, dtype = (1, 64, 64, 16), 8192, torch.float16
+    a, b, c, d = pattern
+    x, w = _inputs(pattern, batch, dtype, False, seed=33)
+    xg = x.to(DEV)
+    wk = kb.generate_factor(a, b, c, d, "kernel", w, dtype, DEV)
+    out = torch.empty((batch, a * b * d), dtype=dtype, device=DEV)
+    code = kb.kernel.dtype_code(dtype)
+
+    def timed(n=20):
+        kb.forward_ex(xg, wk, False, a, b, c, d, out=out)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            kb.forward_ex(xg, wk, False, a, b, c, d, out=out)
+        e1.record()
+        e1.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    t_default = timed()
+    desc = _lib.ForwardDesc(input=xg.data_ptr(), values=wk.data_ptr(), output=out.data_ptr(), bias=None,
+                            batch=batch, a=a, b=b, c=c, d=d, in_dtype=code, out_dtype=code, bs_last=0,
+                            algo=0, config=-1, alpha=1.0)
+    algo, cfg, ms = ctypes.c_int(), ctypes.c_int(), ctypes.c_float()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _lib.check(lib.ksmm_cu_tune(ctypes.byref(desc), 10, stream, ctypes.byref(algo), ctypes.byref(cfg),
+                                ctypes.byref(ms)))
+    t_tuned = timed()
+    assert t_tuned < 1.25 * t_default, (t_tuned, t_default, algo.value, cfg.value)
+    y = kb.forward_ex(xg, wk, False, a, b, c, d)
+    assert ko.rel_fro_error(y.float().cpu().numpy(), _oracle(x, w, False)) < 1e-2
+    # pin a TMA-based choice for a batch-last problem, then call with a pointer 2 bytes off 16-byte alignment
+    pattern2, batch2 = (2, 64, 32, 1), 256
+    a, b, c, d = pattern2
+    assert lib.ksmm_cu_set_choice(batch2, a, b, c, d, code, code, 1, _lib.KSMM_ALGO_TC, 1) == 0
+    x2, w2 = _inputs(pattern2, batch2, dtype, True, seed=34)
+    wk2 = kb.generate_factor(a, b, c, d, "kernel", w2, dtype, DEV)
+    xs = torch.empty(x2.numel() + 1, dtype=dtype, device=DEV)[1:].view(x2.shape).copy_(x2)
+    y2 = kb.forward_ex(xs, wk2, True, a, b, c, d)
+    assert ko.rel_fro_error(y2.float().cpu().numpy(), _oracle(x2, w2, True)) < 1e-2
+    kb.check_device()
+
+
+def test_layout_scratch_from_the_caller_and_per_stream():
+    """A batch-first d = 16 factor through the conversion path: with the scratch passed in the
+    descriptor the library allocates nothing; without it, calls on two streams get a buffer each
+    and may overlap."""
+    lib = _lib.load()
+    pattern, batch, dtype = (1, 64, 64, 16), 1000, torch.float16
+    a, b, c, d = pattern
+    x, w = _inputs(pattern, batch, dtype, False, seed=35)
+    ref = _oracle(x, w, False)
+    xg = x.to(DEV)
+    wk = kb.generate_factor(a, b, c, d, "kernel", w, dtype, DEV)
+    code = kb.kernel.dtype_code(dtype)
+    out = torch.full((batch, a * b * d), float("nan"), dtype=dtype, device=DEV)
+    desc = _lib.ForwardDesc(input=xg.data_ptr(), values=wk.data_ptr(), output=out.data_ptr(), bias=None,
+                            batch=batch, a=a, b=b, c=c, d=d, in_dtype=code, out_dtype=code, bs_last=0,
+                            algo=0, config=-1, alpha=1.0)
+    need = lib.ksmm_cu_layout_scratch_bytes(ctypes.byref(desc))
+    if need:
+        scratch = torch.empty(need, dtype=torch.uint8, device=DEV)
+        desc.scratch, desc.scratch_bytes = scratch.data_ptr(), need
+    torch.cuda.synchronize()
+    allocs = lib.ksmm_cu_alloc_count()
+    _lib.check(lib.ksmm_cu_forward_ex(ctypes.byref(desc), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    torch.cuda.synchronize()
+    assert lib.ksmm_cu_alloc_count() == allocs
+    assert ko.rel_fro_error(out.float().cpu().numpy(), ref) < 1e-2
+    # two streams, library-owned scratch: interleaved calls, each correct
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    outs = []
+    for rep in range(4):
+        for s in (s1, s2):
+            with torch.cuda.stream(s):
+                outs.append(kb.forward_ex(xg, wk, False, a, b, c, d))
+    torch.cuda.synchronize()
+    for y in outs:
+        assert ko.rel_fro_error(y.float().cpu().numpy(), ref) < 1e-2
+    _lib.check(lib.ksmm_cu_release_scratch())
+    kb.check_device()
+
+
+def test_chain_forward_host_async_tickets():
+    """Several host-buffer calls in flight: each is enqueued at once, results are complete after
+    the wait on its ticket, in any waiting order, and equal the synchronous call's."""
+    lib = _lib.load()
+    pats = [(2, 8, 4, 2), (4, 6, 4, 2)]
+    rng = np.random.RandomState(23)
+    ws = make_weights(pats, rng)
+    wk = [ko.abcd_to_kernel_format(w) for w in ws]
+    vals = (ctypes.c_void_p * 2)(*[w.ctypes.data for w in wk])
+    flat = _lib.int32_array([v for p in pats for v in p])
+    calls = []
+    for ci, (bs_last, batch) in enumerate(((1, 9000), (0, 50), (0, 17000), (1, 300), (0, 8200), (1, 64))):
+        x = torch.from_numpy(rng.standard_normal((16, batch) if bs_last else (batch, 16)).astype(np.float32)).pin_memory()
+        y = torch.full((48, batch) if bs_last else (batch, 48), float("nan")).pin_memory()
+        calls.append((bs_last, batch, x, y))
+    for rep in range(2):
+        tickets = []
+        for bs_last, batch, x, y in calls:
+            y.fill_(float("nan"))
+            t = ctypes.c_uint64(0)
+            _lib.check(lib.ksmm_cu_chain_forward_host_async(x.data_ptr(), vals, y.data_ptr(), None, batch, 2,
+                                                            flat, _lib.KSMM_F32, bs_last, 0, ctypes.byref(t)))
+            assert t.value > 0
+            tickets.append(t.value)
+        assert tickets == sorted(tickets)
+        for idx in (reversed(range(len(calls))) if rep else range(len(calls))):
+            _lib.check(lib.ksmm_cu_host_wait(tickets[idx]))
+            bs_last, batch, x, y = calls[idx]
+            ref = ko.chain_apply(x.numpy(), ws, bool(bs_last))
+            assert ko.rel_fro_error(y.numpy(), ref) < 1e-5, (rep, idx)
+    t = ctypes.c_uint64(7)
+    x0 = calls[1][2]
+    _lib.check(lib.ksmm_cu_chain_forward_host_async(x0.data_ptr(), vals, calls[1][3].data_ptr(), None, 0, 2, flat,
+                                                    _lib.KSMM_F32, 0, 0, ctypes.byref(t)))
+    assert t.value == 0 and lib.ksmm_cu_host_wait(0) == _lib.KSMM_OK          # empty batch
+    assert lib.ksmm_cu_host_wait(1 << 40) == _lib.KSMM_ERR_BAD_ARGUMENT       # never issued

@@ -66,3 +66,26 @@ def test_chain_forward_with_bias_and_activation(ext):
         y2 = ext.chain_forward(x.cuda(), wk, [list(p) for p in pats], 0, bias.cuda(), 1)
     s.synchronize()
     assert torch.equal(y, y2)
+
+
+@pytest.mark.gpu
+def test_chain_forward_validates_shapes_before_anything_runs(ext):
+    """A factor, pattern or input that does not fit is refused by the binding: nothing may reach
+    the kernels with sizes that would make them read or write out of bounds."""
+    x = torch.zeros(16, 768, dtype=torch.float16, device="cuda:0")
+    w0 = torch.zeros(768, 192, dtype=torch.float16, device="cuda:0")
+    w1 = torch.zeros(768, 768, dtype=torch.float16, device="cuda:0")
+    pats = [[4, 192, 192, 1], [1, 768, 192, 4]]
+    ext.chain_forward(x, [w0, w1], pats, 0)
+    with pytest.raises(RuntimeError, match="receives"):
+        ext.chain_forward(x[:, :760].contiguous(), [w0, w1], pats, 0)
+    with pytest.raises(RuntimeError, match="must have shape"):
+        ext.chain_forward(x, [w0, w1[:700].contiguous()], pats, 0)
+    with pytest.raises(RuntimeError, match="receives"):
+        ext.chain_forward(x, [w0, w1], [[4, 192, 192, 1], [1, 768, 96, 4]], 0)
+    with pytest.raises(RuntimeError, match="positive"):
+        ext.chain_forward(x, [w0, w1], [[4, 192, 192, 1], [1, 768, 192, 0]], 0)
+    with pytest.raises(RuntimeError, match="2-D"):
+        ext.chain_forward(x.view(4, 4, 768), [w0, w1], pats, 0)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        ext.chain_forward(x, [w0, w1.cpu()], pats, 0)
