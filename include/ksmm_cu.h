@@ -171,6 +171,64 @@ KSMM_API int ksmm_cu_chain_forward_act(const void* input, const void* const* val
                               int dtype, int bs_last, int activation, void* stream);
 
 /*
+ * Several problems of one pattern in one call ("groups"): the q, k and v
+ * projections of an attention layer apply the same patterns to the same input
+ * (src/ksmm_py/model/get_vit.py:164-215 builds to_q, to_k, to_v from one
+ * pattern list; src/ksmm_py/model/vit.py:477-478 calls them one after the
+ * other on the same x).  Here the `groups` weight sets are stacked,
+ * values = (groups, a*d*c, b), the outputs are stacked, output = (groups,
+ * a*b*d, batch) batch-last or (groups, batch, a*b*d) batch-first (each group's
+ * result is a contiguous tensor), and the input is either one tensor read by
+ * every group (shared_input = 1: the first factor of q/k/v) or stacked like
+ * the output (shared_input = 0: the later factors of the three chains).
+ * `bias` is NULL or groups * a*b*d elements.  The 16-bit tensor-core kernel
+ * runs all groups in one launch, the groups of an input tile side by side so
+ * that the tile is fetched from HBM once; other cases run group by group.
+ */
+KSMM_API int ksmm_cu_grouped_forward(const void* input, const void* values, void* output,
+                                     const void* bias, int64_t batch, int a, int b, int c, int d,
+                                     int dtype, int bs_last, int groups, int shared_input,
+                                     void* stream);
+/* The same for chains: every group applies the same `patterns`; values[f] is
+ * the stacked (groups, a*d*c, b) weight of factor f; the input is shared by
+ * the groups, the output is stacked.  Workspace: groups times
+ * ksmm_cu_chain_workspace_bytes_ex of one chain. */
+KSMM_API int ksmm_cu_grouped_chain_forward(const void* input, const void* const* values, void* output,
+                                           const void* bias, void* workspace, size_t workspace_bytes,
+                                           int64_t batch, int nfactors, const int32_t* patterns,
+                                           int dtype, int bs_last, int groups, void* stream);
+
+/*
+ * Backward of one factor.  The reference has none: Kernel.backward is a stub
+ * that calls an undefined kernel.backward
+ * (src/ksmm_py/layer/kronecker_sparse/kernel.py:323-329).
+ *
+ * ksmm_cu_backward_input: grad_input = K^T grad_output, i.e. the same
+ *   multiplication with pattern (a, c, b, d) and every b x c block
+ *   transposed.  The workspace receives the transposed blocks (a*b*c*d
+ *   elements) and, where the (a, c, b, d) multiplication needs one, its layout
+ *   scratch; ..._workspace_bytes gives the total (the first part is
+ *   mandatory, without the second the library-owned scratch is used).
+ *   grad_output has the forward output's shape, grad_input the input's.
+ * ksmm_cu_backward_weights: grad_values[(i*d + l)*c + k, j] = sum over the
+ *   batch of grad_output[(i, j, l), n] * input[(i, k, l), n], in the kernel
+ *   format and type of the weights (fp32 accumulation).  16-bit batch-last
+ *   and batch-first d = 1 problems run on the tensor cores with the batch
+ *   split over CTAs; they need ..._workspace_bytes of fp32 partial sums
+ *   (without it, and for every other case, a plain FFMA kernel runs).
+ */
+KSMM_API size_t ksmm_cu_backward_input_workspace_bytes(int64_t batch, int a, int b, int c, int d,
+                                                       int dtype, int bs_last);
+KSMM_API int ksmm_cu_backward_input(const void* grad_output, const void* values, void* grad_input,
+                                    void* workspace, size_t workspace_bytes, int64_t batch,
+                                    int a, int b, int c, int d, int dtype, int bs_last, void* stream);
+KSMM_API size_t ksmm_cu_backward_weights_workspace_bytes(int64_t batch, int a, int b, int c, int d,
+                                                         int dtype, int bs_last);
+KSMM_API int ksmm_cu_backward_weights(const void* input, const void* grad_output, void* grad_values,
+                                      void* workspace, size_t workspace_bytes, int64_t batch,
+                                      int a, int b, int c, int d, int dtype, int bs_last, void* stream);
+
+/*
  * ksmm_cu_chain_forward without any allocation: the intermediate activations
  * live in a fixed array of KSMM_CU_STATIC_SCRATCH_BYTES that is part of the
  * library image (each GPU that loads the library carries it until the process
@@ -190,8 +248,10 @@ KSMM_API int ksmm_cu_chain_forward_act(const void* input, const void* const* val
  *     the call never falls back to an allocation.  The default size holds one
  *     38.5 MB intermediate, e.g. the two-factor KS-ViT-B MLP layers in fp16 or
  *     the batch-last README layer in fp32 at batch 25088;
- *   - the first call on a device resolves the array's device address; make
- *     that call before starting a stream capture;
+ *   - the first call on a device resolves the array's device address, which
+ *     makes the driver load the part of the library image that holds the
+ *     array (its free-memory reading drops by the array's size then, once);
+ *     make that call before starting a stream capture;
  *   - all calls on one GPU share the array, and it keeps the previous call's
  *     contents: calls that may overlap on the GPU (different streams) race and
  *     must be serialised by the caller.  Nothing has to be cleared between

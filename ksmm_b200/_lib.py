@@ -37,6 +37,9 @@ EXPORTS = (
     "ksmm_cu_layout_scratch_bytes", "ksmm_cu_release_scratch", "ksmm_cu_chain_workspace_bytes_ex",
     "ksmm_cu_alloc_count", "ksmm_cu_debug_wait_probe",
     "ksmm_cu_chain_forward_host_async", "ksmm_cu_host_wait",
+    "ksmm_cu_grouped_forward", "ksmm_cu_grouped_chain_forward",
+    "ksmm_cu_backward_input_workspace_bytes", "ksmm_cu_backward_input",
+    "ksmm_cu_backward_weights_workspace_bytes", "ksmm_cu_backward_weights",
 )
 
 
@@ -99,6 +102,19 @@ def load():
     lib.ksmm_cu_chain_forward_host_async.argtypes = [vp, ctypes.POINTER(vp), vp, vp, i64, i32,
                                                      ctypes.POINTER(ctypes.c_int32), i32, i32, i32,
                                                      ctypes.POINTER(ctypes.c_uint64)]
+    lib.ksmm_cu_grouped_forward.restype = i32
+    lib.ksmm_cu_grouped_forward.argtypes = [vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, vp]
+    lib.ksmm_cu_grouped_chain_forward.restype = i32
+    lib.ksmm_cu_grouped_chain_forward.argtypes = [vp, ctypes.POINTER(vp), vp, vp, vp, ctypes.c_size_t, i64,
+                                                  i32, ctypes.POINTER(ctypes.c_int32), i32, i32, i32, vp]
+    for name in ("ksmm_cu_backward_input_workspace_bytes", "ksmm_cu_backward_weights_workspace_bytes"):
+        fn = getattr(lib, name)
+        fn.restype = ctypes.c_size_t
+        fn.argtypes = [i64, i32, i32, i32, i32, i32, i32]
+    for name in ("ksmm_cu_backward_input", "ksmm_cu_backward_weights"):
+        fn = getattr(lib, name)
+        fn.restype = i32
+        fn.argtypes = [vp, vp, vp, vp, ctypes.c_size_t, i64, i32, i32, i32, i32, i32, i32, vp]
     lib.ksmm_cu_host_wait.restype = i32
     lib.ksmm_cu_host_wait.argtypes = [ctypes.c_uint64]
     lib.ksmm_cu_num_configs.restype = i32

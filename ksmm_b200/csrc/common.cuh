@@ -147,6 +147,11 @@ struct Problem {
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
   int no_alloc = 0;
+  // groups > 1: that many problems of this pattern in one call.  Weights (groups, a*d*c, b) and
+  // outputs (groups, ...) are stacked; the input is one tensor shared by all groups, or stacked
+  // like the output when group_shared_input == 0.  The bias, if any, holds groups * a*b*d elements.
+  int groups = 1;
+  int group_shared_input = 1;
 };
 
 // element-wise epilogue function (ksmm_activation_t)

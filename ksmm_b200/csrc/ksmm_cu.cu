@@ -55,6 +55,11 @@ bool ffma_tma_first_supported(const Problem& p, bool check_pointers);
 int ffma_tma_first_launch(const Problem& p, cudaStream_t stream);
 int launch_transpose(const void* in, void* out, int64_t rows, int64_t cols, int es,
                      cudaStream_t stream);
+// backward.cu
+int launch_transpose_blocks(const void* in, void* out, int64_t nblk, int c, int b, int es, cudaStream_t stream);
+size_t wgrad_workspace_bytes(const Problem& p);
+int wgrad_launch(const Problem& p, const void* grad_out, void* workspace, size_t workspace_bytes,
+                 cudaStream_t stream);
 static constexpr int kFfmaTmaWide = 6, kFfmaTmaNarrow = 7, kFfmaTmaFirst = 8, kNumFfmaConfigs = 9;
 
 static int simt_launch_raw(const Problem& p, int config, cudaStream_t stream) {
@@ -702,6 +707,156 @@ int ksmm_cu_chain_forward_act(const void* input, const void* const* values, void
   return chain_forward_impl(input, values, output, bias, workspace, workspace_bytes, /*no_alloc=*/0, batch,
                             nfactors, patterns, dtype, bs_last, activation,
                             static_cast<cudaStream_t>(stream));
+}
+
+// One factor for `groups` stacked problems: one grouped launch where a kernel has that form,
+// else one dispatch per group.
+static int grouped_factor(Problem p, int groups, int shared_input, cudaStream_t stream) {
+  const size_t es = dtype_size(p.in_dtype), os = dtype_size(p.out_dtype);
+  const size_t in_elems = static_cast<size_t>(p.a) * p.c * p.d * p.batch;
+  const size_t out_elems = static_cast<size_t>(p.a) * p.b * p.d * p.batch;
+  const size_t w_elems = static_cast<size_t>(p.a) * p.b * p.c * p.d;
+  int st = check_problem(p);
+  if (st != KSMM_OK) return st;
+  if (p.batch == 0) return KSMM_OK;
+  if (groups > 1) {
+    Problem g = p;
+    g.groups = groups;
+    g.group_shared_input = shared_input;
+    Choice ch;
+    const bool pinned = lookup_choice(p, &ch);  // a tuned choice for the single problem wins
+    const int cfg = tc_default_config(g);
+    if (!pinned && cfg >= 0) return tc_launch(g, cfg, stream);
+  }
+  for (int q = 0; q < groups; ++q) {
+    Problem g = p;
+    g.in = static_cast<const char*>(p.in) + (shared_input ? 0 : q * in_elems * es);
+    g.w = static_cast<const char*>(p.w) + q * w_elems * es;
+    g.out = static_cast<char*>(p.out) + q * out_elems * os;
+    g.bias = p.bias ? static_cast<const char*>(p.bias) + q * static_cast<size_t>(p.a) * p.b * p.d * os : nullptr;
+    st = dispatch(g, KSMM_ALGO_AUTO, -1, stream);
+    if (st != KSMM_OK) return st;
+  }
+  return KSMM_OK;
+}
+
+int ksmm_cu_grouped_forward(const void* input, const void* values, void* output, const void* bias,
+                            int64_t batch, int a, int b, int c, int d, int dtype, int bs_last,
+                            int groups, int shared_input, void* stream) {
+  if (groups < 1) return set_error(KSMM_ERR_BAD_ARGUMENT, "groups must be at least 1");
+  if (dtype == KSMM_F8E4M3)
+    return set_error(KSMM_ERR_UNSUPPORTED, "grouped calls run in fp32, fp16 or bf16");
+  Problem p;
+  p.in = input; p.w = values; p.out = output; p.bias = bias;
+  p.batch = batch; p.a = a; p.b = b; p.c = c; p.d = d;
+  p.in_dtype = dtype; p.out_dtype = dtype; p.bs_last = bs_last; p.alpha = 1.f;
+  return grouped_factor(p, groups, shared_input ? 1 : 0, static_cast<cudaStream_t>(stream));
+}
+
+int ksmm_cu_grouped_chain_forward(const void* input, const void* const* values, void* output,
+                                  const void* bias, void* workspace, size_t workspace_bytes,
+                                  int64_t batch, int nfactors, const int32_t* patterns, int dtype,
+                                  int bs_last, int groups, void* stream) {
+  if (groups < 1) return set_error(KSMM_ERR_BAD_ARGUMENT, "groups must be at least 1");
+  int st = check_chain(nfactors, patterns, values, dtype, 0);
+  if (st != KSMM_OK) return st;
+  if (bs_last != 0 && bs_last != 1) return set_error(KSMM_ERR_BAD_ARGUMENT, "bs_last must be 0 or 1");
+  if (batch < 0) return set_error(KSMM_ERR_BAD_ARGUMENT, "negative batch");
+  // per group: the intermediates of one chain; whatever follows the groups' intermediates is
+  // layout scratch for the factors that run group by group
+  const size_t inter1 = chain_intermediate_bytes(nfactors, patterns, batch, dtype);
+  const size_t inter = inter1 * groups;
+  if (inter > 0 && (!workspace || workspace_bytes < inter))
+    return set_error(KSMM_ERR_WORKSPACE, "grouped chain workspace: need %zu bytes, got %zu", inter,
+                     workspace_bytes);
+  const size_t half1 = nfactors == 2 ? inter1 : inter1 / 2;  // one buffer of one group
+  char* ws = static_cast<char*>(workspace);
+  const void* cur = input;
+  for (int f = 0; f < nfactors; ++f) {
+    const int32_t* q = patterns + 4 * f;
+    const bool last = (f + 1 == nfactors);
+    // the groups' copies of intermediate buffer (f & 1) are contiguous: a stacked tensor
+    void* dst = last ? output : ws + static_cast<size_t>(f & 1) * half1 * groups;
+    Problem p;
+    p.in = cur; p.w = values[f]; p.out = dst; p.bias = last ? bias : nullptr;
+    p.batch = batch; p.a = q[0]; p.b = q[1]; p.c = q[2]; p.d = q[3];
+    p.in_dtype = dtype; p.out_dtype = dtype; p.bs_last = bs_last; p.alpha = 1.f;
+    if (workspace && workspace_bytes > inter) {
+      p.scratch = ws + inter;
+      p.scratch_bytes = workspace_bytes - inter;
+    }
+    st = grouped_factor(p, groups, f == 0 ? 1 : 0, static_cast<cudaStream_t>(stream));
+    if (st != KSMM_OK) return st;
+    cur = dst;
+  }
+  return KSMM_OK;
+}
+
+// ---- backward of one factor -------------------------------------------------------------------
+static Problem backward_problem(const void* in, const void* w, void* out, int64_t batch, int a, int b, int c,
+                                int d, int dtype, int bs_last) {
+  Problem p;
+  p.in = in; p.w = w; p.out = out; p.bias = nullptr;
+  p.batch = batch; p.a = a; p.b = b; p.c = c; p.d = d;
+  p.in_dtype = dtype; p.out_dtype = dtype; p.bs_last = bs_last; p.alpha = 1.f;
+  return p;
+}
+
+static int check_backward(const Problem& p) {
+  if (p.in_dtype == KSMM_F8E4M3)
+    return set_error(KSMM_ERR_UNSUPPORTED, "the backward passes run in fp32, fp16 or bf16");
+  return check_problem(p);
+}
+
+size_t ksmm_cu_backward_input_workspace_bytes(int64_t batch, int a, int b, int c, int d, int dtype,
+                                              int bs_last) {
+  if (batch <= 0 || a <= 0 || b <= 0 || c <= 0 || d <= 0) return 0;
+  // the transposed blocks, then the layout scratch of the (a, c, b, d) multiplication, if any
+  const size_t wt = align_up(static_cast<size_t>(a) * b * c * d * dtype_size(dtype), 256);
+  Problem q = backward_problem(reinterpret_cast<void*>(256), reinterpret_cast<void*>(256),
+                               reinterpret_cast<void*>(256), batch, a, c, b, d, dtype, bs_last);
+  if (check_backward(q) != KSMM_OK) return 0;
+  return wt + scratch_need(q, auto_choice(q));
+}
+
+int ksmm_cu_backward_input(const void* grad_output, const void* values, void* grad_input, void* workspace,
+                           size_t workspace_bytes, int64_t batch, int a, int b, int c, int d, int dtype,
+                           int bs_last, void* stream) {
+  // dX = K^T dY: pattern (a, c, b, d) with every block transposed
+  Problem q = backward_problem(grad_output, nullptr, grad_input, batch, a, c, b, d, dtype, bs_last);
+  q.w = workspace;
+  int st = check_backward(q);
+  if (st != KSMM_OK) return st;
+  if (!values) return set_error(KSMM_ERR_BAD_ARGUMENT, "null weights");
+  if (batch == 0) return KSMM_OK;
+  const size_t wt = align_up(static_cast<size_t>(a) * b * c * d * dtype_size(dtype), 256);
+  if (!workspace || workspace_bytes < wt)
+    return set_error(KSMM_ERR_WORKSPACE, "backward workspace: need at least %zu bytes, got %zu", wt,
+                     workspace_bytes);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  st = launch_transpose_blocks(values, workspace, static_cast<int64_t>(a) * d, c, b, dtype_size(dtype), s);
+  if (st != KSMM_OK) return st;
+  if (workspace_bytes > wt) {
+    q.scratch = static_cast<char*>(workspace) + wt;
+    q.scratch_bytes = workspace_bytes - wt;
+  }
+  return dispatch(q, KSMM_ALGO_AUTO, -1, s);
+}
+
+size_t ksmm_cu_backward_weights_workspace_bytes(int64_t batch, int a, int b, int c, int d, int dtype,
+                                                int bs_last) {
+  if (batch <= 0 || a <= 0 || b <= 0 || c <= 0 || d <= 0) return 0;
+  Problem p = backward_problem(nullptr, nullptr, nullptr, batch, a, b, c, d, dtype, bs_last);
+  return wgrad_workspace_bytes(p);
+}
+
+int ksmm_cu_backward_weights(const void* input, const void* grad_output, void* grad_values, void* workspace,
+                             size_t workspace_bytes, int64_t batch, int a, int b, int c, int d, int dtype,
+                             int bs_last, void* stream) {
+  Problem p = backward_problem(input, grad_output, grad_values, batch, a, b, c, d, dtype, bs_last);
+  int st = check_backward(p);
+  if (st != KSMM_OK) return st;
+  return wgrad_launch(p, grad_output, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int ksmm_cu_chain_forward_static(const void* input, const void* const* values, void* output,

@@ -74,6 +74,11 @@ struct Params {
   int* status;
   int act;         // ksmm_activation_t
   int rg_d, rg_c;  // batch-first, 16-bit: store regrouped for the next factor's (c, d); 0 = natural order
+  // Grouped launch: `groups` problems of the same pattern in one grid (weights and outputs of the
+  // groups are stacked; the input is shared, or stacked as well when gx = 1).  A CTA's j tile slot
+  // encodes (group, j tile), so the groups of one input tile run at the same time and share it in L2.
+  int groups, gx;
+  int tiles_jg;    // tiles_j * groups
 };
 
 // WRES = true  ("weight-stationary"): the CTA's weight tile (all NWC k chunks of
@@ -161,11 +166,19 @@ __global__ void __launch_bounds__(kThreads, 1)
   // input tile in L2; the weight tile changes only when the block changes.
   const uint32_t d = P.d;
   const int nk = P.nk;
-  const int tj = static_cast<int>(blockIdx.x % P.tiles_j);
-  const uint32_t rc = blockIdx.x / P.tiles_j;
+  const int tjg = static_cast<int>(blockIdx.x % P.tiles_jg);
+  const int grp_id = tjg / P.tiles_j;
+  const int tj = tjg % P.tiles_j;
+  const uint32_t rc = blockIdx.x / P.tiles_jg;
   const uint32_t row_begin = static_cast<uint32_t>(static_cast<uint64_t>(rc) * P.rows / P.row_groups);
   const uint32_t row_end = static_cast<uint32_t>(static_cast<uint64_t>(rc + 1) * P.rows / P.row_groups);
   const int j0 = tj * (BS_LAST ? 128 : NT);
+  // offsets of this CTA's group in the stacked tensors: weight blocks, block rows of a batch-last
+  // input / output, batch rows of a batch-first input / output, bias elements
+  const int wblk0 = grp_id * P.a * P.d;
+  const int xi0 = P.gx ? grp_id * P.a : 0, yi0 = grp_id * P.a;
+  const int xn0 = P.gx ? grp_id * static_cast<int>(P.batch) : 0, yn0 = grp_id * static_cast<int>(P.batch);
+  const int64_t bias0 = static_cast<int64_t>(grp_id) * P.a * P.b * P.d;
 
   if (warp == 0) {
     // ===================== TMA producer =====================
@@ -188,7 +201,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
             for (int wb = 0; wb < (BS_LAST ? 128 : NT) / C::NBOX; ++wb)
               tma_load_3d(wres0 + kc * C::WB + wb * KC * 128, &tmW, wfull_bar, j0 + wb * C::NBOX,
-                          kc * KC, blk);
+                          kc * KC, blk + wblk0);
           }
           cur_blk = blk;
         }
@@ -202,14 +215,14 @@ __global__ void __launch_bounds__(kThreads, 1)
           if constexpr (BS_LAST) {
 #pragma unroll
             for (int xb = 0; xb < NT / C::NBOX; ++xb)
-              tma_load_4d(dst + xb * KC * 128, &tmX, bar, n0 + xb * C::NBOX, l, kc * KC, i);
+              tma_load_4d(dst + xb * KC * 128, &tmX, bar, n0 + xb * C::NBOX, l, kc * KC, i + xi0);
           } else {
-            tma_load_3d(dst, &tmX, bar, kc * KC, i, n0);
+            tma_load_3d(dst, &tmX, bar, kc * KC, i, n0 + xn0);
           }
           if constexpr (!WRES) {
 #pragma unroll
             for (int wb = 0; wb < (BS_LAST ? 128 : NT) / C::NBOX; ++wb)
-              tma_load_3d(dst + C::XB + wb * KC * 128, &tmW, bar, j0 + wb * C::NBOX, kc * KC, blk);
+              tma_load_3d(dst + C::XB + wb * KC * 128, &tmW, bar, j0 + wb * C::NBOX, kc * KC, blk + wblk0);
           }
           KSMM_TRACE(0, 5);
           if (++si == SX) { si = 0; sph ^= 1u; }
@@ -310,7 +323,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int col_limit = BS_LAST ? static_cast<int>(min(P.batch - n0, static_cast<int64_t>(NT))) : P.b - j0;
       float bias_row = 0.f;
       if (BS_LAST && P.bias != nullptr && q * 32 + lane < row_limit)
-        bias_row = bias_at(P.bias, (static_cast<int64_t>(i) * P.b + j0 + q * 32 + lane) * d + l,
+        bias_row = bias_at(P.bias, bias0 + (static_cast<int64_t>(i) * P.b + j0 + q * 32 + lane) * d + l,
                            P.out_dtype);
       if (warp_active) {
 #pragma unroll 1
@@ -332,7 +345,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (!BS_LAST && P.bias != nullptr) {
               const int col = cbi * C::CB + (OS == 2 ? 2 * lane : lane);
               if (col < col_limit) {
-                const int64_t e0 = static_cast<int64_t>(i) * P.b + j0 + col;
+                const int64_t e0 = bias0 + static_cast<int64_t>(i) * P.b + j0 + col;
                 if constexpr (OS == 2) {
                   // (col_limit is even for 16-bit outputs: b * 2 bytes is a multiple of 16)
                   const uint16_t* bp = static_cast<const uint16_t*>(P.bias) + e0;
@@ -418,13 +431,13 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (tron) KSMM_TRACE(trole, 25);
           if (lane == 0) {
             if constexpr (BS_LAST) {
-              tma_store_4d(&tmY, stg, n0 + cbi * C::CB, l, j0 + q * 32, i);
+              tma_store_4d(&tmY, stg, n0 + cbi * C::CB, l, j0 + q * 32, i + yi0);
             } else if (P.rg_d != 0) {
               // output seen as (k2, l2, i2, n): the tile starts at feature m0 = i*b + j0 + 64*cbi
               const int m0 = i * P.b + j0 + cbi * C::CB, seg = P.rg_c * P.rg_d;
               tma_store_4d(&tmY, stg, (m0 % seg) / P.rg_d, 0, m0 / seg, n0 + q * 32);
             } else {
-              tma_store_3d(&tmY, stg, j0 + cbi * C::CB, i, n0 + q * 32);
+              tma_store_3d(&tmY, stg, j0 + cbi * C::CB, i, n0 + q * 32 + yn0);
             }
             bulk_commit();
           }
@@ -561,11 +574,12 @@ static int launch_one(const Problem& p, cudaStream_t stream) {
     attr_set[dev] = true;
   }
   const uint64_t a = p.a, b = p.b, c = p.c, d = p.d, B = p.batch;
+  const uint64_t G = p.groups > 1 ? p.groups : 1, GX = (G > 1 && !p.group_shared_input) ? G : 1;
   CUtensorMap tmX, tmW, tmY;
   int st;
   {
-    // weights (a*d*c, b) row-major seen as (b, c, a*d)
-    const uint64_t dims[3] = {b, c, a * d};
+    // weights (a*d*c, b) row-major seen as (b, c, a*d); the groups' weights follow one another
+    const uint64_t dims[3] = {b, c, G * a * d};
     const uint64_t str[3] = {1, b, c * b};
     const uint32_t box[3] = {static_cast<uint32_t>(C::NBOX), static_cast<uint32_t>(KC), 1};
     if ((st = encode_map(&tmW, p.in_dtype, 3, p.w, dims, str, box)) != KSMM_OK) return st;
@@ -580,6 +594,8 @@ static int launch_one(const Problem& p, cudaStream_t stream) {
   P.act = p.activation;
   P.rg_d = (!BS_LAST && OS == 2) ? p.out_regroup_d : 0;
   P.rg_c = p.out_regroup_c;
+  P.groups = static_cast<int>(G);
+  P.gx = GX > 1 ? 1 : 0;
   P.status = status_word();
   if (!P.status) return set_error(KSMM_ERR_CUDA, "cannot resolve the device status word");
   const uint32_t fmt = p.in_dtype == KSMM_BF16 ? 1u : 0u;  // f16 / e4m3 = 0, bf16 = 1
@@ -587,18 +603,18 @@ static int launch_one(const Problem& p, cudaStream_t stream) {
                    (static_cast<uint32_t>(NT >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
   if (BS_LAST) {
     idesc |= (1u << 15);  // A (weights) is MN-major as well
-    const uint64_t xd[4] = {B, d, c, a};
+    const uint64_t xd[4] = {B, d, c, GX * a};
     const uint64_t xs[4] = {1, B, d * B, c * d * B};
     const uint32_t xb[4] = {static_cast<uint32_t>(C::NBOX), 1, static_cast<uint32_t>(KC), 1};
     if ((st = encode_map(&tmX, p.in_dtype, 4, p.in, xd, xs, xb)) != KSMM_OK) return st;
-    const uint64_t yd[4] = {B, d, b, a};
+    const uint64_t yd[4] = {B, d, b, G * a};
     const uint64_t ys[4] = {1, B, d * B, b * d * B};
     const uint32_t yb[4] = {static_cast<uint32_t>(C::CB), 1, 32, 1};  // one epilogue warp's rows
     if ((st = encode_map(&tmY, p.out_dtype, 4, p.out, yd, ys, yb)) != KSMM_OK) return st;
     P.tiles_n = static_cast<int>((B + NT - 1) / NT);
     P.tiles_j = static_cast<int>((b + 127) / 128);
   } else {
-    const uint64_t xd[3] = {c, a, B};
+    const uint64_t xd[3] = {c, a, GX * B};
     const uint64_t xs[3] = {1, c, a * c};
     const uint32_t xb[3] = {static_cast<uint32_t>(KC), 1, 128};
     if ((st = encode_map(&tmX, p.in_dtype, 3, p.in, xd, xs, xb)) != KSMM_OK) return st;
@@ -610,7 +626,7 @@ static int launch_one(const Problem& p, cudaStream_t stream) {
       const uint32_t yb[4] = {static_cast<uint32_t>(C::CB / d2), static_cast<uint32_t>(d2), 1, 32};
       if ((st = encode_map(&tmY, p.out_dtype, 4, p.out, yd, ys, yb, false)) != KSMM_OK) return st;
     } else {
-      const uint64_t yd[3] = {b, a, B};
+      const uint64_t yd[3] = {b, a, G * B};
       const uint64_t ys[3] = {1, b, a * b};
       const uint32_t yb[3] = {static_cast<uint32_t>(C::CB), 1, 32};
       if ((st = encode_map(&tmY, p.out_dtype, 3, p.out, yd, ys, yb)) != KSMM_OK) return st;
@@ -621,16 +637,17 @@ static int launch_one(const Problem& p, cudaStream_t stream) {
   P.idesc = idesc;
   const int sms = num_sms();
   if (sms <= 0) return set_error(KSMM_ERR_NO_DEVICE, "no CUDA device");
+  P.tiles_jg = P.tiles_j * static_cast<int>(G);
   const int64_t rows = static_cast<int64_t>(P.tiles_n) * p.a * p.d;
-  if (rows <= 0 || rows > 0x7fffffffLL || P.tiles_j > sms)
+  if (rows <= 0 || rows > 0x7fffffffLL || P.tiles_jg > sms)
     return set_error(KSMM_ERR_UNSUPPORTED,
                      "tensor-core family: %lld rows x %d j tiles exceed the work-split limits",
-                     static_cast<long long>(rows), P.tiles_j);
+                     static_cast<long long>(rows), P.tiles_jg);
   P.rows = static_cast<uint32_t>(rows);
-  int64_t groups = sms / P.tiles_j;
+  int64_t groups = sms / P.tiles_jg;
   if (groups > rows) groups = rows;
   P.row_groups = static_cast<uint32_t>(groups);
-  const unsigned grid = static_cast<unsigned>(groups * P.tiles_j);
+  const unsigned grid = static_cast<unsigned>(groups * P.tiles_jg);
   kern<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tmX, tmW, tmY, P);
   count_launch();
   cudaError_t err = cudaGetLastError();
@@ -685,6 +702,16 @@ int tc_num_configs() { return tc::kNumConfigs; }
 
 bool tc_config_supported(const Problem& p, int config, bool check_pointers) {
   if (config < 0 || config >= tc::kNumConfigs) return false;
+  if (p.groups > 1) {
+    // grouped launches exist in the 16-bit / 8-bit kernel of this file only; batch-first outputs of
+    // the groups follow one another row-wise, so a partly filled last store box would spill into
+    // the next group: the batch has to be a whole number of 32-row boxes
+    if (p.in_dtype == KSMM_F32 || (!p.bs_last && (p.d != 1 || p.batch % 32 != 0))) return false;
+    if (p.out_regroup_d || p.in_regrouped) return false;
+    if (static_cast<int64_t>(p.groups) * p.batch > 0x7fffffffLL ||
+        static_cast<int64_t>(p.groups) * p.a * p.d > 0x7fffffffLL)
+      return false;
+  }
   if (p.in_dtype == KSMM_F32) return config >= 0 && config <= 3 && tc_f32x3_supported(p, check_pointers);
   if (!p.bs_last && p.d != 1)
     return config == 0 ? tc_bsfirst_d_supported(p, check_pointers)

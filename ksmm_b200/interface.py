@@ -60,8 +60,12 @@ class KSLinear(nn.Module):
 
     def __init__(self, patterns, weights=None, bias=True, algo="kernel",
                  dtype: torch.dtype = torch.float16, bs_last: bool = False, vsize: int = 4,
-                 device: str = "cuda", fuse_chain: bool = True, activation=None):
+                 device: str = "cuda", fuse_chain: bool = True, activation=None,
+                 requires_grad: bool = False):
         super().__init__()
+        # `requires_grad` is an addition as well: the reference's kernel path is inference-only (its
+        # backward is a stub).  With trainable factors the forward runs factor by factor through
+        # autograd (FactorFunction: dX and dW kernels of the library)
         # `activation` (None, "gelu", "relu") is an addition to the reference's signature: it is applied
         # after the bias inside the last factor's epilogue instead of as a separate kernel
         if activation not in (None, "gelu", "relu"):
@@ -98,7 +102,7 @@ class KSLinear(nn.Module):
         parameters = []
         for p, w in zip(self.patterns, self.weights):
             factor = generate_factor(*p, "kernel", w, store_dtype, device)
-            parameters.append(nn.Parameter(factor, requires_grad=False))
+            parameters.append(nn.Parameter(factor, requires_grad=bool(requires_grad) and not self.is_fp8))
         self.factors = nn.ParameterList(parameters)
         self._fp8_cache = None
 
@@ -108,7 +112,7 @@ class KSLinear(nn.Module):
             shape = (self.out_size, 1) if self.bs_last else (self.out_size,)
             self.bias = nn.Parameter(
                 torch.empty(*shape, device=device).uniform_(-bound, bound).to(bias_dtype),
-                requires_grad=False)
+                requires_grad=bool(requires_grad) and not self.is_fp8)
         else:
             self.register_parameter("bias", None)
         self._workspace = None
@@ -128,6 +132,19 @@ class KSLinear(nn.Module):
                 last = idx + 1 == self.num_mat
                 y = _k.forward_fp8(xq, wq, self.bs_last, *p, sx, sw, out_dtype=torch.bfloat16,
                                    bias=bias if last else None)
+            if self.activation == "gelu":
+                y = torch.nn.functional.gelu(y)
+            elif self.activation == "relu":
+                y = torch.relu(y)
+            return y
+        if torch.is_grad_enabled() and (x.requires_grad or any(f.requires_grad for f in self.factors)
+                                        or (self.bias is not None and self.bias.requires_grad)):
+            # differentiable path: one autograd node per factor; bias and activation are torch ops
+            y = x
+            for p, f in zip(self.patterns, self.factors):
+                y = _k.FactorFunction.apply(y, f, self.bs_last, *p)
+            if self.bias is not None:
+                y = y + (self.bias.reshape(-1, 1) if self.bs_last else self.bias.reshape(1, -1))
             if self.activation == "gelu":
                 y = torch.nn.functional.gelu(y)
             elif self.activation == "relu":
@@ -192,3 +209,52 @@ class KSLinear(nn.Module):
         return "in_size={}, out_size={}, num_mat={}, patterns={}, algo={}, bias={}".format(
             self.in_size, self.out_size, self.num_mat, self.patterns, self.algo,
             self.bias is not None)
+
+
+class KSLinearGroup(nn.Module):
+    """Several ``KSLinear`` layers with the same patterns applied to the same input in one library
+    call: the q, k and v projections of an attention layer, which the reference builds from one
+    pattern list and calls one after the other on the same tensor
+    (src/ksmm_py/model/get_vit.py:164-215, src/ksmm_py/model/vit.py:477-478).  ``forward`` returns
+    one output per layer.  The layers stay ordinary ``KSLinear`` modules (their parameters are the
+    source of truth); the stacked copy of their factors that the grouped kernel reads is rebuilt
+    whenever a factor changes."""
+
+    def __init__(self, layers):
+        super().__init__()
+        layers = list(layers)
+        if not layers:
+            raise ValueError("need at least one layer")
+        first = layers[0]
+        for l in layers:
+            if not isinstance(l, KSLinear):
+                raise TypeError("KSLinearGroup holds KSLinear layers")
+            if l.patterns != first.patterns or l.dtype != first.dtype or l.bs_last != first.bs_last \
+                    or l.is_fp8 or l.activation is not None or (l.bias is None) != (first.bias is None):
+                raise ValueError("the layers of a group share patterns, dtype, layout and bias setting "
+                                 "(fp8 layers and fused activations are not grouped)")
+        self.layers = nn.ModuleList(layers)
+        self._stacked = None
+        self._versions = None
+
+    def _stack(self):
+        versions = [(f._version, f.data_ptr()) for l in self.layers for f in l.factors]
+        if self.layers[0].bias is not None:
+            versions += [(l.bias._version, l.bias.data_ptr()) for l in self.layers]
+        if self._stacked is None or versions != self._versions:
+            nf = self.layers[0].num_mat
+            factors = [torch.cat([l.factors[f].data for l in self.layers], dim=0).contiguous() for f in range(nf)]
+            bias = None
+            if self.layers[0].bias is not None:
+                bias = torch.cat([l.bias.data.reshape(-1) for l in self.layers]).contiguous()
+            self._stacked, self._versions = (factors, bias), versions
+        return self._stacked
+
+    def forward(self, tensor):
+        first = self.layers[0]
+        x = first.pre_process(tensor)
+        if x.dtype != first.dtype:
+            raise TypeError(f"input dtype {x.dtype} differs from the layers' {first.dtype}")
+        factors, bias = self._stack()
+        out = _k.grouped_chain_forward(x, factors, first.patterns, first.bs_last, len(self.layers), bias=bias)
+        return tuple(first.post_process(tensor, out[g]) for g in range(len(self.layers)))

@@ -96,6 +96,13 @@ def forward_ex(input, factor, bs_last, a, b, c, d, *, out_dtype=None, alpha=1.0,
         bias=bias.data_ptr() if bias is not None else None, batch=batch, a=a, b=b, c=c, d=d,
         in_dtype=dtype_code(input.dtype), out_dtype=dtype_code(out_dtype), bs_last=bs_last,
         algo=algo, config=config, alpha=float(alpha), activation=_lib.ACTIVATIONS[activation])
+    # A factor that runs through a layout conversion needs room for its transposed copies.  It comes
+    # from torch's allocator (stream-ordered, and legal inside a CUDA-graph capture), so that the
+    # library never has to grow a buffer of its own on behalf of a Python caller.
+    need = lib.ksmm_cu_layout_scratch_bytes(ctypes.byref(desc))
+    if need:
+        scratch = torch.empty(need, dtype=torch.uint8, device=input.device)
+        desc.scratch, desc.scratch_bytes = scratch.data_ptr(), need
     with torch.cuda.device(input.device):
         _lib.check(lib.ksmm_cu_forward_ex(ctypes.byref(desc), _stream_ptr(input.device)))
     return out
@@ -182,6 +189,126 @@ def chain_forward(input, factors, patterns, bs_last, bias=None, workspace=None, 
             workspace.numel() * workspace.element_size() if workspace is not None else 0,
             batch, nf, pat, code, bs_last, _lib.ACTIVATIONS[activation], _stream_ptr(input.device)))
     return out
+
+
+def grouped_chain_forward(input, stacked_factors, patterns, bs_last, groups, bias=None):
+    """``groups`` chains with the same ``patterns`` on one shared input (``ksmm_cu_grouped_chain_forward``):
+    ``stacked_factors[f]`` is the (groups * a*d*c, b) concatenation of the groups' kernel-format
+    factors f.  Returns the stacked output (groups, out, batch) / (groups, batch, out); ``out[g]`` is
+    group g's result, a contiguous tensor."""
+    lib = _lib.load()
+    bs_last = int(bool(bs_last))
+    nf = len(patterns)
+    if nf == 0 or len(stacked_factors) != nf or groups < 1:
+        raise ValueError("need one stacked factor per pattern and at least one group")
+    a0, b0, c0, d0 = patterns[0]
+    if input.dim() != 2 or not input.is_cuda or not input.is_contiguous():
+        raise ValueError("input must be a contiguous 2-D CUDA tensor")
+    if (input.shape[0] if bs_last else input.shape[1]) != a0 * c0 * d0:
+        raise ValueError(f"input has the wrong number of features for pattern {tuple(patterns[0])}")
+    feats = a0 * c0 * d0
+    for f, (p, w) in enumerate(zip(patterns, stacked_factors)):
+        a, b, c, d = p
+        if a * c * d != feats:
+            raise ValueError(f"factor {f} expects {a * c * d} features but receives {feats}")
+        if tuple(w.shape) != (groups * a * d * c, b) or w.dtype != input.dtype or not w.is_contiguous() \
+                or w.device != input.device:
+            raise ValueError(f"stacked factor {f} must be a contiguous ({groups * a * d * c}, {b}) tensor of {input.dtype}")
+        feats = a * b * d
+    batch = input.shape[1] if bs_last else input.shape[0]
+    out = torch.empty((groups, feats, batch) if bs_last else (groups, batch, feats), dtype=input.dtype,
+                      device=input.device)
+    if bias is not None and (bias.numel() != groups * feats or bias.dtype != input.dtype or not bias.is_contiguous()):
+        raise ValueError("bias must hold groups * out_size contiguous elements of the input dtype")
+    flat = [int(v) for p in patterns for v in p]
+    pat = _lib.int32_array(flat)
+    code = dtype_code(input.dtype)
+    need = groups * lib.ksmm_cu_chain_workspace_bytes_ex(nf, pat, batch, code, bs_last)
+    workspace = torch.empty(need, dtype=torch.uint8, device=input.device) if need else None
+    vals = (ctypes.c_void_p * nf)(*[w.data_ptr() for w in stacked_factors])
+    with torch.cuda.device(input.device):
+        _lib.check(lib.ksmm_cu_grouped_chain_forward(
+            input.data_ptr(), vals, out.data_ptr(), bias.data_ptr() if bias is not None else None,
+            workspace.data_ptr() if workspace is not None else None, need, batch, nf, pat, code, bs_last,
+            int(groups), _stream_ptr(input.device)))
+    return out
+
+
+def _check_grad_output(grad_output, input_like_shape, bs_last, a, b, d):
+    if not grad_output.is_cuda or grad_output.dim() != 2:
+        raise ValueError("grad_output must be a 2-D CUDA tensor")
+    batch = input_like_shape[1] if bs_last else input_like_shape[0]
+    want = (a * b * d, batch) if bs_last else (batch, a * b * d)
+    if tuple(grad_output.shape) != want:
+        raise ValueError(f"grad_output must have the forward output's shape {want}, got {tuple(grad_output.shape)}")
+
+
+def backward_input(grad_output, factor, bs_last, a, b, c, d):
+    """Gradient of one factor with respect to its input (``ksmm_cu_backward_input``): the
+    multiplication with pattern (a, c, b, d) and transposed blocks."""
+    lib = _lib.load()
+    bs_last = int(bool(bs_last))
+    grad_output = grad_output.contiguous()
+    batch = grad_output.shape[1] if bs_last else grad_output.shape[0]
+    _check_grad_output(grad_output, (a * c * d, batch) if bs_last else (batch, a * c * d), bs_last, a, b, d)
+    if tuple(factor.shape) != (a * d * c, b) or factor.dtype != grad_output.dtype or not factor.is_contiguous() \
+            or factor.device != grad_output.device:
+        raise ValueError(f"factor must be a contiguous ({a * d * c}, {b}) tensor of {grad_output.dtype}")
+    code = dtype_code(grad_output.dtype)
+    out = torch.empty((a * c * d, batch) if bs_last else (batch, a * c * d), dtype=grad_output.dtype,
+                      device=grad_output.device)
+    need = lib.ksmm_cu_backward_input_workspace_bytes(batch, a, b, c, d, code, bs_last)
+    ws = torch.empty(max(need, 1), dtype=torch.uint8, device=grad_output.device)
+    with torch.cuda.device(grad_output.device):
+        _lib.check(lib.ksmm_cu_backward_input(grad_output.data_ptr(), factor.data_ptr(), out.data_ptr(),
+                                              ws.data_ptr(), need, batch, a, b, c, d, code, bs_last,
+                                              _stream_ptr(grad_output.device)))
+    return out
+
+
+def backward_weights(input, grad_output, bs_last, a, b, c, d):
+    """Gradient of one factor with respect to its kernel-format weights
+    (``ksmm_cu_backward_weights``): (a*d*c, b), the input's dtype, fp32 accumulation."""
+    lib = _lib.load()
+    bs_last = int(bool(bs_last))
+    input, grad_output = input.contiguous(), grad_output.contiguous()
+    if not input.is_cuda or input.dim() != 2 or (input.shape[0] if bs_last else input.shape[1]) != a * c * d:
+        raise ValueError(f"input must be a 2-D CUDA tensor with {a * c * d} features")
+    _check_grad_output(grad_output, input.shape, bs_last, a, b, d)
+    if grad_output.dtype != input.dtype or grad_output.device != input.device:
+        raise ValueError("input and grad_output share dtype and device")
+    batch = input.shape[1] if bs_last else input.shape[0]
+    code = dtype_code(input.dtype)
+    out = torch.empty((a * d * c, b), dtype=input.dtype, device=input.device)
+    need = lib.ksmm_cu_backward_weights_workspace_bytes(batch, a, b, c, d, code, bs_last)
+    ws = torch.empty(max(need, 1), dtype=torch.uint8, device=input.device)
+    with torch.cuda.device(input.device):
+        _lib.check(lib.ksmm_cu_backward_weights(input.data_ptr(), grad_output.data_ptr(), out.data_ptr(),
+                                                ws.data_ptr(), need, batch, a, b, c, d, code, bs_last,
+                                                _stream_ptr(input.device)))
+    return out
+
+
+class FactorFunction(torch.autograd.Function):
+    """One factor as a differentiable operation.  The reference wires its kernel into autograd the
+    same way but leaves ``backward`` a stub (kernel.py:62-73, 323-329)."""
+
+    @staticmethod
+    def forward(ctx, input, factor, bs_last, a, b, c, d):
+        ctx.save_for_backward(input, factor)
+        ctx.pattern = (bool(bs_last), a, b, c, d)
+        return forward_ex(input, factor.detach(), bs_last, a, b, c, d)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        input, factor = ctx.saved_tensors
+        bs_last, a, b, c, d = ctx.pattern
+        grad_input = grad_factor = None
+        if ctx.needs_input_grad[0]:
+            grad_input = backward_input(grad_output, factor.detach(), bs_last, a, b, c, d)
+        if ctx.needs_input_grad[1]:
+            grad_factor = backward_weights(input.detach(), grad_output, bs_last, a, b, c, d)
+        return grad_input, grad_factor, None, None, None, None, None
 
 
 def quantize_e4m3(t):

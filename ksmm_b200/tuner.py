@@ -23,7 +23,7 @@ from .kernel import dtype_code
 
 _DT_NAME = {_lib.KSMM_F32: "f32", _lib.KSMM_F16: "f16", _lib.KSMM_BF16: "bf16", _lib.KSMM_F8E4M3: "f8e4m3"}
 _DT_CODE = {v: k for k, v in _DT_NAME.items()}
-_ALGO_NAME = {_lib.KSMM_ALGO_SIMT: "ffma", _lib.KSMM_ALGO_TC: "tensor"}
+_ALGO_NAME = {_lib.KSMM_ALGO_SIMT: "ffma", _lib.KSMM_ALGO_TC: "tensor", _lib.KSMM_ALGO_CONVERT: "convert"}
 _ALGO_CODE = {v: k for k, v in _ALGO_NAME.items()}
 
 # entries tuned or loaded in this process: key -> dict
@@ -100,11 +100,81 @@ def load(path, sm=None):
 
 def export_best_rows(path):
     """Write the table in the column order of the reference's ``.best`` files
-    (``batch a b c d TILEX TILEK TILEY TX TY VSIZE ms std mse``).  The tile columns
-    of the reference have no counterpart here: TILEX carries the configuration
-    index, TILEK the kernel family (1 = ffma, 2 = tensor), the rest are zero."""
+    (``batch a b c d TILEX TILEK TILEY TX TY VSIZE ms std mse``), header line included, so that
+    tooling written for those files keeps reading it.  The tile columns of the reference have no
+    counterpart here: TILEX carries the configuration index, TILEK the kernel family (1 = ffma,
+    2 = tensor, 3 = layout conversion), the rest are zero."""
     with open(path, "w") as f:
+        f.write(BEST_HEADER + "\n")
         for e in entries():
             a, b, c, d = e["pattern"]
             f.write(f"{e['batch']} {a} {b} {c} {d} {e['config']} {_ALGO_CODE[e['family']]} 0 0 0 0 "
                     f"{e['ms']:.6f} 0.000000 0.000000e+00\n")
+
+
+# ---------------------------------------------------------------------------
+# The reference's tables as priors
+# ---------------------------------------------------------------------------
+BEST_HEADER = "batch_size a b c d TILEX TILEK TILEY TX TY VSIZE ms std mse"
+# output-tile height (j) of the register-staged FFMA configurations 0..5 and their batch tile
+_FFMA_TILES = {0: (128, 128), 1: (64, 128), 2: (32, 128), 3: (16, 128), 4: (64, 256), 5: (8, 128)}
+
+
+def read_best_rows(path):
+    """Parse a ``.best`` table of the reference (kernel_bs_last_float.best and its siblings; the
+    reference scans them line by line in kernel.py:151-169).  Returns one dict per row:
+    ``batch, pattern, tile = (TILEX, TILEK, TILEY, TX, TY, VSIZE), ms``.  Malformed lines raise."""
+    rows = []
+    with open(path) as f:
+        lines = [ln.strip() for ln in f if ln.strip()]
+    if not lines or lines[0].split()[:5] != BEST_HEADER.split()[:5]:
+        raise ValueError(f"{path}: not a .best table (header line missing)")
+    for ln in lines[1:]:
+        t = ln.split()
+        if len(t) != 14:
+            raise ValueError(f"{path}: expected 14 columns, got {len(t)}: {ln!r}")
+        rows.append({"batch": int(t[0]), "pattern": [int(v) for v in t[1:5]],
+                     "tile": tuple(int(v) for v in t[5:11]), "ms": float(t[11])})
+    return rows
+
+
+def ffma_config_from_tile(tilex, tiley):
+    """The register-staged FFMA configuration whose output tile is nearest to the reference's
+    (TILEX = output rows j per CTA, TILEY = batch entries per CTA)."""
+    import math as _m
+    return min(_FFMA_TILES, key=lambda q: (abs(_m.log2(_FFMA_TILES[q][0] / max(tilex, 1))),
+                                           abs(_m.log2(_FFMA_TILES[q][1] / max(tiley, 1)))))
+
+
+def import_best_rows(path, dtype, bs_last, apply=True):
+    """Use a reference ``.best`` table as priors: every row names a problem the reference was tuned
+    for.  Returns the list of ``(pattern, batch)`` it holds (what ``tune_factor`` should be run on),
+    and, with ``apply``, seeds the library's choice cache for the rows that only the FFMA family can
+    run (no tensor-core kernel and no layout conversion for that problem) with the configuration
+    whose tile is nearest to the reference's winner.  Problems the heuristic already sends to a
+    tensor-core kernel are left to it: the reference's tiles say nothing about those kernels.
+    ``dtype``/``bs_last`` are what the table's file name encodes (``kernel_bs_{first,last}_{float,half}``)."""
+    from .kernel import default_choice
+    lib = _lib.load()
+    code = dtype_code(dtype)
+    known, seeded = [], 0
+    for r in read_best_rows(path):
+        a, b, c, d = r["pattern"]
+        known.append((tuple(r["pattern"]), r["batch"]))
+        if not apply:
+            continue
+        family, _, conv = default_choice(r["pattern"], r["batch"], dtype, bs_last)
+        algo, cfg = ctypes.c_int(), ctypes.c_int()
+        cached = lib.ksmm_cu_get_choice(r["batch"], a, b, c, d, code, code, int(bool(bs_last)),
+                                        ctypes.byref(algo), ctypes.byref(cfg)) == _lib.KSMM_OK
+        if family != "ffma" or conv or cached:
+            continue
+        config = ffma_config_from_tile(r["tile"][0], r["tile"][2])
+        if lib.ksmm_cu_set_choice(r["batch"], a, b, c, d, code, code, int(bool(bs_last)),
+                                  _lib.KSMM_ALGO_SIMT, config) == _lib.KSMM_OK:
+            _table[_key(r["batch"], r["pattern"], code, code, bs_last)] = {
+                "sm": None, "dtype": _DT_NAME[code], "out_dtype": _DT_NAME[code], "bs_last": bool(bs_last),
+                "pattern": list(r["pattern"]), "batch": r["batch"], "family": "ffma", "config": config,
+                "ms": float("nan"), "prior": {"tile": list(r["tile"]), "reference_ms": r["ms"]}}
+            seeded += 1
+    return known, seeded

@@ -33,7 +33,8 @@ import numpy as np
 
 __all__ = [
     "in_size", "out_size", "abcd_to_kernel_format", "kernel_format_to_abcd",
-    "abcd_to_dense", "factor_apply", "factor_apply_einsum", "chain_apply", "chain_dense",
+    "abcd_to_dense", "factor_apply", "factor_apply_einsum", "factor_grad_input",
+    "factor_grad_weights", "chain_apply", "chain_dense",
     "rel_fro_error", "quantize_e4m3", "e4m3_scale", "flops", "min_bytes",
 ]
 
@@ -116,6 +117,28 @@ def factor_apply_einsum(x, w, bs_last, acc_dtype=np.float64):
         return np.einsum("acdn,abcd->abdn", x.reshape(a, c, d, nb), w, optimize=True).reshape(a * b * d, nb)
     nb = x.shape[0]
     return np.einsum("nacd,abcd->nabd", x.reshape(nb, a, c, d), w, optimize=True).reshape(nb, a * b * d)
+
+
+def factor_grad_input(grad_out, w, bs_last, acc_dtype=np.float64):
+    """dL/dx of one factor: the transposed operator K^T applied to dL/dy, i.e. the factor with
+    pattern (a, c, b, d) and weights W^T[i,k,j,l] = W[i,j,k,l] (the dense K of interface.py:108-113
+    transposed).  The reference's kernel path has no backward (kernel.py:323-329); this is what
+    autograd yields for its ``einsum`` and ``dense`` algorithms."""
+    return factor_apply(grad_out, np.transpose(np.asarray(w), (0, 2, 1, 3)), bs_last, acc_dtype)
+
+
+def factor_grad_weights(x, grad_out, pattern, bs_last, acc_dtype=np.float64):
+    """dL/dW[i,j,k,l] = sum_n dL/dy[(i,j,l), n] * x[(i,k,l), n], as a 4-D (a,b,c,d) array."""
+    a, b, c, d = pattern
+    x = np.asarray(x, dtype=acc_dtype)
+    g = np.asarray(grad_out, dtype=acc_dtype)
+    if not bs_last:
+        x, g = x.T, g.T
+    nb = x.shape[1]
+    x4 = np.transpose(x.reshape(a, c, d, nb), (0, 2, 1, 3))      # (a, d, c, B)
+    g4 = np.transpose(g.reshape(a, b, d, nb), (0, 2, 1, 3))      # (a, d, b, B)
+    dw = np.matmul(g4, np.transpose(x4, (0, 1, 3, 2)))           # (a, d, b, c)
+    return np.ascontiguousarray(np.transpose(dw, (0, 2, 3, 1)))  # (a, b, c, d)
 
 
 def chain_apply(x, weights, bs_last, bias=None, acc_dtype=np.float64, round_to=None):

@@ -898,3 +898,146 @@ def test_chain_forward_host_async_tickets():
                                                     _lib.KSMM_F32, 0, 0, ctypes.byref(t)))
     assert t.value == 0 and lib.ksmm_cu_host_wait(0) == _lib.KSMM_OK          # empty batch
     assert lib.ksmm_cu_host_wait(1 << 40) == _lib.KSMM_ERR_BAD_ARGUMENT       # never issued
+
+
+# ---------------------------------------------------------------------------
+# 9. grouped calls: several weight sets of one pattern on one input (q, k, v projections)
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("bs_last", [True, False])
+def test_grouped_forward_shared_and_stacked_inputs(dtype, bs_last):
+    lib = _lib.load()
+    G = 3
+    code = kb.kernel.dtype_code(dtype)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for pi, pattern in enumerate([(1, 768, 768, 1), (6, 128, 128, 1), (2, 96, 48, 2), (1, 64, 64, 4)]):
+        a, b, c, d = pattern
+        for batch in (512, 136):
+            for shared in (1, 0):
+                rng = np.random.RandomState(1200 + pi)
+                ws = [torch.from_numpy(make_weights([pattern], rng)[0]).to(dtype) for _ in range(G)]
+                wk = torch.cat([kb.generate_factor(a, b, c, d, "kernel", w, dtype, DEV) for w in ws]).contiguous()
+                shape = (a * c * d, batch) if bs_last else (batch, a * c * d)
+                xs = [torch.from_numpy(rng.standard_normal(shape).astype(np.float32)).to(dtype)
+                      for _ in range(1 if shared else G)]
+                xg = torch.stack(xs).contiguous().to(DEV) if not shared else xs[0].to(DEV)
+                bias = torch.from_numpy(rng.standard_normal(G * a * b * d).astype(np.float32)).to(dtype)
+                oshape = (G, a * b * d, batch) if bs_last else (G, batch, a * b * d)
+                out = torch.full(oshape, float("nan"), dtype=dtype, device=DEV)
+                before = kb.launch_count()
+                _lib.check(lib.ksmm_cu_grouped_forward(xg.data_ptr(), wk.data_ptr(), out.data_ptr(),
+                                                       bias.to(DEV).data_ptr(), batch, a, b, c, d, code,
+                                                       int(bs_last), G, shared, stream))
+                launches = kb.launch_count() - before
+                one_launch = dtype != torch.float32 and (bs_last or (d == 1 and batch % 32 == 0))
+                if one_launch and b >= 32 and c >= 16:
+                    assert launches == 1, (pattern, batch, shared, launches)
+                for g in range(G):
+                    xq = xs[0] if shared else xs[g]
+                    bf = bias.float().numpy()[g * a * b * d:(g + 1) * a * b * d]
+                    ref = _oracle(xq, ws[g], bs_last) + (bf[:, None] if bs_last else bf[None, :])
+                    y = out[g].float().cpu().numpy()
+                    assert not np.isnan(y).any(), (pattern, batch, shared, g)
+                    assert ko.rel_fro_error(y, ref) < TOL[dtype], (pattern, batch, shared, g)
+    kb.check_device()
+
+
+@pytest.mark.parametrize("bs_last", [True, False])
+def test_kslinear_group_matches_separate_layers(bs_last):
+    """q, k, v as one KSLinearGroup: same results as the three layers called one by one, one launch
+    per factor instead of three, and the stacked weights follow an in-place update of a layer."""
+    pats = [(6, 128, 128, 1), (1, 768, 128, 6)]
+    dtype = torch.float16
+    torch.manual_seed(5)
+    layers = [kb.KSLinear(pats, bias=True, algo="kernel", dtype=dtype, bs_last=bs_last, device=DEV) for _ in range(3)]
+    group = kb.KSLinearGroup(layers)
+    x = torch.randn((768, 4, 160) if bs_last else (4, 160, 768), device=DEV).to(dtype)
+    before = kb.launch_count()
+    q, k, v = group(x)
+    fused_launches = kb.launch_count() - before
+    singles = [l(x) for l in layers]
+    for y, ref in zip((q, k, v), singles):
+        assert y.shape == ref.shape and y.is_contiguous()
+        rel = (torch.linalg.norm(y.float() - ref.float()) / torch.linalg.norm(ref.float())).item()
+        assert rel < 2e-3, rel
+    if bs_last:
+        assert fused_launches == len(pats)           # batch-first: the d = 6 factor runs group by group
+    dense = layers[1].get_dense_product()
+    xf = x.float().reshape(768, -1) if bs_last else x.float().reshape(-1, 768)
+    ref = (dense @ xf + layers[1].bias.float().reshape(-1, 1)) if bs_last else (xf @ dense.t() + layers[1].bias.float())
+    rel = (torch.linalg.norm(k.float().reshape(ref.shape) - ref) / torch.linalg.norm(ref)).item()
+    assert rel < 1e-2, rel
+    with torch.no_grad():
+        layers[2].factors[0].mul_(0.5)
+    v2 = group(x)[2]
+    ref2 = layers[2](x)
+    rel = (torch.linalg.norm(v2.float() - ref2.float()) / torch.linalg.norm(ref2.float())).item()
+    assert rel < 2e-3, rel
+    with pytest.raises(ValueError):
+        kb.KSLinearGroup([layers[0], kb.KSLinear([(1, 768, 768, 1)], dtype=dtype, bs_last=bs_last, device=DEV)])
+    kb.check_device()
+
+
+# ---------------------------------------------------------------------------
+# 10. backward of one factor
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("bs_last", [True, False])
+def test_factor_backward_against_the_oracle(dtype, bs_last):
+    """dX (the forward kernels on transposed blocks) and dW (tensor-core kernel with the batch
+    split over CTAs for 16-bit batch-last and batch-first d = 1; FFMA kernel otherwise)."""
+    pats = [(2, 96, 48, 2), (1, 768, 192, 4), (4, 192, 192, 1), (3, 40, 24, 3), (1, 64, 64, 16), (6, 64, 64, 1),
+            (1, 200, 136, 1), (2, 8, 300, 1)]
+    for pi, pattern in enumerate(pats):
+        a, b, c, d = pattern
+        for batch in (136, 4104):
+            rng = np.random.RandomState(1300 + pi)
+            x, w = _inputs(pattern, batch, dtype, bs_last, seed=1300 + pi)
+            gshape = (a * b * d, batch) if bs_last else (batch, a * b * d)
+            g = torch.from_numpy(rng.standard_normal(gshape).astype(np.float32)).to(dtype)
+            wk = kb.generate_factor(a, b, c, d, "kernel", w, dtype, DEV)
+            dx = kb.backward_input(g.to(DEV), wk, bs_last, a, b, c, d).float().cpu().numpy()
+            ref_dx = ko.factor_grad_input(g.float().numpy(), w.float().numpy(), bs_last)
+            assert ko.rel_fro_error(dx, ref_dx) < TOL[dtype], (pattern, batch, "dX")
+            dwk = kb.backward_weights(x.to(DEV), g.to(DEV), bs_last, a, b, c, d)
+            assert tuple(dwk.shape) == (a * d * c, b) and dwk.dtype == dtype
+            ref_dw = ko.abcd_to_kernel_format(ko.factor_grad_weights(x.float().numpy(), g.float().numpy(), pattern, bs_last))
+            assert ko.rel_fro_error(dwk.float().cpu().numpy(), ref_dw) < TOL[dtype], (pattern, batch, "dW")
+            # repeatable bit for bit (partial sums are added in a fixed order)
+            assert torch.equal(dwk, kb.backward_weights(x.to(DEV), g.to(DEV), bs_last, a, b, c, d))
+    kb.check_device()
+
+
+@pytest.mark.parametrize("bs_last", [True, False])
+def test_kslinear_trains_through_autograd(bs_last):
+    """A two-factor KSLinear with trainable factors and bias: gradients of a scalar loss against torch
+    autograd on the dense matrices of the same factors (fp32)."""
+    pats = [(4, 192, 192, 1), (1, 768, 192, 4)]
+    torch.manual_seed(11)
+    layer = kb.KSLinear(pats, bias=True, algo="kernel", dtype=torch.float32, bs_last=bs_last, device=DEV,
+                        requires_grad=True)
+    x = torch.randn((768, 256) if bs_last else (256, 768), device=DEV, requires_grad=True)
+    gy = torch.randn((3072, 256) if bs_last else (256, 3072), device=DEV)
+    y = layer(x)
+    (y * gy).sum().backward()
+    # reference: dense factors rebuilt from 4-D leaves so that autograd reaches (a,b,c,d) weights
+    leaves = [kb.from_kernel_format_to_abcd(f.detach(), p).clone().requires_grad_(True)
+              for f, p in zip(layer.factors, pats)]
+    xr = x.detach().clone().requires_grad_(True)
+    br = layer.bias.detach().clone().requires_grad_(True)
+    h = xr
+    for wl, (a, b, c, d) in zip(leaves, pats):
+        blocks = torch.diag_embed(wl).permute(0, 1, 3, 2, 4).reshape(a, b * d, c * d)
+        dense = torch.block_diag(*torch.unbind(blocks, dim=0))
+        h = dense @ h if bs_last else h @ dense.t()
+    yr = h + (br.reshape(-1, 1) if bs_last else br.reshape(1, -1))
+    (yr * gy).sum().backward()
+    rel = lambda u, v: (torch.linalg.norm(u - v) / torch.linalg.norm(v)).item()  # noqa: E731
+    assert rel(y.detach(), yr.detach()) < 1e-5
+    assert rel(x.grad, xr.grad) < 1e-5
+    assert rel(layer.bias.grad, br.grad) < 1e-5
+    for f, wl, p in zip(layer.factors, leaves, pats):
+        a, b, c, d = p
+        ref = wl.grad.permute(0, 3, 2, 1).reshape(a * d * c, b)
+        assert rel(f.grad, ref) < 1e-5, p
+    kb.check_device()

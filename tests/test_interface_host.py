@@ -101,8 +101,43 @@ def test_tuner_table_round_trip(tmp_path):
     assert len(json.loads(out.read_text())["entries"]) >= 2
     best = tmp_path / "kernel.best"
     tuner.export_best_rows(str(best))
-    assert best.read_text().splitlines()[0].split()[:5] == ["25088", "1", "768", "192", "4"]
+    rows = best.read_text().splitlines()
+    assert rows[0] == tuner.BEST_HEADER and rows[1].split()[:5] == ["25088", "1", "768", "192", "4"]
+    assert len(tuner.read_best_rows(str(best))) == len(rows) - 1      # its own export parses back
     with pytest.raises(ValueError):
         bad = tmp_path / "bad.json"
         bad.write_text("{}")
         tuner.load(str(bad))
+
+
+def test_reference_best_table_as_priors(tmp_path):
+    """A table in the reference's `.best` format (batch a b c d TILEX TILEK TILEY TX TY VSIZE ms std
+    mse, one header line) names the problems to tune and seeds the FFMA family's configuration for
+    the problems that only that family can run; tensor-core problems are left to the heuristic."""
+    import ctypes
+
+    import torch
+
+    from ksmm_b200 import _lib, tuner
+    path = tmp_path / "kernel_bs_last_float.best"
+    path.write_text(tuner.BEST_HEADER + "\n"
+                    "25088 1 16 16 6 16 16 64 4 4 4 0.0301 0.0002 1.1e-08\n"      # tiny block: FFMA only
+                    "25088 2 8 8 3 8 8 128 2 8 4 0.0202 0.0002 1.0e-08\n"
+                    "12544 1 768 192 2 64 16 64 8 4 4 0.9000 0.0010 2.0e-08\n")   # tensor-core kernel exists
+    rows = tuner.read_best_rows(str(path))
+    assert [r["pattern"] for r in rows] == [[1, 16, 16, 6], [2, 8, 8, 3], [1, 768, 192, 2]]
+    assert rows[0]["tile"] == (16, 16, 64, 4, 4, 4) and rows[2]["ms"] == 0.9
+    known, seeded = tuner.import_best_rows(str(path), torch.float32, True)
+    assert known == [((1, 16, 16, 6), 25088), ((2, 8, 8, 3), 25088), ((1, 768, 192, 2), 12544)]
+    assert seeded == 2
+    lib = _lib.load()
+    algo, cfg = ctypes.c_int(), ctypes.c_int()
+    assert lib.ksmm_cu_get_choice(25088, 1, 16, 16, 6, 0, 0, 1, ctypes.byref(algo), ctypes.byref(cfg)) == 0
+    assert (algo.value, cfg.value) == (_lib.KSMM_ALGO_SIMT, 3)            # 16 rows x 128 batch entries
+    assert lib.ksmm_cu_get_choice(25088, 2, 8, 8, 3, 0, 0, 1, ctypes.byref(algo), ctypes.byref(cfg)) == 0
+    assert (algo.value, cfg.value) == (_lib.KSMM_ALGO_SIMT, 5)            # 8 rows
+    assert lib.ksmm_cu_get_choice(12544, 1, 768, 192, 2, 0, 0, 1, ctypes.byref(algo), ctypes.byref(cfg)) != 0
+    assert tuner.ffma_config_from_tile(64, 256) == 4 and tuner.ffma_config_from_tile(128, 128) == 0
+    with pytest.raises(ValueError):
+        (tmp_path / "x.best").write_text("1 2 3\n")
+        tuner.read_best_rows(str(tmp_path / "x.best"))

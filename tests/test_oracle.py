@@ -104,3 +104,36 @@ def test_work_formulas():
     assert abs(ko.flops((1, 768, 192, 4), 25088) - 29.60e9) < 0.01e9
     assert abs(ko.min_bytes((1, 768, 192, 4), 25088, 2) - 193.9e6) < 0.1e6
     assert abs(ko.min_bytes((1, 768, 192, 4), 25088, 4) - 387.7e6) < 0.1e6
+
+
+def test_matmul_form_equals_the_literal_einsum_form():
+    """factor_apply hands the block products to BLAS; it must give the sums of the reference's
+    einsum strings."""
+    rng = np.random.RandomState(5)
+    for pattern in [(2, 3, 5, 4), (1, 48, 24, 3), (3, 7, 9, 2), (4, 8, 8, 1), (1, 1, 1, 8)]:
+        a, b, c, d = pattern
+        w = rng.standard_normal(pattern)
+        for bs_last in (True, False):
+            x = rng.standard_normal((a * c * d, 7) if bs_last else (7, a * c * d))
+            assert np.allclose(ko.factor_apply(x, w, bs_last), ko.factor_apply_einsum(x, w, bs_last),
+                               rtol=1e-12, atol=1e-12)
+
+
+def test_gradients_against_autograd_of_the_dense_operator():
+    """The oracle's input and weight gradients of one factor equal what torch autograd gives for
+    y = K x with the dense K of the reference (interface.py:108-113)."""
+    import torch
+    rng = np.random.RandomState(6)
+    for pattern in [(2, 3, 5, 4), (1, 6, 4, 3), (3, 4, 4, 1)]:
+        a, b, c, d = pattern
+        w = torch.tensor(rng.standard_normal(pattern), requires_grad=True)
+        x = torch.tensor(rng.standard_normal((a * c * d, 5)), requires_grad=True)
+        g = torch.tensor(rng.standard_normal((a * b * d, 5)))
+        blocks = torch.diag_embed(w).permute(0, 1, 3, 2, 4).reshape(a, b * d, c * d)
+        dense = torch.block_diag(*torch.unbind(blocks, dim=0))
+        (dense @ x * g).sum().backward()
+        assert np.allclose(ko.factor_grad_input(g.numpy(), w.detach().numpy(), True), x.grad.numpy())
+        assert np.allclose(ko.factor_grad_weights(x.detach().numpy(), g.numpy(), pattern, True), w.grad.numpy())
+        assert np.allclose(ko.factor_grad_input(g.numpy().T, w.detach().numpy(), False), x.grad.numpy().T)
+        assert np.allclose(ko.factor_grad_weights(x.detach().numpy().T, g.numpy().T, pattern, False),
+                           w.grad.numpy())

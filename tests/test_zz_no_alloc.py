@@ -50,10 +50,15 @@ def test_static_chain_first_call_of_a_fresh_process_allocates_nothing():
     line = [ln for ln in res.stdout.splitlines() if ln.startswith("NO_ALLOC_RESULT ")][-1]
     results = json.loads(line[len("NO_ALLOC_RESULT "):])
     assert len(results) == 14
-    for r in results:
+    for idx, r in enumerate(results):
         assert r["status"] == 0, r
         assert r["allocs"] == 0, r                      # no cudaMalloc inside the library
-        assert r["free_delta"] < 4 * 1024 * 1024, r      # every case needs more than 4 MiB of scratch...
+        # Free device memory: the first call on a device makes the driver load the part of the library
+        # image that holds the array (its 40 MiB and some code), once, whatever the chain; after that
+        # nothing may move, although every case here needs more than 4 MiB of scratch (intermediates,
+        # and from the second case on transposed copies that no earlier call has ever needed).
+        limit = _lib.STATIC_SCRATCH_BYTES + 16 * 1024 * 1024 if idx == 0 else 4 * 1024 * 1024
+        assert r["free_delta"] < limit, (idx, r, [q["free_delta"] for q in results])
         assert not r["nan"], r
         tol = 1e-2 if r["half"] else 1e-5
         assert r["err_vs_ordinary"] < tol, r
