@@ -121,7 +121,9 @@ template <typename T>
 __global__ void __launch_bounds__(256) activation_kernel(T* data, int64_t n, int act) {
   for (int64_t q = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; q < n;
        q += static_cast<int64_t>(gridDim.x) * 256)
-    data[q] = ElemTraits<T>::from_float(apply_activation(ElemTraits<T>::to_float(data[q]), act));
+    data[q] = ElemTraits<T>::from_float(sizeof(T) == 2 && act == KSMM_ACT_GELU
+                                            ? gelu_16bit(ElemTraits<T>::to_float(data[q]))
+                                            : apply_activation(ElemTraits<T>::to_float(data[q]), act));
 }
 
 static int simt_launch(const Problem& p, int config, cudaStream_t stream) {

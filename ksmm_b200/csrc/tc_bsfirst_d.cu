@@ -408,7 +408,7 @@ __global__ void __launch_bounds__(kThreadsD, 1)
 #pragma unroll
             for (int l = 0; l < D; ++l)
 #pragma unroll
-              for (int jj = 0; jj < JB; ++jj) r[l][jj] = __float_as_uint(apply_activation(__uint_as_float(r[l][jj]), 1));
+              for (int jj = 0; jj < JB; ++jj) r[l][jj] = __float_as_uint(gelu_16bit(__uint_as_float(r[l][jj])));
           } else if (P.act == KSMM_ACT_RELU) {
 #pragma unroll
             for (int l = 0; l < D; ++l)

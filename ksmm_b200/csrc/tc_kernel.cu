@@ -374,7 +374,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             if (P.act == KSMM_ACT_GELU) {
 #pragma unroll
-              for (int e = 0; e < C::CB; ++e) r[e] = __float_as_uint(apply_activation(__uint_as_float(r[e]), 1));
+              for (int e = 0; e < C::CB; ++e) r[e] = __float_as_uint(OS == 2 ? gelu_16bit(__uint_as_float(r[e])) : apply_activation(__uint_as_float(r[e]), 1));
             } else if (P.act == KSMM_ACT_RELU) {
 #pragma unroll
               for (int e = 0; e < C::CB; ++e) r[e] = __float_as_uint(fmaxf(__uint_as_float(r[e]), 0.f));
