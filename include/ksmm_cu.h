@@ -171,6 +171,27 @@ KSMM_API int ksmm_cu_chain_forward_act(const void* input, const void* const* val
                               int dtype, int bs_last, int activation, void* stream);
 
 /*
+ * A chain whose output layout may differ from its input layout, e.g. the two
+ * KSLinear layers of an MLP with the activations between them kept batch-last
+ * while the network around them is batch-first (the reference fixes one
+ * layout per layer, interface.py:134, 193-345, and pays for interleaved blocks
+ * in every batch-first factor with d > 1).  The library plans a layout for
+ * every intermediate: 16-bit factors with d = 1 read one layout and write the
+ * other inside the kernel, at no cost; where no such factor exists the tensor
+ * at the chain's end is transposed.  ksmm_cu_chain_forward and
+ * ksmm_cu_chain_forward_act are this call with out_bs_last = bs_last, and use
+ * the same planner, so their intermediates may be batch-last inside a
+ * batch-first chain.  Workspace: ..._workspace_bytes_layouts.
+ */
+KSMM_API size_t ksmm_cu_chain_workspace_bytes_layouts(int nfactors, const int32_t* patterns,
+                                             int64_t batch, int dtype, int bs_last, int out_bs_last);
+KSMM_API int ksmm_cu_chain_forward_layouts(const void* input, const void* const* values, void* output,
+                                  const void* bias, void* workspace, size_t workspace_bytes,
+                                  int64_t batch, int nfactors, const int32_t* patterns,
+                                  int dtype, int bs_last, int out_bs_last, int activation,
+                                  void* stream);
+
+/*
  * Several problems of one pattern in one call ("groups"): the q, k and v
  * projections of an attention layer apply the same patterns to the same input
  * (src/ksmm_py/model/get_vit.py:164-215 builds to_q, to_k, to_v from one

@@ -38,6 +38,7 @@ EXPORTS = (
     "ksmm_cu_alloc_count", "ksmm_cu_debug_wait_probe",
     "ksmm_cu_chain_forward_host_async", "ksmm_cu_host_wait",
     "ksmm_cu_grouped_forward", "ksmm_cu_grouped_chain_forward",
+    "ksmm_cu_chain_workspace_bytes_layouts", "ksmm_cu_chain_forward_layouts",
     "ksmm_cu_backward_input_workspace_bytes", "ksmm_cu_backward_input",
     "ksmm_cu_backward_weights_workspace_bytes", "ksmm_cu_backward_weights",
 )
@@ -102,6 +103,11 @@ def load():
     lib.ksmm_cu_chain_forward_host_async.argtypes = [vp, ctypes.POINTER(vp), vp, vp, i64, i32,
                                                      ctypes.POINTER(ctypes.c_int32), i32, i32, i32,
                                                      ctypes.POINTER(ctypes.c_uint64)]
+    lib.ksmm_cu_chain_workspace_bytes_layouts.restype = ctypes.c_size_t
+    lib.ksmm_cu_chain_workspace_bytes_layouts.argtypes = [i32, ctypes.POINTER(ctypes.c_int32), i64, i32, i32, i32]
+    lib.ksmm_cu_chain_forward_layouts.restype = i32
+    lib.ksmm_cu_chain_forward_layouts.argtypes = [vp, ctypes.POINTER(vp), vp, vp, vp, ctypes.c_size_t, i64,
+                                                  i32, ctypes.POINTER(ctypes.c_int32), i32, i32, i32, i32, vp]
     lib.ksmm_cu_grouped_forward.restype = i32
     lib.ksmm_cu_grouped_forward.argtypes = [vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, vp]
     lib.ksmm_cu_grouped_chain_forward.restype = i32

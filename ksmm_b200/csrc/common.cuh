@@ -133,7 +133,8 @@ struct Problem {
   int64_t batch;
   int a, b, c, d;
   int in_dtype, out_dtype;
-  int bs_last;
+  int bs_last;             // layout of the input (and of the output unless out_bs_last says otherwise)
+  int out_bs_last = -1;    // -1: same as the input; 0 / 1: batch-first / batch-last output (d = 1 factors)
   float alpha;
   // Chains only.  out_regroup_d > 0: store the output regrouped by the blocks of the next factor
   // (c = out_regroup_c, d = out_regroup_d): feature (i2*c + k)*d + l goes to (i2*d + l)*c + k.

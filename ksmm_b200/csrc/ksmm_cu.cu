@@ -545,13 +545,105 @@ size_t ksmm_cu_chain_workspace_bytes(int nfactors, const int32_t* patterns, int6
   return chain_intermediate_bytes(nfactors, patterns, batch, dtype);
 }
 
-// One pass over a chain: either plans it (run == false: returns through *scratch_max the largest
-// layout scratch any of its factors needs under the current dispatch) or runs it.
+// ---------------------------------------------------------------------------
+// Layout plan of a chain.  Batch-last factors are the fast form for every d; batch-first factors
+// with d > 1 pay for the interleaved blocks (in-kernel split, or a layout conversion).  A 16-bit
+// factor with d = 1 can read one layout and write the other at no extra cost, and a whole tensor
+// can be transposed at the chain's ends.  The plan gives every factor its input and output layout
+// so that the estimated time of the chain is smallest; the estimates are byte counts weighted by
+// how far the kernel of that form runs from the memory roofline (measured on the benchmark
+// patterns), which is all this choice needs.
+// ---------------------------------------------------------------------------
+struct ChainPlan {
+  static constexpr int kMax = 16;
+  bool pre_transpose = false, post_transpose = false;
+  int in_last[kMax], out_last[kMax];
+};
+
+static bool can_switch_layout(const int32_t* q, int64_t batch, int dtype) {
+  return (dtype == KSMM_F16 || dtype == KSMM_BF16) && q[3] == 1 && q[1] % 8 == 0 && q[2] % 8 == 0 &&
+         batch % 8 == 0 && q[1] >= 32 && q[2] >= 16;
+}
+
+static double step_cost(const int32_t* q, int64_t batch, int dtype, int in_last, int out_last) {
+  const double bytes = static_cast<double>(dtype_size(dtype)) * q[0] * q[3] * (static_cast<double>(q[1]) + q[2]) * batch;
+  if (in_last != out_last) return can_switch_layout(q, batch, dtype) ? 1.05 * bytes : -1.0;
+  if (in_last || q[3] == 1) return bytes;
+  const bool half = dtype == KSMM_F16 || dtype == KSMM_BF16;
+  if (half && (q[3] == 2 || q[3] == 4) && q[1] % 8 == 0 && (static_cast<int64_t>(q[2]) * q[3]) % 8 == 0)
+    return 1.9 * bytes;   // in-kernel split of the interleaved blocks
+  return 2.6 * bytes;     // layout conversion around the batch-last kernel, or the strided FFMA kernel
+}
+
+static void plan_chain(int nfactors, const int32_t* patterns, int64_t batch, int dtype, int in_last,
+                       int out_last, bool allow_switch, ChainPlan* plan) {
+  // default: every factor in the input's layout, a transpose at the end if the output differs
+  for (int f = 0; f < nfactors && f < ChainPlan::kMax; ++f) plan->in_last[f] = plan->out_last[f] = in_last;
+  plan->pre_transpose = false;
+  plan->post_transpose = in_last != out_last;
+  const bool half = dtype == KSMM_F16 || dtype == KSMM_BF16;
+  if (!half || !allow_switch || nfactors > 8 || batch <= 0) return;
+  const double es = dtype_size(dtype);
+  const int32_t* p0 = patterns;
+  const int32_t* pl = patterns + 4 * (nfactors - 1);
+  const double in_bytes = es * p0[0] * p0[2] * p0[3] * batch, out_bytes = es * pl[0] * pl[1] * pl[3] * batch;
+  const double kTranspose = 0.75 * 2.0;  // read + write, at a higher fraction of the bandwidth than the kernels
+  double best = -1.0;
+  // mask bit f = layout of factor f's output; `pre` = transpose the chain input first
+  for (int pre = 0; pre < 2; ++pre) {
+    for (unsigned mask = 0; mask < (1u << nfactors); ++mask) {
+      int state = pre ? !in_last : in_last;
+      double cost = pre ? kTranspose * in_bytes : 0.0;
+      bool ok = true;
+      for (int f = 0; f < nfactors && ok; ++f) {
+        const int o = (mask >> f) & 1;
+        const double c = step_cost(patterns + 4 * f, batch, dtype, state, o);
+        if (c < 0) ok = false;
+        cost += c;
+        state = o;
+      }
+      if (!ok) continue;
+      if (state != out_last) cost += kTranspose * out_bytes;
+      if (best < 0 || cost < best * 0.999) {   // ties keep the earlier (fewer transposes, layout of the input) plan
+        best = cost;
+        int st2 = pre ? !in_last : in_last;
+        for (int f = 0; f < nfactors; ++f) {
+          plan->in_last[f] = st2;
+          plan->out_last[f] = (mask >> f) & 1;
+          st2 = plan->out_last[f];
+        }
+        plan->pre_transpose = pre != 0;
+        plan->post_transpose = st2 != out_last;
+      }
+    }
+  }
+}
+
 static int chain_walk(bool run, const void* input, const void* const* values, void* output,
                       const void* bias, void* workspace, size_t inter_bytes, void* scratch,
                       size_t scratch_bytes, int no_alloc, int64_t batch, int nfactors,
-                      const int32_t* patterns, int dtype, int bs_last, int activation,
-                      cudaStream_t stream, size_t* scratch_max) {
+                      const int32_t* patterns, int dtype, int bs_last, int out_bs_last, int activation,
+                      cudaStream_t stream, size_t* scratch_max, int allow_switch);
+
+// One pass over a chain: either plans it (run == false: returns through *scratch_max the layout
+// scratch it needs under the current dispatch: transposed copies at the chain's ends plus the
+// largest scratch of any factor) or runs it.
+static int chain_walk(bool run, const void* input, const void* const* values, void* output,
+                      const void* bias, void* workspace, size_t inter_bytes, void* scratch,
+                      size_t scratch_bytes, int no_alloc, int64_t batch, int nfactors,
+                      const int32_t* patterns, int dtype, int bs_last, int out_bs_last, int activation,
+                      cudaStream_t stream, size_t* scratch_max, int allow_switch) {
+  if (nfactors > ChainPlan::kMax)
+    return set_error(KSMM_ERR_UNSUPPORTED, "chains of more than %d factors", ChainPlan::kMax);
+  ChainPlan plan;
+  plan_chain(nfactors, patterns, batch, dtype, bs_last, out_bs_last, allow_switch != 0, &plan);
+  const size_t es = dtype_size(dtype);
+  const int32_t* p0 = patterns;
+  const int32_t* pl = patterns + 4 * (nfactors - 1);
+  const int64_t in_feats = static_cast<int64_t>(p0[0]) * p0[2] * p0[3];
+  const int64_t out_feats = static_cast<int64_t>(pl[0]) * pl[1] * pl[3];
+  const size_t pre_bytes = plan.pre_transpose ? align_up(static_cast<size_t>(in_feats) * batch * es, 256) : 0;
+  const size_t post_bytes = plan.post_transpose ? align_up(static_cast<size_t>(out_feats) * batch * es, 256) : 0;
   const size_t half = nfactors == 2 ? inter_bytes : inter_bytes / 2;
   const void* cur = input;
   bool cur_regrouped = false;  // the intermediate in `cur` is regrouped by the blocks of factor f
@@ -561,22 +653,61 @@ static int chain_walk(bool run, const void* input, const void* const* values, vo
     ws = reinterpret_cast<char*>(static_cast<uintptr_t>(1) << 20);
     cur = output = ws;
   }
+  // One region holds everything the chain needs beside its intermediates: the transposed copies
+  // at the chain's ends first, the factors' layout scratch after them.  It is the caller's
+  // scratch when that is large enough, else the library-owned buffer of this stream, taken once
+  // for the whole chain (a second request could move it under the first).
+  char* t_pre = nullptr;
+  char* t_post = nullptr;
+  void* f_scratch = nullptr;
+  size_t f_scratch_bytes = 0;
+  int f_no_alloc = no_alloc;
+  if (run && batch > 0) {
+    size_t total = 0;
+    int stp = chain_walk(false, nullptr, nullptr, nullptr, nullptr, nullptr, inter_bytes, nullptr, 0, 0, batch,
+                         nfactors, patterns, dtype, bs_last, out_bs_last, activation, nullptr, &total,
+                         allow_switch);
+    if (stp != KSMM_OK) return stp;
+    if (total > 0) {
+      Problem sp;
+      sp.scratch = scratch; sp.scratch_bytes = scratch_bytes; sp.no_alloc = no_alloc;
+      void* base = nullptr;
+      stp = layout_scratch(sp, total, stream, &base);
+      if (stp != KSMM_OK) return stp;
+      t_pre = static_cast<char*>(base);
+      t_post = t_pre + pre_bytes;
+      f_scratch = t_post + post_bytes;
+      f_scratch_bytes = total - pre_bytes - post_bytes;
+      f_no_alloc = 1;  // what the factors need is inside the region by construction
+    }
+  }
+  if (plan.pre_transpose && run && batch > 0) {
+    // (batch, features) -> (features, batch) or back
+    int st = bs_last ? launch_transpose(input, t_pre, in_feats, batch, static_cast<int>(es), stream)
+                     : launch_transpose(input, t_pre, batch, in_feats, static_cast<int>(es), stream);
+    if (st != KSMM_OK) return st;
+    cur = t_pre;
+  }
+  size_t factor_scratch_max = 0;
   for (int f = 0; f < nfactors; ++f) {
     const int32_t* q = patterns + 4 * f;
     const bool last = (f + 1 == nfactors);
-    void* dst = last ? output : ws + (f & 1) * half;
+    void* dst = last ? (plan.post_transpose && run ? static_cast<void*>(t_post) : output) : ws + (f & 1) * half;
     Problem p;
     p.in = cur; p.w = run ? values[f] : ws; p.out = dst; p.bias = last ? bias : nullptr;
     p.batch = batch; p.a = q[0]; p.b = q[1]; p.c = q[2]; p.d = q[3];
-    p.in_dtype = dtype; p.out_dtype = dtype; p.bs_last = bs_last; p.alpha = 1.f;
+    p.in_dtype = dtype; p.out_dtype = dtype; p.alpha = 1.f;
+    p.bs_last = plan.in_last[f];
+    p.out_bs_last = plan.out_last[f] == plan.in_last[f] ? -1 : plan.out_last[f];
     p.activation = last ? activation : 0;
-    p.scratch = scratch; p.scratch_bytes = scratch_bytes; p.no_alloc = no_alloc;
+    p.scratch = f_scratch; p.scratch_bytes = f_scratch_bytes; p.no_alloc = f_no_alloc;
+    const bool same_first = !plan.in_last[f] && !plan.out_last[f];
     // Layout fusion of consecutive batch-first factors: when the next factor has d = 2 or 4 and
     // this one can store its output regrouped by the next factor's blocks, the intermediate is
     // written in that order and the next factor runs the kernel without the transposer stage
     // (and without a regrouping pass).
     bool next_regrouped = false;
-    if (!last && !bs_last) {
+    if (!last && same_first && !plan.in_last[f + 1] && !plan.out_last[f + 1]) {
       const int32_t* r = patterns + 4 * (f + 1);
       Problem nx = p;
       // the next factor reads this factor's destination and writes its own one
@@ -596,7 +727,11 @@ static int chain_walk(bool run, const void* input, const void* const* values, vo
       }
     }
     int st = KSMM_OK;
-    if (cur_regrouped) {
+    if (p.out_bs_last >= 0) {
+      // a factor that changes the layout: the 16-bit tensor kernel only (the plan checked its shape
+      // rules; pointers are the caller's)
+      if (run) st = tc_launch(p, -1, stream);
+    } else if (cur_regrouped) {
       p.in_regrouped = 1;
       if (run) st = tc_launch(p, 1, stream);
     } else if (next_regrouped) {
@@ -607,13 +742,21 @@ static int chain_walk(bool run, const void* input, const void* const* values, vo
       st = check_problem(p);
       if (st == KSMM_OK && batch > 0) {
         const size_t need = scratch_need(p, auto_choice(p));
-        if (scratch_max && need > *scratch_max) *scratch_max = need;
+        if (need > factor_scratch_max) factor_scratch_max = need;
       }
     }
     if (st != KSMM_OK) return st;
     cur = dst;
     cur_regrouped = next_regrouped;
   }
+  if (plan.post_transpose && run && batch > 0) {
+    // the last factor wrote the other layout into t_post
+    const int last_layout = plan.out_last[nfactors - 1];
+    int st = last_layout ? launch_transpose(t_post, output, out_feats, batch, static_cast<int>(es), stream)
+                         : launch_transpose(t_post, output, batch, out_feats, static_cast<int>(es), stream);
+    if (st != KSMM_OK) return st;
+  }
+  if (scratch_max) *scratch_max = pre_bytes + post_bytes + factor_scratch_max;
   return KSMM_OK;
 }
 
@@ -647,13 +790,18 @@ static int check_chain(int nfactors, const int32_t* patterns, const void* const*
 
 size_t ksmm_cu_chain_workspace_bytes_ex(int nfactors, const int32_t* patterns, int64_t batch,
                                         int dtype, int bs_last) {
+  return ksmm_cu_chain_workspace_bytes_layouts(nfactors, patterns, batch, dtype, bs_last, bs_last);
+}
+
+size_t ksmm_cu_chain_workspace_bytes_layouts(int nfactors, const int32_t* patterns, int64_t batch,
+                                             int dtype, int bs_last, int out_bs_last) {
   if (nfactors <= 0 || !patterns || batch <= 0) return 0;
   const void* dummy = nullptr;
   if (check_chain(nfactors, patterns, &dummy, dtype, 0) != KSMM_OK) return 0;
   const size_t inter = chain_intermediate_bytes(nfactors, patterns, batch, dtype);
   size_t scratch = 0;
   if (chain_walk(false, nullptr, nullptr, nullptr, nullptr, nullptr, inter, nullptr, 0, 0, batch, nfactors,
-                 patterns, dtype, bs_last ? 1 : 0, 0, nullptr, &scratch) != KSMM_OK)
+                 patterns, dtype, bs_last ? 1 : 0, out_bs_last ? 1 : 0, 0, nullptr, &scratch, 1) != KSMM_OK)
     return 0;
   return inter + scratch;
 }
@@ -671,10 +819,12 @@ int ksmm_cu_chain_forward(const void* input, const void* const* values, void* ou
 static int chain_forward_impl(const void* input, const void* const* values, void* output,
                               const void* bias, void* workspace, size_t workspace_bytes, int no_alloc,
                               int64_t batch, int nfactors, const int32_t* patterns, int dtype,
-                              int bs_last, int activation, cudaStream_t stream) {
+                              int bs_last, int out_bs_last, int activation, cudaStream_t stream) {
   int st = check_chain(nfactors, patterns, values, dtype, activation);
   if (st != KSMM_OK) return st;
   if (bs_last != 0 && bs_last != 1) return set_error(KSMM_ERR_BAD_ARGUMENT, "bs_last must be 0 or 1");
+  if (out_bs_last != 0 && out_bs_last != 1)
+    return set_error(KSMM_ERR_BAD_ARGUMENT, "the output layout must be 0 (batch-first) or 1 (batch-last)");
   if (batch < 0) return set_error(KSMM_ERR_BAD_ARGUMENT, "negative batch");
   const size_t inter = chain_intermediate_bytes(nfactors, patterns, batch, dtype);
   if (inter > 0 && (!workspace || workspace_bytes < inter))
@@ -686,11 +836,15 @@ static int chain_forward_impl(const void* input, const void* const* values, void
     scratch = static_cast<char*>(workspace) + inter;
     scratch_bytes = workspace_bytes - inter;
   }
+  // layout-changing factors go through TMA on both sides: every buffer has to be 16-byte aligned
+  auto al16 = [](const void* q) { return reinterpret_cast<uintptr_t>(q) % 16 == 0; };
+  int allow_switch = al16(input) && al16(output) && al16(workspace) ? 1 : 0;
+  for (int f = 0; f < nfactors; ++f) allow_switch &= al16(values[f]) ? 1 : 0;
   if (no_alloc) {
     // refuse before the first launch, not half-way through the chain
     size_t need = 0;
     st = chain_walk(false, nullptr, nullptr, nullptr, nullptr, nullptr, inter, nullptr, 0, 0, batch,
-                    nfactors, patterns, dtype, bs_last, activation, nullptr, &need);
+                    nfactors, patterns, dtype, bs_last, out_bs_last, activation, nullptr, &need, allow_switch);
     if (st != KSMM_OK) return st;
     if (need > scratch_bytes)
       return set_error(KSMM_ERR_WORKSPACE,
@@ -699,7 +853,8 @@ static int chain_forward_impl(const void* input, const void* const* values, void
                        inter, need, workspace_bytes);
   }
   return chain_walk(true, input, values, output, bias, workspace, inter, scratch, scratch_bytes, no_alloc,
-                    batch, nfactors, patterns, dtype, bs_last, activation, stream, nullptr);
+                    batch, nfactors, patterns, dtype, bs_last, out_bs_last, activation, stream, nullptr,
+                    allow_switch);
 }
 
 int ksmm_cu_chain_forward_act(const void* input, const void* const* values, void* output,
@@ -707,7 +862,16 @@ int ksmm_cu_chain_forward_act(const void* input, const void* const* values, void
                               int64_t batch, int nfactors, const int32_t* patterns, int dtype,
                               int bs_last, int activation, void* stream) {
   return chain_forward_impl(input, values, output, bias, workspace, workspace_bytes, /*no_alloc=*/0, batch,
-                            nfactors, patterns, dtype, bs_last, activation,
+                            nfactors, patterns, dtype, bs_last, bs_last, activation,
+                            static_cast<cudaStream_t>(stream));
+}
+
+int ksmm_cu_chain_forward_layouts(const void* input, const void* const* values, void* output,
+                                  const void* bias, void* workspace, size_t workspace_bytes,
+                                  int64_t batch, int nfactors, const int32_t* patterns, int dtype,
+                                  int bs_last, int out_bs_last, int activation, void* stream) {
+  return chain_forward_impl(input, values, output, bias, workspace, workspace_bytes, /*no_alloc=*/0, batch,
+                            nfactors, patterns, dtype, bs_last, out_bs_last, activation,
                             static_cast<cudaStream_t>(stream));
 }
 
@@ -883,7 +1047,7 @@ int ksmm_cu_chain_forward_static(const void* input, const void* const* values, v
   // nothing in the scratch has to start at zero
   return chain_forward_impl(input, values, output, bias, scratch,
                             need > 0 ? static_cast<size_t>(KSMM_CU_STATIC_SCRATCH_BYTES) : 0,
-                            /*no_alloc=*/1, batch, nfactors, patterns, dtype, bs_last, KSMM_ACT_NONE,
+                            /*no_alloc=*/1, batch, nfactors, patterns, dtype, bs_last, bs_last, KSMM_ACT_NONE,
                             static_cast<cudaStream_t>(stream));
 }
 

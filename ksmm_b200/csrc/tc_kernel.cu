@@ -86,14 +86,22 @@ struct Params {
 //   stream through the ring (SX stages of one chunk each).
 // WRES = false ("streaming"): a ring stage holds one k chunk of both operands
 //   (NWC = 0); used when the weight tile is too large to keep.
-template <bool BS_LAST, int ES, int OS, int NT, int KC, bool WRES, int NWC, int SX>
+// IN_LAST / OUT_LAST: layout of the input and of the output.  The accumulator's rows are output
+// features when the output is batch-last (weights = M-side operand) and batch entries when it is
+// batch-first (input = M-side operand); the input operand is MN-major when the input is batch-last
+// (rows of the tile = k, consecutive batch entries) and K-major when it is batch-first (rows =
+// batch entries, consecutive k).  The two mixed combinations (d = 1 only) let a chain change its
+// layout inside a factor at no cost.
+template <bool IN_LAST, bool OUT_LAST, int ES, int OS, int NT, int KC, bool WRES, int NWC, int SX>
 struct Cfg {
   static constexpr int NBOX = 128 / ES;        // elements in one 128-byte box row
   static constexpr int UK = 32 / ES;           // k extent of one MMA
   static constexpr int M_BYTES = 128 * KC * ES;  // one k chunk of the M-side operand
   static constexpr int N_BYTES = NT * KC * ES;   // one k chunk of the N-side operand
-  static constexpr int XB = BS_LAST ? N_BYTES : M_BYTES;  // input chunk
-  static constexpr int WB = BS_LAST ? M_BYTES : N_BYTES;  // weight chunk
+  static constexpr int XB = OUT_LAST ? N_BYTES : M_BYTES;  // input chunk
+  static constexpr int WB = OUT_LAST ? M_BYTES : N_BYTES;  // weight chunk
+  static constexpr int XN = OUT_LAST ? NT : 128;           // batch entries per tile
+  static constexpr int WJ = OUT_LAST ? 128 : NT;           // output features per tile
   static constexpr int STAGE_BYTES = XB + (WRES ? 0 : WB);
   static constexpr int CB = 128 / OS;          // output elements in one staging row
   static constexpr int STG_WARP_BYTES = 32 * 128;  // one warp's 32 rows x 128 bytes
@@ -106,17 +114,19 @@ struct Cfg {
   static constexpr int TMEM_COLS = 2 * NT;
   static_assert(NT == 64 || NT == 128 || NT == 256, "TMEM allocation must be a power of two");
   static_assert(KC % UK == 0 && KC % 8 == 0, "k chunk");
-  static_assert(BS_LAST || KC == NBOX, "batch-first input chunks are one 128-byte k box");
+  static_assert(IN_LAST || KC == NBOX, "batch-first input chunks are one 128-byte k box");
+  static_assert(IN_LAST || XN <= 256, "a batch-first input chunk is one TMA box of XN rows");
   static_assert(NT % NBOX == 0, "N tile must be whole 128-byte box rows");
   static_assert(8 * NBAR + 16 <= BAR_BYTES, "barrier area");
   static_assert(WRES ? NWC > 0 : NWC == 0, "resident weight chunks exist in weight-stationary mode only");
 };
 
-template <bool BS_LAST, int ES, int OS, int NT, int KC, bool WRES, int NWC, int SX>
+template <bool IN_LAST, bool OUT_LAST, int ES, int OS, int NT, int KC, bool WRES, int NWC, int SX>
 __global__ void __launch_bounds__(kThreads, 1)
     ksmm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
                    const __grid_constant__ CUtensorMap tmY, const Params P) {
-  using C = Cfg<BS_LAST, ES, OS, NT, KC, WRES, NWC, SX>;
+  using C = Cfg<IN_LAST, OUT_LAST, ES, OS, NT, KC, WRES, NWC, SX>;
+  constexpr bool BS_LAST = OUT_LAST;  // orientation of the accumulator and of the epilogue
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t sm0 = (raw + 1023u) & ~1023u;  // 1024-byte alignment for the 128-byte swizzle
@@ -178,6 +188,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int wblk0 = grp_id * P.a * P.d;
   const int xi0 = P.gx ? grp_id * P.a : 0, yi0 = grp_id * P.a;
   const int xn0 = P.gx ? grp_id * static_cast<int>(P.batch) : 0, yn0 = grp_id * static_cast<int>(P.batch);
+  (void)xi0; (void)xn0; (void)yi0; (void)yn0;
   const int64_t bias0 = static_cast<int64_t>(grp_id) * P.a * P.b * P.d;
 
   if (warp == 0) {
@@ -191,7 +202,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int blk = static_cast<int>(row / P.tiles_n);
         const int tn = static_cast<int>(row % P.tiles_n);
         const int i = blk / d, l = blk % d;
-        const int n0 = tn * (BS_LAST ? NT : 128);
+        const int n0 = tn * C::XN;
         if (WRES && blk != cur_blk) {
           // new block: fetch its weight tile once the MMAs on the old one are done
           if (!mbar_wait<64>(wempty_bar, wph ^ 1u, abort_flag, P.status, 1)) { ok = false; break; }
@@ -199,7 +210,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           mbar_expect_tx(wfull_bar, nk * C::WB);
           for (int kc = 0; kc < nk; ++kc) {
 #pragma unroll
-            for (int wb = 0; wb < (BS_LAST ? 128 : NT) / C::NBOX; ++wb)
+            for (int wb = 0; wb < C::WJ / C::NBOX; ++wb)
               tma_load_3d(wres0 + kc * C::WB + wb * KC * 128, &tmW, wfull_bar, j0 + wb * C::NBOX,
                           kc * KC, blk + wblk0);
           }
@@ -212,16 +223,16 @@ __global__ void __launch_bounds__(kThreads, 1)
           const uint32_t dst = ring0 + si * C::STAGE_BYTES;
           const uint32_t bar = full_bar(si);
           mbar_expect_tx(bar, C::STAGE_BYTES);
-          if constexpr (BS_LAST) {
+          if constexpr (IN_LAST) {
 #pragma unroll
-            for (int xb = 0; xb < NT / C::NBOX; ++xb)
+            for (int xb = 0; xb < C::XN / C::NBOX; ++xb)
               tma_load_4d(dst + xb * KC * 128, &tmX, bar, n0 + xb * C::NBOX, l, kc * KC, i + xi0);
           } else {
             tma_load_3d(dst, &tmX, bar, kc * KC, i, n0 + xn0);
           }
           if constexpr (!WRES) {
 #pragma unroll
-            for (int wb = 0; wb < (BS_LAST ? 128 : NT) / C::NBOX; ++wb)
+            for (int wb = 0; wb < C::WJ / C::NBOX; ++wb)
               tma_load_3d(dst + C::XB + wb * KC * 128, &tmW, bar, j0 + wb * C::NBOX, kc * KC, blk + wblk0);
           }
           KSMM_TRACE(0, 5);
@@ -263,11 +274,11 @@ __global__ void __launch_bounds__(kThreads, 1)
           KSMM_TRACE(1, 15);
           const uint32_t xsrc = ring0 + si * C::STAGE_BYTES;
           const uint32_t wsrc = WRES ? wres0 + kc * C::WB : xsrc + C::XB;
-          const uint32_t xlo = (xsrc >> 4) | (BS_LAST ? kLboMN : kLboK);
+          const uint32_t xlo = (xsrc >> 4) | (IN_LAST ? kLboMN : kLboK);
           const uint32_t wlo = (wsrc >> 4) | kLboMN;
 #pragma unroll
           for (int k = 0; k < KC / C::UK; ++k) {
-            const uint32_t xl = xlo + k * (BS_LAST ? kStepMN : kStepK);
+            const uint32_t xl = xlo + k * (IN_LAST ? kStepMN : kStepK);
             const uint32_t wl = wlo + k * kStepMN;
             const uint64_t xdesc = (static_cast<uint64_t>(kDescHi) << 32) | xl;
             const uint64_t wdesc = (static_cast<uint64_t>(kDescHi) << 32) | wl;
@@ -308,7 +319,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int blk = static_cast<int>(row / P.tiles_n);
       const int tn = static_cast<int>(row % P.tiles_n);
       const int i = blk / d, l = blk % d;
-      const int n0 = tn * (BS_LAST ? NT : 128);
+      const int n0 = tn * C::XN;
       const uint32_t buf = ut & 1u, bph = (ut >> 1) & 1u;
       if (tron) KSMM_TRACE(trole, 20);
       int got = 1;
@@ -558,10 +569,10 @@ int num_sms() {
   return n;
 }
 
-template <bool BS_LAST, int ES, int OS, int NT, int KC, bool WRES, int NWC, int SX>
+template <bool IN_LAST, bool OUT_LAST, int ES, int OS, int NT, int KC, bool WRES, int NWC, int SX>
 static int launch_one(const Problem& p, cudaStream_t stream) {
-  using C = Cfg<BS_LAST, ES, OS, NT, KC, WRES, NWC, SX>;
-  auto kern = ksmm_tc_kernel<BS_LAST, ES, OS, NT, KC, WRES, NWC, SX>;
+  using C = Cfg<IN_LAST, OUT_LAST, ES, OS, NT, KC, WRES, NWC, SX>;
+  auto kern = ksmm_tc_kernel<IN_LAST, OUT_LAST, ES, OS, NT, KC, WRES, NWC, SX>;
   static std::atomic<bool> attr_set[64];  // zero-initialised; set once per device (a repeated set is harmless)
   int dev = 0;
   cudaGetDevice(&dev);
@@ -592,48 +603,49 @@ static int launch_one(const Problem& p, cudaStream_t stream) {
   P.bias = p.bias;
   P.out_dtype = p.out_dtype;
   P.act = p.activation;
-  P.rg_d = (!BS_LAST && OS == 2) ? p.out_regroup_d : 0;
+  P.rg_d = (!OUT_LAST && OS == 2) ? p.out_regroup_d : 0;
   P.rg_c = p.out_regroup_c;
   P.groups = static_cast<int>(G);
   P.gx = GX > 1 ? 1 : 0;
   P.status = status_word();
   if (!P.status) return set_error(KSMM_ERR_CUDA, "cannot resolve the device status word");
   const uint32_t fmt = p.in_dtype == KSMM_BF16 ? 1u : 0u;  // f16 / e4m3 = 0, bf16 = 1
-  uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) |
+  // fp32 accumulate; bit 15 / 16: the A / B operand is MN-major.  Weights always are; the input
+  // is when it is batch-last.  A = weights for a batch-last output, else the input.
+  const uint32_t a_mn = (OUT_LAST || IN_LAST) ? 1u : 0u, b_mn = (!OUT_LAST || IN_LAST) ? 1u : 0u;
+  uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (a_mn << 15) | (b_mn << 16) |
                    (static_cast<uint32_t>(NT >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
-  if (BS_LAST) {
-    idesc |= (1u << 15);  // A (weights) is MN-major as well
+  if (IN_LAST) {
     const uint64_t xd[4] = {B, d, c, GX * a};
     const uint64_t xs[4] = {1, B, d * B, c * d * B};
     const uint32_t xb[4] = {static_cast<uint32_t>(C::NBOX), 1, static_cast<uint32_t>(KC), 1};
     if ((st = encode_map(&tmX, p.in_dtype, 4, p.in, xd, xs, xb)) != KSMM_OK) return st;
+  } else {
+    const uint64_t xd[3] = {c, a, GX * B};
+    const uint64_t xs[3] = {1, c, a * c};
+    const uint32_t xb[3] = {static_cast<uint32_t>(KC), 1, static_cast<uint32_t>(C::XN)};
+    if ((st = encode_map(&tmX, p.in_dtype, 3, p.in, xd, xs, xb)) != KSMM_OK) return st;
+  }
+  if (OUT_LAST) {
     const uint64_t yd[4] = {B, d, b, G * a};
     const uint64_t ys[4] = {1, B, d * B, b * d * B};
     const uint32_t yb[4] = {static_cast<uint32_t>(C::CB), 1, 32, 1};  // one epilogue warp's rows
     if ((st = encode_map(&tmY, p.out_dtype, 4, p.out, yd, ys, yb)) != KSMM_OK) return st;
-    P.tiles_n = static_cast<int>((B + NT - 1) / NT);
-    P.tiles_j = static_cast<int>((b + 127) / 128);
+  } else if (p.out_regroup_d > 0 && OS == 2) {
+    // regrouped output (k2, l2, i2, n): a staging tile of 64 features is d2 runs of 64 / d2
+    const uint64_t c2 = p.out_regroup_c, d2 = p.out_regroup_d;
+    const uint64_t yd[4] = {c2, d2, a * b / (c2 * d2), B};
+    const uint64_t ys[4] = {1, c2, c2 * d2, a * b};
+    const uint32_t yb[4] = {static_cast<uint32_t>(C::CB / d2), static_cast<uint32_t>(d2), 1, 32};
+    if ((st = encode_map(&tmY, p.out_dtype, 4, p.out, yd, ys, yb, false)) != KSMM_OK) return st;
   } else {
-    const uint64_t xd[3] = {c, a, GX * B};
-    const uint64_t xs[3] = {1, c, a * c};
-    const uint32_t xb[3] = {static_cast<uint32_t>(KC), 1, 128};
-    if ((st = encode_map(&tmX, p.in_dtype, 3, p.in, xd, xs, xb)) != KSMM_OK) return st;
-    if (p.out_regroup_d > 0 && OS == 2) {
-      // regrouped output (k2, l2, i2, n): a staging tile of 64 features is d2 runs of 64 / d2
-      const uint64_t c2 = p.out_regroup_c, d2 = p.out_regroup_d;
-      const uint64_t yd[4] = {c2, d2, a * b / (c2 * d2), B};
-      const uint64_t ys[4] = {1, c2, c2 * d2, a * b};
-      const uint32_t yb[4] = {static_cast<uint32_t>(C::CB / d2), static_cast<uint32_t>(d2), 1, 32};
-      if ((st = encode_map(&tmY, p.out_dtype, 4, p.out, yd, ys, yb, false)) != KSMM_OK) return st;
-    } else {
-      const uint64_t yd[3] = {b, a, G * B};
-      const uint64_t ys[3] = {1, b, a * b};
-      const uint32_t yb[3] = {static_cast<uint32_t>(C::CB), 1, 32};
-      if ((st = encode_map(&tmY, p.out_dtype, 3, p.out, yd, ys, yb)) != KSMM_OK) return st;
-    }
-    P.tiles_n = static_cast<int>((B + 127) / 128);
-    P.tiles_j = static_cast<int>((b + NT - 1) / NT);
+    const uint64_t yd[3] = {b, a, G * B};
+    const uint64_t ys[3] = {1, b, a * b};
+    const uint32_t yb[3] = {static_cast<uint32_t>(C::CB), 1, 32};
+    if ((st = encode_map(&tmY, p.out_dtype, 3, p.out, yd, ys, yb)) != KSMM_OK) return st;
   }
+  P.tiles_n = static_cast<int>((B + C::XN - 1) / C::XN);
+  P.tiles_j = static_cast<int>((b + C::WJ - 1) / C::WJ);
   P.idesc = idesc;
   const int sms = num_sms();
   if (sms <= 0) return set_error(KSMM_ERR_NO_DEVICE, "no CUDA device");
@@ -660,12 +672,12 @@ static int launch_one(const Problem& p, cudaStream_t stream) {
 // the first is used when all k chunks of the weight tile fit in its NWC slots.
 //   <layout, ES, OS, N tile, bytes of k per chunk row, resident weight chunks,
 //    ring stages (weight-stationary), ring stages (streaming)>
-template <bool BS_LAST, int ES, int OS, int NT, int KCB, int NWC, int SX_W, int SX_S>
+template <bool IN_LAST, bool OUT_LAST, int ES, int OS, int NT, int KCB, int NWC, int SX_W, int SX_S>
 static int launch_flavour(const Problem& p, cudaStream_t stream) {
   constexpr int KC = KCB / ES;
   const int nk = (p.c + KC - 1) / KC;
-  if (nk <= NWC) return launch_one<BS_LAST, ES, OS, NT, KC, true, NWC, SX_W>(p, stream);
-  return launch_one<BS_LAST, ES, OS, NT, KC, false, 0, SX_S>(p, stream);
+  if (nk <= NWC) return launch_one<IN_LAST, OUT_LAST, ES, OS, NT, KC, true, NWC, SX_W>(p, stream);
+  return launch_one<IN_LAST, OUT_LAST, ES, OS, NT, KC, false, 0, SX_S>(p, stream);
 }
 
 template <bool BS_LAST, int ES, int OS>
@@ -674,24 +686,39 @@ static int launch_cfg(const Problem& p, int config, cudaStream_t stream) {
   // batch-first, 16-bit: input chunk = 16 KB, weight chunk = NT x 64 x 2 bytes
   if constexpr (BS_LAST) {
     switch (config) {
-      case 0: return launch_flavour<true, ES, OS, 256, 128, 3, 4, 4>(p, stream);
-      case 1: return launch_flavour<true, ES, OS, 128, 128, 6, 6, 6>(p, stream);
-      case 2: return launch_flavour<true, ES, OS, 256, 128, 1, 5, 4>(p, stream);
-      case 3: return launch_flavour<true, ES, OS, 128, 128, 3, 8, 6>(p, stream);
+      case 0: return launch_flavour<true, true, ES, OS, 256, 128, 3, 4, 4>(p, stream);
+      case 1: return launch_flavour<true, true, ES, OS, 128, 128, 6, 6, 6>(p, stream);
+      case 2: return launch_flavour<true, true, ES, OS, 256, 128, 1, 5, 4>(p, stream);
+      case 3: return launch_flavour<true, true, ES, OS, 128, 128, 3, 8, 6>(p, stream);
       case 4:
-        if constexpr (ES == 2) return launch_flavour<true, ES, OS, 64, 128, 6, 8, 8>(p, stream);
+        if constexpr (ES == 2) return launch_flavour<true, true, ES, OS, 64, 128, 6, 8, 8>(p, stream);
         break;
     }
   } else {
     switch (config) {
-      case 0: return launch_flavour<false, ES, OS, 256, 128, 3, 6, 4>(p, stream);
-      case 1: return launch_flavour<false, ES, OS, 128, 128, 6, 6, 6>(p, stream);
-      case 2: return launch_flavour<false, ES, OS, 256, 128, 1, 10, 4>(p, stream);
-      case 3: return launch_flavour<false, ES, OS, 128, 128, 3, 8, 6>(p, stream);
+      case 0: return launch_flavour<false, false, ES, OS, 256, 128, 3, 6, 4>(p, stream);
+      case 1: return launch_flavour<false, false, ES, OS, 128, 128, 6, 6, 6>(p, stream);
+      case 2: return launch_flavour<false, false, ES, OS, 256, 128, 1, 10, 4>(p, stream);
+      case 3: return launch_flavour<false, false, ES, OS, 128, 128, 3, 8, 6>(p, stream);
       case 4:
-        if constexpr (ES == 2) return launch_flavour<false, ES, OS, 64, 128, 6, 8, 8>(p, stream);
+        if constexpr (ES == 2) return launch_flavour<false, false, ES, OS, 64, 128, 6, 8, 8>(p, stream);
         break;
     }
+  }
+  return set_error(KSMM_ERR_BAD_ARGUMENT, "tensor-core family: no configuration %d", config);
+}
+
+// Layout-changing factors (d = 1, 16-bit): the tile shapes of the output's layout, configurations
+// 0, 1 and 4 of it (the other two differ only in ring depth).
+template <bool IN_LAST>
+static int launch_mixed(const Problem& p, int config, cudaStream_t stream) {
+  constexpr bool OUT_LAST = !IN_LAST;
+  if (config == 2) config = 0;
+  if (config == 3) config = 1;
+  switch (config) {
+    case 0: return launch_flavour<IN_LAST, OUT_LAST, 2, 2, 256, 128, 3, OUT_LAST ? 4 : 6, 4>(p, stream);
+    case 1: return launch_flavour<IN_LAST, OUT_LAST, 2, 2, 128, 128, 6, 6, 6>(p, stream);
+    case 4: return launch_flavour<IN_LAST, OUT_LAST, 2, 2, 64, 128, 6, 8, 8>(p, stream);
   }
   return set_error(KSMM_ERR_BAD_ARGUMENT, "tensor-core family: no configuration %d", config);
 }
@@ -711,6 +738,18 @@ bool tc_config_supported(const Problem& p, int config, bool check_pointers) {
     if (static_cast<int64_t>(p.groups) * p.batch > 0x7fffffffLL ||
         static_cast<int64_t>(p.groups) * p.a * p.d > 0x7fffffffLL)
       return false;
+  }
+  const bool out_last = p.out_bs_last < 0 ? p.bs_last != 0 : p.out_bs_last != 0;
+  if (out_last != (p.bs_last != 0)) {
+    // a factor that changes the layout: 16-bit, d = 1, no groups, no regrouping
+    if (p.d != 1 || p.groups > 1 || p.out_regroup_d || p.in_regrouped) return false;
+    if ((p.in_dtype != KSMM_F16 && p.in_dtype != KSMM_BF16) || p.out_dtype != p.in_dtype) return false;
+    if (p.batch <= 0 || p.batch > 0x7fffffffLL) return false;
+    if (p.b % 8 != 0 || p.c % 8 != 0 || p.batch % 8 != 0) return false;   // 16-byte strides on both sides
+    if (check_pointers && (reinterpret_cast<uintptr_t>(p.in) % 16 || reinterpret_cast<uintptr_t>(p.w) % 16 ||
+                           reinterpret_cast<uintptr_t>(p.out) % 16))
+      return false;
+    return true;
   }
   if (p.in_dtype == KSMM_F32) return config >= 0 && config <= 3 && tc_f32x3_supported(p, check_pointers);
   if (!p.bs_last && p.d != 1)
@@ -762,8 +801,9 @@ int tc_default_config(const Problem& p) {
   // then the kernel without the transposer stage) measured slower for a single factor (94 us
   // against 85 us for (1,768,192,4) fp16); chains use its kernel when the previous factor can
   // store the intermediate regrouped for free.
-  if (!p.bs_last && p.d != 1) return 0;
-  if (p.bs_last) return p.batch >= 256 * 148 / 2 || p.batch >= 4096 ? 0 : 1;
+  const bool out_last = p.out_bs_last < 0 ? p.bs_last != 0 : p.out_bs_last != 0;
+  if (out_last == (p.bs_last != 0) && !p.bs_last && p.d != 1) return 0;
+  if (out_last) return p.batch >= 256 * 148 / 2 || p.batch >= 4096 ? 0 : 1;
   return p.b > 128 ? 0 : (p.b > 64 ? 1 : 4);
 }
 
@@ -775,6 +815,8 @@ int tc_launch(const Problem& p, int config, cudaStream_t stream) {
                      "bs_last %d (alignment or layout rule)",
                      p.a, p.b, p.c, p.d, static_cast<long long>(p.batch), p.in_dtype, p.bs_last);
   const bool last = p.bs_last != 0;
+  const bool out_last = p.out_bs_last < 0 ? last : p.out_bs_last != 0;
+  if (out_last != last) return last ? tc::launch_mixed<true>(p, config, stream) : tc::launch_mixed<false>(p, config, stream);
   if (p.in_dtype == KSMM_F32) return tc_f32x3_launch(p, config, stream);
   if (!last && p.d != 1) return config == 1 ? tc_bsfirst_dp_launch(p, stream) : tc_bsfirst_d_launch(p, stream);
   if (p.out_regroup_d > 0 && !tc_can_regroup_output(p))

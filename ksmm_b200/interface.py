@@ -61,7 +61,7 @@ class KSLinear(nn.Module):
     def __init__(self, patterns, weights=None, bias=True, algo="kernel",
                  dtype: torch.dtype = torch.float16, bs_last: bool = False, vsize: int = 4,
                  device: str = "cuda", fuse_chain: bool = True, activation=None,
-                 requires_grad: bool = False):
+                 requires_grad: bool = False, out_bs_last=None):
         super().__init__()
         # `requires_grad` is an addition as well: the reference's kernel path is inference-only (its
         # backward is a stub).  With trainable factors the forward runs factor by factor through
@@ -90,6 +90,13 @@ class KSLinear(nn.Module):
         self.weights = weights
         self.device = device
         self.fuse_chain = fuse_chain
+        # `out_bs_last` (an addition; default: the input's layout) makes the layer return the other
+        # layout, as a 2-D tensor: (out_size, batch) or (batch, out_size).  Two layers of an MLP can
+        # then keep the activations between them batch-last inside a batch-first network, which is
+        # the fast form for factors with d > 1.
+        self.out_bs_last = bs_last if out_bs_last is None else bool(out_bs_last)
+        if self.out_bs_last != bool(bs_last) and dtype == torch.float8_e4m3fn:
+            raise ValueError("fp8 layers keep one layout")
         if str(self.device) == "cpu":
             raise Exception("kernel expects device='cuda'.")
         _k.dtype_code(dtype)  # validates
@@ -145,6 +152,8 @@ class KSLinear(nn.Module):
                 y = _k.FactorFunction.apply(y, f, self.bs_last, *p)
             if self.bias is not None:
                 y = y + (self.bias.reshape(-1, 1) if self.bs_last else self.bias.reshape(1, -1))
+            if self.out_bs_last != bool(self.bs_last):
+                y = y.t().contiguous()
             if self.activation == "gelu":
                 y = torch.nn.functional.gelu(y)
             elif self.activation == "relu":
@@ -153,7 +162,9 @@ class KSLinear(nn.Module):
         if self.fuse_chain or self.num_mat == 1:
             ws = self._ensure_workspace(x)
             return _k.chain_forward(x, list(self.factors), self.patterns, self.bs_last, bias=bias,
-                                    workspace=ws, activation=self.activation)
+                                    workspace=ws, activation=self.activation, out_bs_last=self.out_bs_last)
+        if self.out_bs_last != bool(self.bs_last):
+            raise ValueError("a layer that changes the layout runs as one chain call (fuse_chain=True)")
         y = x
         for idx, (p, f) in enumerate(zip(self.patterns, self.factors)):
             last = idx + 1 == self.num_mat
@@ -166,8 +177,9 @@ class KSLinear(nn.Module):
         lib = _lib.load()
         batch = x.shape[1] if self.bs_last else x.shape[0]
         flat = [v for p in self.patterns for v in p]
-        need = lib.ksmm_cu_chain_workspace_bytes_ex(self.num_mat, _lib.int32_array(flat), batch,
-                                                    _k.dtype_code(x.dtype), int(bool(self.bs_last)))
+        need = lib.ksmm_cu_chain_workspace_bytes_layouts(self.num_mat, _lib.int32_array(flat), batch,
+                                                         _k.dtype_code(x.dtype), int(bool(self.bs_last)),
+                                                         int(bool(self.out_bs_last)))
         if need == 0:
             return None
         ws = self._workspace
@@ -193,6 +205,8 @@ class KSLinear(nn.Module):
 
     def post_process(self, tensor, output):
         # the bias has already been added by the last factor's epilogue
+        if self.out_bs_last != bool(self.bs_last):
+            return output              # 2-D, in the requested layout
         if self.bs_last:
             return output.view(self.out_size, *tensor.shape[1:])
         return output.view(*tensor.shape[:-1], self.out_size)

@@ -148,15 +148,18 @@ def forward(input, factor, bs_last, a, b, c, d, dtype, vsize=4):
 
 
 def chain_forward(input, factors, patterns, bs_last, bias=None, workspace=None, out=None,
-                  activation=None):
-    """All factors of one KSLinear in one library call (``ksmm_cu_chain_forward_act``).
+                  activation=None, out_bs_last=None):
+    """All factors of one KSLinear in one library call (``ksmm_cu_chain_forward_layouts``).
 
     ``factors[f]`` is the kernel-format (a*d*c, b) weight of ``patterns[f]``;
     ``patterns[0]`` is applied first.  ``bias`` (out features, output dtype)
     and ``activation`` (None, "gelu" or "relu") are fused into the last factor.
+    ``out_bs_last`` (default: same as ``bs_last``) asks for the output in the other
+    layout: (out, batch) when true, (batch, out) when false.
     """
     lib = _lib.load()
     bs_last = int(bool(bs_last))
+    out_last = bs_last if out_bs_last is None else int(bool(out_bs_last))
     nf = len(patterns)
     if nf == 0 or len(factors) != nf:
         raise ValueError("need one factor per pattern")
@@ -170,24 +173,26 @@ def chain_forward(input, factors, patterns, bs_last, bias=None, workspace=None, 
     batch = input.shape[1] if bs_last else input.shape[0]
     la, lb, lc, ld = patterns[-1]
     n_out = la * lb * ld
-    shape = (n_out, batch) if bs_last else (batch, n_out)
+    shape = (n_out, batch) if out_last else (batch, n_out)
     if out is None:
         out = torch.empty(shape, dtype=input.dtype, device=input.device)
+    elif tuple(out.shape) != shape or out.dtype != input.dtype or not out.is_contiguous():
+        raise ValueError("out has the wrong shape, dtype or strides")
     flat = [int(v) for p in patterns for v in p]
     pat = _lib.int32_array(flat)
     code = dtype_code(input.dtype)
-    need = lib.ksmm_cu_chain_workspace_bytes_ex(nf, pat, batch, code, bs_last)
+    need = lib.ksmm_cu_chain_workspace_bytes_layouts(nf, pat, batch, code, bs_last, out_last)
     if need > 0 and (workspace is None or workspace.numel() * workspace.element_size() < need):
         workspace = torch.empty(need, dtype=torch.uint8, device=input.device)
     if bias is not None and (bias.numel() != n_out or bias.dtype != input.dtype):
         raise ValueError("bias must hold out_size elements of the input dtype")
     vals = (ctypes.c_void_p * nf)(*[w.data_ptr() for w in factors])
     with torch.cuda.device(input.device):
-        _lib.check(lib.ksmm_cu_chain_forward_act(
+        _lib.check(lib.ksmm_cu_chain_forward_layouts(
             input.data_ptr(), vals, out.data_ptr(), bias.data_ptr() if bias is not None else None,
             workspace.data_ptr() if workspace is not None else None,
             workspace.numel() * workspace.element_size() if workspace is not None else 0,
-            batch, nf, pat, code, bs_last, _lib.ACTIVATIONS[activation], _stream_ptr(input.device)))
+            batch, nf, pat, code, bs_last, out_last, _lib.ACTIVATIONS[activation], _stream_ptr(input.device)))
     return out
 
 

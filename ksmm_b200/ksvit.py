@@ -35,29 +35,36 @@ def posemb_sincos_2d(h, w, dim, temperature=10000.0):
 
 
 class KSFeedForward(nn.Module):
-    def __init__(self, dim, dtype, device, dense=False, fuse_gelu=False):
+    """LayerNorm -> fc1 -> GELU -> fc2.  `layout_plan` (default) keeps the 3072-feature activations
+    between the two KSLinear layers batch-last: fc1 reads batch-first tokens and returns
+    (3072, tokens), fc2 reads that and returns (tokens, 768).  Their d = 1 factors change the
+    layout inside the kernel, so the d = 4 factors run in their fast batch-last form and nothing
+    is transposed; the GELU is element-wise and does not care.  `fuse_gelu` applies it in the
+    epilogue of fc1's last factor instead of as a separate PyTorch kernel (model/vit.py:416-431)."""
+
+    def __init__(self, dim, dtype, device, dense=False, fuse_gelu=True, layout_plan=True):
         super().__init__()
         self.norm = nn.LayerNorm(dim)
         self.dense = dense
         self.fuse_gelu = fuse_gelu and not dense
+        self.layout_plan = layout_plan and not dense
         if dense:  # same shapes with nn.Linear, for an accuracy / speed comparison
             self.fc1 = nn.Linear(dim, 4 * dim)
             self.fc2 = nn.Linear(4 * dim, dim)
         else:
-            # fuse_gelu: the GELU runs in the epilogue of fc1's last factor instead of as a separate
-            # PyTorch kernel (model/vit.py:416-431).  Off by default: that factor is (1,768,192,4), whose
-            # four accumulators fill TMEM, so its epilogue cannot overlap the MMAs and the erf
-            # arithmetic (measured) costs more there than the separate element-wise kernel.
+            mid_last = True if self.layout_plan else False
             self.fc1 = KSLinear(FC1_PATTERNS, bias=True, algo="kernel", dtype=dtype, bs_last=False,
-                                device=device, activation="gelu" if self.fuse_gelu else None)
-            self.fc2 = KSLinear(FC2_PATTERNS, bias=True, algo="kernel", dtype=dtype, bs_last=False,
-                                device=device)
+                                device=device, activation="gelu" if self.fuse_gelu else None,
+                                out_bs_last=mid_last)
+            self.fc2 = KSLinear(FC2_PATTERNS, bias=True, algo="kernel", dtype=dtype, bs_last=mid_last,
+                                device=device, out_bs_last=False)
 
     def forward(self, x):
         h = self.fc1(self.norm(x))
         if not self.fuse_gelu:
             h = F.gelu(h)
-        return self.fc2(h)
+        y = self.fc2(h)
+        return y.view(x.shape) if self.layout_plan else y
 
 
 class Attention(nn.Module):
@@ -77,14 +84,14 @@ class Attention(nn.Module):
 
 class KSViTB(nn.Module):
     def __init__(self, dtype=torch.float16, device="cuda", depth=12, dim=768, num_classes=1000,
-                 dense_mlp=False, fuse_gelu=False):
+                 dense_mlp=False, fuse_gelu=True, layout_plan=True):
         super().__init__()
         self.patch = 16
         patch_dim = 3 * 16 * 16
         self.embed = nn.Sequential(nn.LayerNorm(patch_dim), nn.Linear(patch_dim, dim), nn.LayerNorm(dim))
         self.register_buffer("pos", posemb_sincos_2d(14, 14, dim), persistent=False)
         self.layers = nn.ModuleList(
-            [nn.ModuleList([Attention(dim), KSFeedForward(dim, dtype, device, dense_mlp, fuse_gelu)])
+            [nn.ModuleList([Attention(dim), KSFeedForward(dim, dtype, device, dense_mlp, fuse_gelu, layout_plan)])
              for _ in range(depth)])
         self.norm = nn.LayerNorm(dim)
         self.head = nn.Linear(dim, num_classes)
