@@ -96,6 +96,8 @@ typedef struct {
   void* scratch;          /* optional device memory for the paths that need a  */
   size_t scratch_bytes;   /* second copy of a tensor (ksmm_cu_layout_scratch_bytes); */
                           /* NULL = a library-owned buffer per (device, stream) */
+  const void* residual;   /* optional tensor shaped, laid out and typed like   */
+                          /* the output, added last: out = act(...) + residual */
 } ksmm_forward_desc_t;
 
 /* Library version: major*10000 + minor*100 + patch. */
@@ -190,6 +192,32 @@ KSMM_API int ksmm_cu_chain_forward_layouts(const void* input, const void* const*
                                   int64_t batch, int nfactors, const int32_t* patterns,
                                   int dtype, int bs_last, int out_bs_last, int activation,
                                   void* stream);
+
+/*
+ * The chain call with every option in one descriptor, among them a residual:
+ * out = act(K_n ... K_1 x + bias) + residual, the `x + ff(x)` of a transformer
+ * block (src/ksmm_py/model/vit.py:574-577 adds it as a separate PyTorch
+ * kernel).  `residual` has the output's shape, layout and type; the 16-bit
+ * tensor kernel adds it in its epilogue, other kernels in a pass after them.
+ * out_layout: 0 = the input's layout, 1 = batch-first, 2 = batch-last.
+ */
+typedef struct {
+  const void* input;
+  const void* const* values;   /* nfactors kernel-format weights                 */
+  void* output;
+  const void* bias;            /* optional, out features                         */
+  const void* residual;        /* optional, shaped like the output               */
+  void* workspace;             /* ksmm_cu_chain_workspace_bytes_layouts          */
+  size_t workspace_bytes;
+  int64_t batch;
+  int32_t nfactors;
+  const int32_t* patterns;     /* 4 * nfactors integers                          */
+  int32_t dtype;               /* ksmm_dtype_t (not fp8)                         */
+  int32_t bs_last;             /* layout of the input                            */
+  int32_t out_layout;          /* 0 = as the input, 1 = batch-first, 2 = batch-last */
+  int32_t activation;          /* ksmm_activation_t                              */
+} ksmm_chain_desc_t;
+KSMM_API int ksmm_cu_chain_forward_desc(const ksmm_chain_desc_t* desc, void* stream);
 
 /*
  * Several problems of one pattern in one call ("groups"): the q, k and v

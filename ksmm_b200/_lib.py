@@ -38,7 +38,7 @@ EXPORTS = (
     "ksmm_cu_alloc_count", "ksmm_cu_debug_wait_probe",
     "ksmm_cu_chain_forward_host_async", "ksmm_cu_host_wait",
     "ksmm_cu_grouped_forward", "ksmm_cu_grouped_chain_forward",
-    "ksmm_cu_chain_workspace_bytes_layouts", "ksmm_cu_chain_forward_layouts",
+    "ksmm_cu_chain_workspace_bytes_layouts", "ksmm_cu_chain_forward_layouts", "ksmm_cu_chain_forward_desc",
     "ksmm_cu_backward_input_workspace_bytes", "ksmm_cu_backward_input",
     "ksmm_cu_backward_weights_workspace_bytes", "ksmm_cu_backward_weights",
 )
@@ -54,6 +54,18 @@ class ForwardDesc(ctypes.Structure):
         ("algo", ctypes.c_int32), ("config", ctypes.c_int32), ("alpha", ctypes.c_float),
         ("activation", ctypes.c_int32),
         ("scratch", ctypes.c_void_p), ("scratch_bytes", ctypes.c_size_t),
+        ("residual", ctypes.c_void_p),
+    ]
+
+
+class ChainDesc(ctypes.Structure):
+    """Mirror of ksmm_chain_desc_t."""
+    _fields_ = [
+        ("input", ctypes.c_void_p), ("values", ctypes.POINTER(ctypes.c_void_p)), ("output", ctypes.c_void_p),
+        ("bias", ctypes.c_void_p), ("residual", ctypes.c_void_p), ("workspace", ctypes.c_void_p),
+        ("workspace_bytes", ctypes.c_size_t), ("batch", ctypes.c_int64), ("nfactors", ctypes.c_int32),
+        ("patterns", ctypes.POINTER(ctypes.c_int32)), ("dtype", ctypes.c_int32), ("bs_last", ctypes.c_int32),
+        ("out_layout", ctypes.c_int32), ("activation", ctypes.c_int32),
     ]
 
 
@@ -108,6 +120,8 @@ def load():
     lib.ksmm_cu_chain_forward_layouts.restype = i32
     lib.ksmm_cu_chain_forward_layouts.argtypes = [vp, ctypes.POINTER(vp), vp, vp, vp, ctypes.c_size_t, i64,
                                                   i32, ctypes.POINTER(ctypes.c_int32), i32, i32, i32, i32, vp]
+    lib.ksmm_cu_chain_forward_desc.restype = i32
+    lib.ksmm_cu_chain_forward_desc.argtypes = [ctypes.POINTER(ChainDesc), vp]
     lib.ksmm_cu_grouped_forward.restype = i32
     lib.ksmm_cu_grouped_forward.argtypes = [vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, vp]
     lib.ksmm_cu_grouped_chain_forward.restype = i32

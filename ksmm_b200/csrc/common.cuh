@@ -142,6 +142,9 @@ struct Problem {
   int out_regroup_d = 0, out_regroup_c = 0;
   int in_regrouped = 0;
   int activation = 0;  // ksmm_activation_t, applied after alpha and bias
+  // optional tensor of the output's shape, layout and type, added last:
+  // out = act(alpha * K x + bias) + residual
+  const void* residual = nullptr;
   // Caller-provided memory for the paths that need a second copy of a tensor (layout conversion,
   // regrouping).  With scratch == nullptr the library's own per-stream scratch is used, unless
   // no_alloc is set: then the call fails with KSMM_ERR_WORKSPACE instead of allocating.

@@ -126,6 +126,31 @@ __global__ void __launch_bounds__(256) activation_kernel(T* data, int64_t n, int
                                             : apply_activation(ElemTraits<T>::to_float(data[q]), act));
 }
 
+// out += residual, for the kernels whose epilogue has no residual input
+template <typename T>
+__global__ void __launch_bounds__(256) residual_kernel(T* data, const T* __restrict__ res, int64_t n) {
+  for (int64_t q = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; q < n;
+       q += static_cast<int64_t>(gridDim.x) * 256)
+    data[q] = ElemTraits<T>::from_float(ElemTraits<T>::to_float(data[q]) + ElemTraits<T>::to_float(res[q]));
+}
+
+static int residual_pass(const Problem& p, cudaStream_t stream) {
+  const int64_t n = static_cast<int64_t>(p.a) * p.b * p.d * p.batch;
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>((n + 255) / 256, 148 * 16));
+  if (p.out_dtype == KSMM_F32)
+    residual_kernel<float><<<grid, 256, 0, stream>>>(static_cast<float*>(p.out), static_cast<const float*>(p.residual), n);
+  else if (p.out_dtype == KSMM_F16)
+    residual_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<__half*>(p.out), static_cast<const __half*>(p.residual), n);
+  else
+    residual_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(p.out),
+                                                             static_cast<const __nv_bfloat16*>(p.residual), n);
+  count_launch();
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess)
+    return set_error(KSMM_ERR_CUDA, "residual kernel launch failed: %s", cudaGetErrorString(err));
+  return KSMM_OK;
+}
+
 static int simt_launch(const Problem& p, int config, cudaStream_t stream) {
   int st = simt_launch_raw(p, config, stream);
   if (st != KSMM_OK || p.activation == 0) return st;
@@ -294,6 +319,13 @@ static int forward_via_transpose(const Problem& p, cudaStream_t stream) {
 }
 
 static int run_family(const Problem& p, int algo, int config, cudaStream_t stream) {
+  if (p.residual != nullptr && !(algo == KSMM_ALGO_TC && tc_fuses_residual(p))) {
+    // this kernel has no residual input: add it in a pass over the output
+    Problem q = p;
+    q.residual = nullptr;
+    int st = run_family(q, algo, config, stream);
+    return st != KSMM_OK ? st : residual_pass(p, stream);
+  }
   if (algo == KSMM_ALGO_SIMT) return simt_launch(p, config, stream);
   if (algo == KSMM_ALGO_TC) return tc_launch(p, config, stream);
   if (algo == KSMM_ALGO_CONVERT) return forward_via_transpose(p, stream);
@@ -355,6 +387,7 @@ static Problem problem_of(const ksmm_forward_desc_t& dsc) {
   p.activation = dsc.activation;
   p.scratch = dsc.scratch;
   p.scratch_bytes = dsc.scratch_bytes;
+  p.residual = dsc.residual;
   return p;
 }
 
@@ -623,7 +656,8 @@ static int chain_walk(bool run, const void* input, const void* const* values, vo
                       const void* bias, void* workspace, size_t inter_bytes, void* scratch,
                       size_t scratch_bytes, int no_alloc, int64_t batch, int nfactors,
                       const int32_t* patterns, int dtype, int bs_last, int out_bs_last, int activation,
-                      cudaStream_t stream, size_t* scratch_max, int allow_switch);
+                      cudaStream_t stream, size_t* scratch_max, int allow_switch,
+                      const void* residual = nullptr);
 
 // One pass over a chain: either plans it (run == false: returns through *scratch_max the layout
 // scratch it needs under the current dispatch: transposed copies at the chain's ends plus the
@@ -632,7 +666,7 @@ static int chain_walk(bool run, const void* input, const void* const* values, vo
                       const void* bias, void* workspace, size_t inter_bytes, void* scratch,
                       size_t scratch_bytes, int no_alloc, int64_t batch, int nfactors,
                       const int32_t* patterns, int dtype, int bs_last, int out_bs_last, int activation,
-                      cudaStream_t stream, size_t* scratch_max, int allow_switch) {
+                      cudaStream_t stream, size_t* scratch_max, int allow_switch, const void* residual) {
   if (nfactors > ChainPlan::kMax)
     return set_error(KSMM_ERR_UNSUPPORTED, "chains of more than %d factors", ChainPlan::kMax);
   ChainPlan plan;
@@ -700,6 +734,9 @@ static int chain_walk(bool run, const void* input, const void* const* values, vo
     p.bs_last = plan.in_last[f];
     p.out_bs_last = plan.out_last[f] == plan.in_last[f] ? -1 : plan.out_last[f];
     p.activation = last ? activation : 0;
+    // the residual has the chain output's layout: it can join the last factor's epilogue only when
+    // that factor writes the final layout itself
+    p.residual = (last && !plan.post_transpose) ? residual : nullptr;
     p.scratch = f_scratch; p.scratch_bytes = f_scratch_bytes; p.no_alloc = f_no_alloc;
     const bool same_first = !plan.in_last[f] && !plan.out_last[f];
     // Layout fusion of consecutive batch-first factors: when the next factor has d = 2 or 4 and
@@ -730,12 +767,12 @@ static int chain_walk(bool run, const void* input, const void* const* values, vo
     if (p.out_bs_last >= 0) {
       // a factor that changes the layout: the 16-bit tensor kernel only (the plan checked its shape
       // rules; pointers are the caller's)
-      if (run) st = tc_launch(p, -1, stream);
+      if (run) st = run_family(p, KSMM_ALGO_TC, -1, stream);
     } else if (cur_regrouped) {
       p.in_regrouped = 1;
-      if (run) st = tc_launch(p, 1, stream);
+      if (run) st = run_family(p, KSMM_ALGO_TC, 1, stream);
     } else if (next_regrouped) {
-      if (run) st = tc_launch(p, -1, stream);
+      if (run) st = run_family(p, KSMM_ALGO_TC, -1, stream);
     } else if (run) {
       st = dispatch(p, KSMM_ALGO_AUTO, -1, stream);
     } else {
@@ -755,6 +792,13 @@ static int chain_walk(bool run, const void* input, const void* const* values, vo
     int st = last_layout ? launch_transpose(t_post, output, out_feats, batch, static_cast<int>(es), stream)
                          : launch_transpose(t_post, output, batch, out_feats, static_cast<int>(es), stream);
     if (st != KSMM_OK) return st;
+    if (residual != nullptr) {
+      Problem rp;
+      rp.out = output; rp.residual = residual; rp.out_dtype = dtype;
+      rp.a = pl[0]; rp.b = pl[1]; rp.d = pl[3]; rp.batch = batch;
+      st = residual_pass(rp, stream);
+      if (st != KSMM_OK) return st;
+    }
   }
   if (scratch_max) *scratch_max = pre_bytes + post_bytes + factor_scratch_max;
   return KSMM_OK;
@@ -819,7 +863,8 @@ int ksmm_cu_chain_forward(const void* input, const void* const* values, void* ou
 static int chain_forward_impl(const void* input, const void* const* values, void* output,
                               const void* bias, void* workspace, size_t workspace_bytes, int no_alloc,
                               int64_t batch, int nfactors, const int32_t* patterns, int dtype,
-                              int bs_last, int out_bs_last, int activation, cudaStream_t stream) {
+                              int bs_last, int out_bs_last, int activation, cudaStream_t stream,
+                              const void* residual = nullptr) {
   int st = check_chain(nfactors, patterns, values, dtype, activation);
   if (st != KSMM_OK) return st;
   if (bs_last != 0 && bs_last != 1) return set_error(KSMM_ERR_BAD_ARGUMENT, "bs_last must be 0 or 1");
@@ -838,7 +883,7 @@ static int chain_forward_impl(const void* input, const void* const* values, void
   }
   // layout-changing factors go through TMA on both sides: every buffer has to be 16-byte aligned
   auto al16 = [](const void* q) { return reinterpret_cast<uintptr_t>(q) % 16 == 0; };
-  int allow_switch = al16(input) && al16(output) && al16(workspace) ? 1 : 0;
+  int allow_switch = al16(input) && al16(output) && al16(workspace) && al16(residual) ? 1 : 0;
   for (int f = 0; f < nfactors; ++f) allow_switch &= al16(values[f]) ? 1 : 0;
   if (no_alloc) {
     // refuse before the first launch, not half-way through the chain
@@ -854,7 +899,7 @@ static int chain_forward_impl(const void* input, const void* const* values, void
   }
   return chain_walk(true, input, values, output, bias, workspace, inter, scratch, scratch_bytes, no_alloc,
                     batch, nfactors, patterns, dtype, bs_last, out_bs_last, activation, stream, nullptr,
-                    allow_switch);
+                    allow_switch, residual);
 }
 
 int ksmm_cu_chain_forward_act(const void* input, const void* const* values, void* output,
@@ -864,6 +909,17 @@ int ksmm_cu_chain_forward_act(const void* input, const void* const* values, void
   return chain_forward_impl(input, values, output, bias, workspace, workspace_bytes, /*no_alloc=*/0, batch,
                             nfactors, patterns, dtype, bs_last, bs_last, activation,
                             static_cast<cudaStream_t>(stream));
+}
+
+int ksmm_cu_chain_forward_desc(const ksmm_chain_desc_t* dsc, void* stream) {
+  if (!dsc) return set_error(KSMM_ERR_BAD_ARGUMENT, "null descriptor");
+  const int out_last = dsc->out_layout == 0 ? dsc->bs_last : (dsc->out_layout == 2 ? 1 : 0);
+  if (dsc->out_layout < 0 || dsc->out_layout > 2)
+    return set_error(KSMM_ERR_BAD_ARGUMENT, "out_layout is 0 (as the input), 1 (batch-first) or 2 (batch-last)");
+  return chain_forward_impl(dsc->input, dsc->values, dsc->output, dsc->bias, dsc->workspace,
+                            dsc->workspace_bytes, /*no_alloc=*/0, dsc->batch, dsc->nfactors, dsc->patterns,
+                            dsc->dtype, dsc->bs_last, out_last, dsc->activation,
+                            static_cast<cudaStream_t>(stream), dsc->residual);
 }
 
 int ksmm_cu_chain_forward_layouts(const void* input, const void* const* values, void* output,

@@ -117,6 +117,11 @@ __global__ void __launch_bounds__(kThreadsP, 1)
     *abort_flag = 0;
     fence_mbar_init();
   }
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&tmX);
+    prefetch_tensormap(&tmW);
+    prefetch_tensormap(&tmY);
+  }
   if (warp == 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::TMEM_COLS);
     tmem_relinquish();
@@ -125,6 +130,9 @@ __global__ void __launch_bounds__(kThreadsP, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above overlaps the tail of the previous kernel in the stream; memory comes after this
+  grid_dep_wait();
+  grid_dep_launch();
 
   const int nkc = P.nkc;
   const int tj = static_cast<int>(blockIdx.x % P.tiles_j);
@@ -400,9 +408,9 @@ static int launch_p(const Problem& p, const void* regrouped, cudaStream_t stream
   if (groups > rows) groups = rows;
   P.row_groups = static_cast<uint32_t>(groups);
   const unsigned grid = static_cast<unsigned>(groups * P.tiles_j);
-  kern<<<grid, kThreadsP, C::SMEM_BYTES, stream>>>(tmX, tmW, tmY, P);
+  cudaError_t err = launch_pdl(kern, grid, kThreadsP, C::SMEM_BYTES, stream, tmX, tmW, tmY, P);
   count_launch();
-  cudaError_t err = cudaGetLastError();
+  if (err == cudaSuccess) err = cudaGetLastError();
   if (err != cudaSuccess)
     return set_error(KSMM_ERR_CUDA, "tensor-core kernel launch failed: %s", cudaGetErrorString(err));
   return KSMM_OK;

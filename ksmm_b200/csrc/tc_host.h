@@ -18,6 +18,25 @@ int encode_map(CUtensorMap* tm, int dt, int rank, const void* base, const uint64
 // Device address of the per-device status word (0 = no device-side timeout).
 int* status_word();
 int num_sms();
+// false when the environment variable KSMM_NO_PDL is set (read once): launches are then plain ones
+bool pdl_enabled();
+
+// Launch with the programmatic-stream-serialisation attribute (see grid_dep_wait in tc_ptx.cuh).
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kern)(KArgs...), unsigned grid, unsigned block, size_t smem, cudaStream_t stream,
+                       Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
 
 }  // namespace tc
 }  // namespace ksmm

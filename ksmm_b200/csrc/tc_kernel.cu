@@ -47,6 +47,7 @@
 #include <cuda.h>
 
 #include <atomic>
+#include <cstdlib>
 
 #include <mutex>
 
@@ -79,6 +80,7 @@ struct Params {
   // encodes (group, j tile), so the groups of one input tile run at the same time and share it in L2.
   int groups, gx;
   int tiles_jg;    // tiles_j * groups
+  const void* residual;  // added after the activation; output's layout and type; or nullptr
 };
 
 // WRES = true  ("weight-stationary"): the CTA's weight tile (all NWC k chunks of
@@ -92,7 +94,7 @@ struct Params {
 // (rows of the tile = k, consecutive batch entries) and K-major when it is batch-first (rows =
 // batch entries, consecutive k).  The two mixed combinations (d = 1 only) let a chain change its
 // layout inside a factor at no cost.
-template <bool IN_LAST, bool OUT_LAST, int ES, int OS, int NT, int KC, bool WRES, int NWC, int SX>
+template <bool IN_LAST, bool OUT_LAST, int ES, int OS, int NT, int KC, bool WRES, int NWC, int SX, int STGN = 1>
 struct Cfg {
   static constexpr int NBOX = 128 / ES;        // elements in one 128-byte box row
   static constexpr int UK = 32 / ES;           // k extent of one MMA
@@ -104,14 +106,19 @@ struct Cfg {
   static constexpr int WJ = OUT_LAST ? 128 : NT;           // output features per tile
   static constexpr int STAGE_BYTES = XB + (WRES ? 0 : WB);
   static constexpr int CB = 128 / OS;          // output elements in one staging row
-  static constexpr int STG_WARP_BYTES = 32 * 128;  // one warp's 32 rows x 128 bytes
+  static constexpr int STG_TILE_BYTES = 32 * 128;  // one warp's 32 rows x 128 bytes
+  // STGN staging tiles per epilogue warp: with two, a warp fills one while the TMA store of the
+  // other is still reading shared memory
+  static constexpr int STG_WARP_BYTES = STGN * STG_TILE_BYTES;
   static constexpr int STG_BYTES = kEpilogueWarps * STG_WARP_BYTES;
   static constexpr int NBAR = 2 * SX + 2 + 4;
   static constexpr int BAR_BYTES = 512;
   static constexpr int SMEM_BYTES = NWC * WB + SX * STAGE_BYTES + STG_BYTES + BAR_BYTES + 1024;
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
-  static_assert(SMEM_BYTES > 116 * 1024, "one CTA per SM, so that the TMEM allocation never waits");
   static constexpr int TMEM_COLS = 2 * NT;
+  // CTAs that fit one SM: their TMEM allocations must fit together, so that an allocation never waits
+  static constexpr int CTAS = SMEM_BYTES <= 115712 ? 2 : 1;
+  static_assert(CTAS * TMEM_COLS <= 512, "tensor memory of the CTAs resident on one SM");
   static_assert(NT == 64 || NT == 128 || NT == 256, "TMEM allocation must be a power of two");
   static_assert(KC % UK == 0 && KC % 8 == 0, "k chunk");
   static_assert(IN_LAST || KC == NBOX, "batch-first input chunks are one 128-byte k box");
@@ -121,11 +128,11 @@ struct Cfg {
   static_assert(WRES ? NWC > 0 : NWC == 0, "resident weight chunks exist in weight-stationary mode only");
 };
 
-template <bool IN_LAST, bool OUT_LAST, int ES, int OS, int NT, int KC, bool WRES, int NWC, int SX>
-__global__ void __launch_bounds__(kThreads, 1)
+template <bool IN_LAST, bool OUT_LAST, int ES, int OS, int NT, int KC, bool WRES, int NWC, int SX, int STGN>
+__global__ void __launch_bounds__(kThreads, Cfg<IN_LAST, OUT_LAST, ES, OS, NT, KC, WRES, NWC, SX, STGN>::CTAS)
     ksmm_tc_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
                    const __grid_constant__ CUtensorMap tmY, const Params P) {
-  using C = Cfg<IN_LAST, OUT_LAST, ES, OS, NT, KC, WRES, NWC, SX>;
+  using C = Cfg<IN_LAST, OUT_LAST, ES, OS, NT, KC, WRES, NWC, SX, STGN>;
   constexpr bool BS_LAST = OUT_LAST;  // orientation of the accumulator and of the epilogue
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -161,6 +168,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     *abort_flag = 0;
     fence_mbar_init();
   }
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&tmX);
+    prefetch_tensormap(&tmW);
+    prefetch_tensormap(&tmY);
+  }
   if (warp == 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::TMEM_COLS);
     tmem_relinquish();
@@ -169,6 +181,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // everything above overlaps the tail of the previous kernel in the stream; memory comes after this
+  grid_dep_wait();
+  grid_dep_launch();
 
   // Work split: CTA c keeps one j tile (tj = c mod tiles_j) and walks a
   // contiguous range of rows, a row being one (block, batch tile) pair.  CTAs
@@ -309,8 +324,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int grp = ew >> 2;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     const bool plain = (P.alpha == 1.f) && (P.bias == nullptr) && (P.act == 0);
-    const uint32_t stg = stg0 + ew * C::STG_WARP_BYTES;
-    uint32_t ut = 0;
+    const uint32_t stg_base = stg0 + ew * C::STG_WARP_BYTES;
+    uint32_t ut = 0, sti = 0;
     KSMM_TRACE_DECL;
     const int trole = (ew == 0) ? 2 : 3;
     const bool tron = (ew == 0 || ew == 5) && lane == 0;
@@ -340,8 +355,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll 1
         for (int cbi = grp; cbi < NT / C::CB; cbi += kEpilogueWarps / 4) {
           if (cbi * C::CB >= col_limit) break;
-          if (lane == 0) bulk_wait_read<0>();  // this warp's previous store has read the tile
+          // the staging tile about to be written has been read by the store that used it last
+          if (lane == 0) bulk_wait_read<STGN - 1>();
           __syncwarp();
+          const uint32_t stg = stg_base + (STGN > 1 ? sti * C::STG_TILE_BYTES : 0u);
+          if (STGN > 1) sti = (sti + 1 == STGN) ? 0u : sti + 1;
           uint32_t r[C::CB];
 #pragma unroll
           for (int h = 0; h < C::CB / 32; ++h)
@@ -389,6 +407,34 @@ __global__ void __launch_bounds__(kThreads, 1)
             } else if (P.act == KSMM_ACT_RELU) {
 #pragma unroll
               for (int e = 0; e < C::CB; ++e) r[e] = __float_as_uint(fmaxf(__uint_as_float(r[e]), 0.f));
+            }
+          }
+          if (P.residual != nullptr && q * 32 + lane < row_limit) {
+            // this thread's CB outputs are consecutive in memory (128 bytes): eight 16-byte loads
+            const int64_t base = BS_LAST
+                ? ((static_cast<int64_t>(i) * P.b + j0 + q * 32 + lane) * d + l) * P.batch + n0 + cbi * C::CB
+                : (static_cast<int64_t>(n0) + q * 32 + lane) * (static_cast<int64_t>(P.a) * P.b) +
+                      static_cast<int64_t>(i) * P.b + j0 + cbi * C::CB;
+            const uint4* rp = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(P.residual) + base * OS);
+            constexpr int EPC = 16 / OS;  // elements per 16-byte piece
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+              if (cbi * C::CB + ch * EPC < col_limit) {
+                const uint4 v = __ldg(rp + ch);
+                const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int e = 0; e < EPC; ++e) {
+                  float rv;
+                  if constexpr (OS == 4) {
+                    rv = __uint_as_float(w4[e]);
+                  } else {
+                    const uint16_t hv = static_cast<uint16_t>((e & 1) ? (w4[e >> 1] >> 16) : (w4[e >> 1] & 0xffffu));
+                    rv = P.out_dtype == KSMM_BF16 ? __uint_as_float(static_cast<uint32_t>(hv) << 16)
+                                                  : __half2float(__ushort_as_half(hv));
+                  }
+                  r[ch * EPC + e] = __float_as_uint(__uint_as_float(r[ch * EPC + e]) + rv);
+                }
+              }
             }
           }
           const uint32_t rowaddr = stg + lane * 128;
@@ -540,7 +586,7 @@ int encode_map(CUtensorMap* tm, int dt, int rank, const void* base, const uint64
 // launch_cfg.  8-bit inputs use twice the k rows; batch-first stages always
 // hold one 128-byte k box.  Configuration 4 (N tile 64) is narrower than one
 // 128-byte fp8 box row and exists for 16-bit inputs only.
-static constexpr int kNumConfigs = 5;
+static constexpr int kNumConfigs = 8;
 
 int* status_word() {
   // one status word per device, owned by the module image
@@ -557,6 +603,11 @@ int* status_word() {
   return cached;
 }
 
+bool pdl_enabled() {
+  static const bool on = std::getenv("KSMM_NO_PDL") == nullptr;
+  return on;
+}
+
 int num_sms() {
   static std::atomic<int> sms[64];
   int dev = 0;
@@ -569,10 +620,10 @@ int num_sms() {
   return n;
 }
 
-template <bool IN_LAST, bool OUT_LAST, int ES, int OS, int NT, int KC, bool WRES, int NWC, int SX>
+template <bool IN_LAST, bool OUT_LAST, int ES, int OS, int NT, int KC, bool WRES, int NWC, int SX, int STGN = 1>
 static int launch_one(const Problem& p, cudaStream_t stream) {
-  using C = Cfg<IN_LAST, OUT_LAST, ES, OS, NT, KC, WRES, NWC, SX>;
-  auto kern = ksmm_tc_kernel<IN_LAST, OUT_LAST, ES, OS, NT, KC, WRES, NWC, SX>;
+  using C = Cfg<IN_LAST, OUT_LAST, ES, OS, NT, KC, WRES, NWC, SX, STGN>;
+  auto kern = ksmm_tc_kernel<IN_LAST, OUT_LAST, ES, OS, NT, KC, WRES, NWC, SX, STGN>;
   static std::atomic<bool> attr_set[64];  // zero-initialised; set once per device (a repeated set is harmless)
   int dev = 0;
   cudaGetDevice(&dev);
@@ -607,6 +658,7 @@ static int launch_one(const Problem& p, cudaStream_t stream) {
   P.rg_c = p.out_regroup_c;
   P.groups = static_cast<int>(G);
   P.gx = GX > 1 ? 1 : 0;
+  P.residual = p.residual;
   P.status = status_word();
   if (!P.status) return set_error(KSMM_ERR_CUDA, "cannot resolve the device status word");
   const uint32_t fmt = p.in_dtype == KSMM_BF16 ? 1u : 0u;  // f16 / e4m3 = 0, bf16 = 1
@@ -651,18 +703,19 @@ static int launch_one(const Problem& p, cudaStream_t stream) {
   if (sms <= 0) return set_error(KSMM_ERR_NO_DEVICE, "no CUDA device");
   P.tiles_jg = P.tiles_j * static_cast<int>(G);
   const int64_t rows = static_cast<int64_t>(P.tiles_n) * p.a * p.d;
+  const int slots = sms * C::CTAS;  // CTAs resident at the same time
   if (rows <= 0 || rows > 0x7fffffffLL || P.tiles_jg > sms)
     return set_error(KSMM_ERR_UNSUPPORTED,
                      "tensor-core family: %lld rows x %d j tiles exceed the work-split limits",
                      static_cast<long long>(rows), P.tiles_jg);
   P.rows = static_cast<uint32_t>(rows);
-  int64_t groups = sms / P.tiles_jg;
+  int64_t groups = slots / P.tiles_jg;
   if (groups > rows) groups = rows;
   P.row_groups = static_cast<uint32_t>(groups);
   const unsigned grid = static_cast<unsigned>(groups * P.tiles_jg);
-  kern<<<grid, kThreads, C::SMEM_BYTES, stream>>>(tmX, tmW, tmY, P);
+  cudaError_t err = launch_pdl(kern, grid, kThreads, C::SMEM_BYTES, stream, tmX, tmW, tmY, P);
   count_launch();
-  cudaError_t err = cudaGetLastError();
+  if (err == cudaSuccess) err = cudaGetLastError();
   if (err != cudaSuccess)
     return set_error(KSMM_ERR_CUDA, "tensor-core kernel launch failed: %s", cudaGetErrorString(err));
   return KSMM_OK;
@@ -672,12 +725,12 @@ static int launch_one(const Problem& p, cudaStream_t stream) {
 // the first is used when all k chunks of the weight tile fit in its NWC slots.
 //   <layout, ES, OS, N tile, bytes of k per chunk row, resident weight chunks,
 //    ring stages (weight-stationary), ring stages (streaming)>
-template <bool IN_LAST, bool OUT_LAST, int ES, int OS, int NT, int KCB, int NWC, int SX_W, int SX_S>
+template <bool IN_LAST, bool OUT_LAST, int ES, int OS, int NT, int KCB, int NWC, int SX_W, int SX_S, int STGN = 1>
 static int launch_flavour(const Problem& p, cudaStream_t stream) {
   constexpr int KC = KCB / ES;
   const int nk = (p.c + KC - 1) / KC;
-  if (nk <= NWC) return launch_one<IN_LAST, OUT_LAST, ES, OS, NT, KC, true, NWC, SX_W>(p, stream);
-  return launch_one<IN_LAST, OUT_LAST, ES, OS, NT, KC, false, 0, SX_S>(p, stream);
+  if (nk <= NWC) return launch_one<IN_LAST, OUT_LAST, ES, OS, NT, KC, true, NWC, SX_W, STGN>(p, stream);
+  return launch_one<IN_LAST, OUT_LAST, ES, OS, NT, KC, false, 0, SX_S, STGN>(p, stream);
 }
 
 template <bool BS_LAST, int ES, int OS>
@@ -693,6 +746,12 @@ static int launch_cfg(const Problem& p, int config, cudaStream_t stream) {
       case 4:
         if constexpr (ES == 2) return launch_flavour<true, true, ES, OS, 64, 128, 6, 8, 8>(p, stream);
         break;
+      case 5:  // two CTAs per SM: short rings, more independent pipelines in flight
+        return launch_flavour<true, true, ES, OS, 128, 128, 1, 3, 2>(p, stream);
+      case 6:  // two staging tiles per epilogue warp, short blocks
+        return launch_flavour<true, true, ES, OS, 256, 128, 1, 4, 3, 2>(p, stream);
+      case 7:  // two staging tiles per epilogue warp
+        return launch_flavour<true, true, ES, OS, 256, 128, 3, 3, 3, 2>(p, stream);
     }
   } else {
     switch (config) {
@@ -703,6 +762,12 @@ static int launch_cfg(const Problem& p, int config, cudaStream_t stream) {
       case 4:
         if constexpr (ES == 2) return launch_flavour<false, false, ES, OS, 64, 128, 6, 8, 8>(p, stream);
         break;
+      case 5:
+        return launch_flavour<false, false, ES, OS, 128, 128, 1, 3, 2>(p, stream);
+      case 6:
+        return launch_flavour<false, false, ES, OS, 256, 128, 1, 8, 3, 2>(p, stream);
+      case 7:
+        return launch_flavour<false, false, ES, OS, 256, 128, 3, 4, 3, 2>(p, stream);
     }
   }
   return set_error(KSMM_ERR_BAD_ARGUMENT, "tensor-core family: no configuration %d", config);
@@ -713,8 +778,8 @@ static int launch_cfg(const Problem& p, int config, cudaStream_t stream) {
 template <bool IN_LAST>
 static int launch_mixed(const Problem& p, int config, cudaStream_t stream) {
   constexpr bool OUT_LAST = !IN_LAST;
-  if (config == 2) config = 0;
-  if (config == 3) config = 1;
+  if (config == 2 || config == 6 || config == 7) config = 0;
+  if (config == 3 || config == 5) config = 1;
   switch (config) {
     case 0: return launch_flavour<IN_LAST, OUT_LAST, 2, 2, 256, 128, 3, OUT_LAST ? 4 : 6, 4>(p, stream);
     case 1: return launch_flavour<IN_LAST, OUT_LAST, 2, 2, 128, 128, 6, 6, 6>(p, stream);
@@ -788,6 +853,16 @@ bool tc_can_regroup_output(const Problem& p) {
   const int d2 = p.out_regroup_d, c2 = p.out_regroup_c;
   if ((d2 != 2 && d2 != 4) || c2 <= 0 || (c2 * d2) % 64 != 0 || c2 % 8 != 0) return false;
   return (static_cast<int64_t>(p.a) * p.b) % (static_cast<int64_t>(c2) * d2) == 0 && tc_default_config(p) >= 0;
+}
+
+// true if the kernel that tc_launch would run for `p` adds p.residual in its epilogue (the 16-bit /
+// 8-bit kernel of this file; the other kernels of the family leave it to a pass after them)
+bool tc_fuses_residual(const Problem& p) {
+  if (p.in_dtype == KSMM_F32) return false;
+  const bool out_last = p.out_bs_last < 0 ? p.bs_last != 0 : p.out_bs_last != 0;
+  if (out_last == (p.bs_last != 0) && !p.bs_last && p.d != 1) return false;
+  if (p.groups > 1 || p.out_regroup_d) return false;
+  return reinterpret_cast<uintptr_t>(p.residual) % 16 == 0;
 }
 
 int tc_default_config(const Problem& p) {

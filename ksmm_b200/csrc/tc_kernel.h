@@ -13,6 +13,8 @@ bool tc_config_supported(const Problem& p, int config, bool check_pointers);
 // heuristic default configuration, or -1 if the family cannot run `p`
 int tc_default_config(const Problem& p);
 int tc_launch(const Problem& p, int config, cudaStream_t stream);
+// true if the kernel tc_launch runs for `p` adds p.residual in its epilogue
+bool tc_fuses_residual(const Problem& p);
 // true if `p` (with out_regroup_c / out_regroup_d set) can store its output regrouped by the
 // blocks of the next factor of a chain
 bool tc_can_regroup_output(const Problem& p);

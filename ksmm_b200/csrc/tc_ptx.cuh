@@ -94,6 +94,22 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Programmatic dependent launch.  A kernel launched with the stream-serialisation attribute may
+// start while the kernel before it in the stream is still running: everything up to
+// grid_dep_wait() (barrier set-up, TMEM allocation) then overlaps that kernel's tail and the
+// launch latency; grid_dep_wait() returns once the earlier kernels have completed and their
+// writes are visible.  No global memory may be touched before it.  grid_dep_launch() lets the
+// kernel after this one do the same.  Both are no-ops for a normal launch.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// Fetches a tensor map (a kernel parameter) into the descriptor cache ahead of its first use.
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* tm) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tm)) : "memory");
+}
+
 __device__ __forceinline__ void fence_mbar_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }

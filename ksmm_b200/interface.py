@@ -130,7 +130,7 @@ class KSLinear(nn.Module):
             self._fp8_cache = [_k.quantize_e4m3(f.data) for f in self.factors]
         return self._fp8_cache
 
-    def _forward_2d(self, x):
+    def _forward_2d(self, x, residual=None):
         bias = None if self.bias is None else self.bias.reshape(-1)
         if self.is_fp8:
             y = x
@@ -144,8 +144,9 @@ class KSLinear(nn.Module):
             elif self.activation == "relu":
                 y = torch.relu(y)
             return y
-        if torch.is_grad_enabled() and (x.requires_grad or any(f.requires_grad for f in self.factors)
-                                        or (self.bias is not None and self.bias.requires_grad)):
+        if residual is None and torch.is_grad_enabled() and (
+                x.requires_grad or any(f.requires_grad for f in self.factors)
+                or (self.bias is not None and self.bias.requires_grad)):
             # differentiable path: one autograd node per factor; bias and activation are torch ops
             y = x
             for p, f in zip(self.patterns, self.factors):
@@ -162,7 +163,8 @@ class KSLinear(nn.Module):
         if self.fuse_chain or self.num_mat == 1:
             ws = self._ensure_workspace(x)
             return _k.chain_forward(x, list(self.factors), self.patterns, self.bs_last, bias=bias,
-                                    workspace=ws, activation=self.activation, out_bs_last=self.out_bs_last)
+                                    workspace=ws, activation=self.activation, out_bs_last=self.out_bs_last,
+                                    residual=residual)
         if self.out_bs_last != bool(self.bs_last):
             raise ValueError("a layer that changes the layout runs as one chain call (fuse_chain=True)")
         y = x
@@ -188,12 +190,20 @@ class KSLinear(nn.Module):
             self._workspace = ws
         return ws
 
-    def forward(self, tensor):
-        """tensor: (..., in_size) for batch-first, (in_size, ...) for batch-last."""
+    def forward(self, tensor, residual=None):
+        """tensor: (..., in_size) for batch-first, (in_size, ...) for batch-last.  ``residual`` (an
+        addition to the reference's signature; inference path only): a tensor with the shape of the
+        result that is added to it inside the last factor's kernel."""
         output = self.pre_process(tensor)
         if not self.is_fp8 and output.dtype != self.dtype:
             raise TypeError(f"input dtype {output.dtype} differs from the layer's {self.dtype}")
-        output = self._forward_2d(output)
+        res2d = None
+        if residual is not None:
+            if self.is_fp8 or not (self.fuse_chain or self.num_mat == 1):
+                raise ValueError("a residual needs the chained 16/32-bit path")
+            res2d = (residual.reshape(self.out_size, -1) if self.out_bs_last
+                     else residual.reshape(-1, self.out_size)).contiguous()
+        output = self._forward_2d(output, res2d)
         return self.post_process(tensor, output)
 
     def pre_process(self, tensor):

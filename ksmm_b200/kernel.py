@@ -74,7 +74,7 @@ def _check_inputs(input, factor, bs_last, a, b, c, d):
 
 
 def forward_ex(input, factor, bs_last, a, b, c, d, *, out_dtype=None, alpha=1.0, bias=None,
-               algo=_lib.KSMM_ALGO_AUTO, config=-1, out=None, activation=None):
+               algo=_lib.KSMM_ALGO_AUTO, config=-1, out=None, activation=None, residual=None):
     """One factor with every option of ``ksmm_cu_forward_ex``."""
     lib = _lib.load()
     bs_last = int(bool(bs_last))
@@ -91,8 +91,12 @@ def forward_ex(input, factor, bs_last, a, b, c, d, *, out_dtype=None, alpha=1.0,
     if bias is not None:
         if bias.numel() != a * b * d or bias.dtype != out_dtype or not bias.is_contiguous():
             raise ValueError("bias must hold a*b*d contiguous elements of the output dtype")
+    if residual is not None and (tuple(residual.shape) != shape or residual.dtype != out_dtype
+                                 or not residual.is_contiguous() or residual.device != input.device):
+        raise ValueError("residual must be a contiguous tensor shaped and typed like the output")
     desc = ForwardDesc(
         input=input.data_ptr(), values=factor.data_ptr(), output=out.data_ptr(),
+        residual=residual.data_ptr() if residual is not None else None,
         bias=bias.data_ptr() if bias is not None else None, batch=batch, a=a, b=b, c=c, d=d,
         in_dtype=dtype_code(input.dtype), out_dtype=dtype_code(out_dtype), bs_last=bs_last,
         algo=algo, config=config, alpha=float(alpha), activation=_lib.ACTIVATIONS[activation])
@@ -148,14 +152,15 @@ def forward(input, factor, bs_last, a, b, c, d, dtype, vsize=4):
 
 
 def chain_forward(input, factors, patterns, bs_last, bias=None, workspace=None, out=None,
-                  activation=None, out_bs_last=None):
+                  activation=None, out_bs_last=None, residual=None):
     """All factors of one KSLinear in one library call (``ksmm_cu_chain_forward_layouts``).
 
     ``factors[f]`` is the kernel-format (a*d*c, b) weight of ``patterns[f]``;
     ``patterns[0]`` is applied first.  ``bias`` (out features, output dtype)
     and ``activation`` (None, "gelu" or "relu") are fused into the last factor.
     ``out_bs_last`` (default: same as ``bs_last``) asks for the output in the other
-    layout: (out, batch) when true, (batch, out) when false.
+    layout: (out, batch) when true, (batch, out) when false.  ``residual`` (shaped like the
+    output) is added last: ``act(chain(x) + bias) + residual``.
     """
     lib = _lib.load()
     bs_last = int(bool(bs_last))
@@ -186,13 +191,20 @@ def chain_forward(input, factors, patterns, bs_last, bias=None, workspace=None, 
         workspace = torch.empty(need, dtype=torch.uint8, device=input.device)
     if bias is not None and (bias.numel() != n_out or bias.dtype != input.dtype):
         raise ValueError("bias must hold out_size elements of the input dtype")
+    if residual is not None and (tuple(residual.shape) != shape or residual.dtype != input.dtype
+                                 or not residual.is_contiguous() or residual.device != input.device):
+        raise ValueError("residual must be a contiguous tensor shaped and typed like the output")
     vals = (ctypes.c_void_p * nf)(*[w.data_ptr() for w in factors])
+    desc = _lib.ChainDesc(
+        input=input.data_ptr(), values=vals, output=out.data_ptr(),
+        bias=bias.data_ptr() if bias is not None else None,
+        residual=residual.data_ptr() if residual is not None else None,
+        workspace=workspace.data_ptr() if workspace is not None else None,
+        workspace_bytes=workspace.numel() * workspace.element_size() if workspace is not None else 0,
+        batch=batch, nfactors=nf, patterns=pat, dtype=code, bs_last=bs_last, out_layout=2 if out_last else 1,
+        activation=_lib.ACTIVATIONS[activation])
     with torch.cuda.device(input.device):
-        _lib.check(lib.ksmm_cu_chain_forward_layouts(
-            input.data_ptr(), vals, out.data_ptr(), bias.data_ptr() if bias is not None else None,
-            workspace.data_ptr() if workspace is not None else None,
-            workspace.numel() * workspace.element_size() if workspace is not None else 0,
-            batch, nf, pat, code, bs_last, out_last, _lib.ACTIVATIONS[activation], _stream_ptr(input.device)))
+        _lib.check(lib.ksmm_cu_chain_forward_desc(ctypes.byref(desc), _stream_ptr(input.device)))
     return out
 
 

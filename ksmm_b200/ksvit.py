@@ -59,11 +59,17 @@ class KSFeedForward(nn.Module):
             self.fc2 = KSLinear(FC2_PATTERNS, bias=True, algo="kernel", dtype=dtype, bs_last=mid_last,
                                 device=device, out_bs_last=False)
 
-    def forward(self, x):
+    def forward(self, x, add_residual=False):
+        """With add_residual the block's `x + ff(x)` is formed inside fc2's last kernel."""
         h = self.fc1(self.norm(x))
         if not self.fuse_gelu:
             h = F.gelu(h)
-        y = self.fc2(h)
+        if add_residual and not self.dense:
+            y = self.fc2(h, residual=x)
+        else:
+            y = self.fc2(h)
+            if add_residual:
+                y = y.view(x.shape) + x
         return y.view(x.shape) if self.layout_plan else y
 
 
@@ -108,5 +114,5 @@ class KSViTB(nn.Module):
         x = self.embed(x) + self.pos
         for attn, ff in self.layers:
             x = attn(x) + x
-            x = ff(x) + x
+            x = ff(x, add_residual=True)
         return self.head(self.norm(x).mean(dim=1))

@@ -722,6 +722,7 @@ def _dense_twin(model):
                 setattr(m, name, lin)
             m.fuse_gelu = False
             m.layout_plan = False
+            m.dense = True
     return twin.float()
 
 
@@ -1135,4 +1136,47 @@ def test_kslinear_out_layout_option():
     yr = hr @ d2.t() + fc2.bias.float().reshape(-1)
     rel = (torch.linalg.norm(y.float() - yr) / torch.linalg.norm(yr)).item()
     assert rel < 1e-2, rel
+    kb.check_device()
+
+
+def test_residual_in_the_epilogue_and_as_a_pass():
+    """out = act(alpha K x + bias) + residual: in the epilogue of the 16-bit tensor kernel (both
+    layouts, layout-changing factors included), as a pass after every other kernel."""
+    cases = [((2, 96, 48, 1), torch.float16, True, _lib.KSMM_ALGO_TC), ((2, 96, 48, 1), torch.float16, False, _lib.KSMM_ALGO_TC),
+             ((1, 200, 72, 3), torch.bfloat16, True, _lib.KSMM_ALGO_TC), ((4, 192, 192, 1), torch.bfloat16, False, _lib.KSMM_ALGO_TC),
+             ((1, 128, 32, 4), torch.float16, False, _lib.KSMM_ALGO_TC),      # interleaved batch-first kernel: pass
+             ((2, 96, 48, 1), torch.float32, True, _lib.KSMM_ALGO_TC), ((2, 72, 48, 2), torch.float32, False, _lib.KSMM_ALGO_SIMT),
+             ((1, 64, 64, 16), torch.float16, False, _lib.KSMM_ALGO_AUTO)]    # layout conversion: pass
+    for ci, (pattern, dtype, bs_last, algo) in enumerate(cases):
+        for batch in (96, 520):
+            x, w = _inputs(pattern, batch, dtype, bs_last, seed=1600 + ci)
+            rng = np.random.RandomState(1610 + ci)
+            a, b, c, d = pattern
+            oshape = (a * b * d, batch) if bs_last else (batch, a * b * d)
+            bias = torch.from_numpy(rng.standard_normal(a * b * d).astype(np.float32)).to(dtype)
+            res = torch.from_numpy(rng.standard_normal(oshape).astype(np.float32)).to(dtype)
+            y = _run(x, w, pattern, bs_last, algo=algo, bias=bias.to(DEV), alpha=0.5, activation="relu",
+                     residual=res.to(DEV))
+            bf = bias.float().numpy()
+            ref = np.maximum(0.5 * _oracle(x, w, bs_last) + (bf[:, None] if bs_last else bf[None, :]), 0.0)
+            ref = ref + res.float().numpy()
+            tol = 1e-5 if dtype == torch.float32 else 1e-2
+            assert ko.rel_fro_error(y, ref) < tol, (pattern, dtype, bs_last, batch)
+    # chains: fc2 of the KS-ViT-B MLP reads batch-last activations and adds the batch-first residual
+    pats = [(1, 192, 768, 4), (4, 192, 192, 1)]
+    rng = np.random.RandomState(1650)
+    ws = make_weights(pats, rng)
+    wt = [torch.from_numpy(v).half() for v in ws]
+    wk = [kb.generate_factor(*p, "kernel", v, torch.float16, DEV) for p, v in zip(pats, wt)]
+    for in_last, out_last in ((True, False), (False, False), (True, True), (False, True)):
+        batch = 520
+        x = torch.from_numpy(rng.standard_normal((3072, batch) if in_last else (batch, 3072)).astype(np.float32)).half()
+        res = torch.from_numpy(rng.standard_normal((768, batch) if out_last else (batch, 768)).astype(np.float32)).half()
+        before = kb.launch_count()
+        y = kb.chain_forward(x.to(DEV), wk, pats, in_last, out_bs_last=out_last, residual=res.to(DEV))
+        if in_last and not out_last:
+            assert kb.launch_count() - before == 2          # nothing but the two factors
+        ref = ko.chain_apply(x.float().numpy(), [v.float().numpy() for v in wt], in_last)
+        ref = (ref.T if in_last != out_last else ref) + res.float().numpy()
+        assert ko.rel_fro_error(y.float().cpu().numpy(), ref) < 1e-2, (in_last, out_last)
     kb.check_device()
