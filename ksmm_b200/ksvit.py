@@ -90,7 +90,7 @@ class Attention(nn.Module):
 
 class KSViTB(nn.Module):
     def __init__(self, dtype=torch.float16, device="cuda", depth=12, dim=768, num_classes=1000,
-                 dense_mlp=False, fuse_gelu=True, layout_plan=True):
+                 dense_mlp=False, fuse_gelu=True, layout_plan=True, fuse_residual=False):
         super().__init__()
         self.patch = 16
         patch_dim = 3 * 16 * 16
@@ -101,6 +101,7 @@ class KSViTB(nn.Module):
              for _ in range(depth)])
         self.norm = nn.LayerNorm(dim)
         self.head = nn.Linear(dim, num_classes)
+        self.fuse_residual = fuse_residual
         # stock layers to the requested dtype / device; KSLinear parameters were created there
         for m in self.modules():
             if isinstance(m, (nn.Linear, nn.LayerNorm)):
@@ -114,5 +115,5 @@ class KSViTB(nn.Module):
         x = self.embed(x) + self.pos
         for attn, ff in self.layers:
             x = attn(x) + x
-            x = ff(x, add_residual=True)
+            x = ff(x, add_residual=True) if self.fuse_residual else ff(x) + x
         return self.head(self.norm(x).mean(dim=1))
