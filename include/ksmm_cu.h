@@ -382,6 +382,9 @@ KSMM_API int ksmm_cu_get_choice(int64_t batch, int a, int b, int c, int d, int i
                        int bs_last, int* algo, int* config);
 KSMM_API int ksmm_cu_default_choice(const ksmm_forward_desc_t* desc, int* algo, int* config,
                            int* via_transpose);
+/* Removes one cached choice (the heuristic decides again), or the whole cache when batch < 0. */
+KSMM_API int ksmm_cu_clear_choice(int64_t batch, int a, int b, int c, int d, int in_dtype, int out_dtype,
+                         int bs_last);
 
 /*
  * Synchronises `stream` and returns KSMM_ERR_DEVICE_TIMEOUT if a kernel

@@ -10,6 +10,11 @@ from .interface import (KSLinear, KSLinearGroup, from_kernel_format_to_abcd,  # 
 from .kernel import (FactorFunction, Kernel, alloc_count, backward_input, backward_weights, chain_forward, check_device, default_choice, forward,  # noqa: F401
                      forward_ex, forward_fp8, grouped_chain_forward, launch_count, quantize_e4m3)
 
+# the tuned table shipped with the package (choices that beat the heuristic on a B200); needs no device
+from . import tuner as _tuner  # noqa: E402
+
+_tuner.load_default()
+
 __all__ = [
     "KSLinear", "KSLinearGroup", "grouped_chain_forward", "alloc_count", "Kernel", "FactorFunction",
     "backward_input", "backward_weights", "forward", "forward_ex", "forward_fp8", "chain_forward",

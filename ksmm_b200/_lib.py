@@ -36,7 +36,7 @@ EXPORTS = (
     "ksmm_cu_launch_count", "ksmm_cu_measure_ffma_peak",
     "ksmm_cu_layout_scratch_bytes", "ksmm_cu_release_scratch", "ksmm_cu_chain_workspace_bytes_ex",
     "ksmm_cu_alloc_count", "ksmm_cu_debug_wait_probe",
-    "ksmm_cu_chain_forward_host_async", "ksmm_cu_host_wait",
+    "ksmm_cu_chain_forward_host_async", "ksmm_cu_host_wait", "ksmm_cu_clear_choice",
     "ksmm_cu_grouped_forward", "ksmm_cu_grouped_chain_forward",
     "ksmm_cu_chain_workspace_bytes_layouts", "ksmm_cu_chain_forward_layouts", "ksmm_cu_chain_forward_desc",
     "ksmm_cu_backward_input_workspace_bytes", "ksmm_cu_backward_input",
@@ -149,6 +149,8 @@ def load():
     lib.ksmm_cu_get_choice.restype = i32
     lib.ksmm_cu_get_choice.argtypes = [i64, i32, i32, i32, i32, i32, i32, i32,
                                        ctypes.POINTER(i32), ctypes.POINTER(i32)]
+    lib.ksmm_cu_clear_choice.restype = i32
+    lib.ksmm_cu_clear_choice.argtypes = [i64, i32, i32, i32, i32, i32, i32, i32]
     lib.ksmm_cu_default_choice.restype = i32
     lib.ksmm_cu_default_choice.argtypes = [ctypes.POINTER(ForwardDesc), ctypes.POINTER(i32),
                                            ctypes.POINTER(i32), ctypes.POINTER(i32)]

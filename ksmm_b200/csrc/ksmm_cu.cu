@@ -1403,6 +1403,16 @@ int ksmm_cu_set_choice(int64_t batch, int a, int b, int c, int d, int in_dtype, 
   return KSMM_OK;
 }
 
+int ksmm_cu_clear_choice(int64_t batch, int a, int b, int c, int d, int in_dtype, int out_dtype, int bs_last) {
+  std::lock_guard<std::mutex> g(g_choice_mu);
+  if (batch < 0) {
+    g_choices.clear();  // the whole cache
+    return KSMM_OK;
+  }
+  g_choices.erase(ChoiceKey(batch, a, b, c, d, in_dtype, out_dtype, bs_last));
+  return KSMM_OK;
+}
+
 int ksmm_cu_get_choice(int64_t batch, int a, int b, int c, int d, int in_dtype, int out_dtype,
                        int bs_last, int* algo, int* config) {
   std::lock_guard<std::mutex> g(g_choice_mu);

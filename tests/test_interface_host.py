@@ -102,7 +102,8 @@ def test_tuner_table_round_trip(tmp_path):
     best = tmp_path / "kernel.best"
     tuner.export_best_rows(str(best))
     rows = best.read_text().splitlines()
-    assert rows[0] == tuner.BEST_HEADER and rows[1].split()[:5] == ["25088", "1", "768", "192", "4"]
+    assert rows[0] == tuner.BEST_HEADER
+    assert any(r.split()[:5] == ["25088", "1", "768", "192", "4"] for r in rows[1:])
     assert len(tuner.read_best_rows(str(best))) == len(rows) - 1      # its own export parses back
     with pytest.raises(ValueError):
         bad = tmp_path / "bad.json"
