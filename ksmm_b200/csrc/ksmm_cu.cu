@@ -605,6 +605,8 @@ static double step_cost(const int32_t* q, int64_t batch, int dtype, int in_last,
   const bool half = dtype == KSMM_F16 || dtype == KSMM_BF16;
   if (half && (q[3] == 2 || q[3] == 4) && q[1] % 8 == 0 && (static_cast<int64_t>(q[2]) * q[3]) % 8 == 0)
     return 1.9 * bytes;   // in-kernel split of the interleaved blocks
+  if (half && q[3] % 8 == 0 && q[1] % 8 == 0 && q[1] >= 32 && q[1] <= 64 && q[2] >= 16)
+    return 2.3 * bytes;   // groups of eight blocks, 16-byte pieces
   return 2.6 * bytes;     // layout conversion around the batch-last kernel, or the strided FFMA kernel
 }
 

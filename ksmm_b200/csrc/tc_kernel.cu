@@ -817,9 +817,11 @@ bool tc_config_supported(const Problem& p, int config, bool check_pointers) {
     return true;
   }
   if (p.in_dtype == KSMM_F32) return config >= 0 && config <= 3 && tc_f32x3_supported(p, check_pointers);
-  if (!p.bs_last && p.d != 1)
+  if (!p.bs_last && p.d != 1) {
+    if (p.d % 8 == 0) return config == 0 && tc_bsfirst_g_supported(p, check_pointers);
     return config == 0 ? tc_bsfirst_d_supported(p, check_pointers)
                        : (config == 1 && tc_bsfirst_dp_supported(p, check_pointers));
+  }
   if (config == 4 && p.in_dtype == KSMM_F8E4M3) return false;
   const int es = dtype_size(p.in_dtype), os = dtype_size(p.out_dtype);
   if (p.in_dtype == KSMM_F16 || p.in_dtype == KSMM_BF16) {
@@ -897,7 +899,10 @@ int tc_launch(const Problem& p, int config, cudaStream_t stream) {
   const bool out_last = p.out_bs_last < 0 ? last : p.out_bs_last != 0;
   if (out_last != last) return last ? tc::launch_mixed<true>(p, config, stream) : tc::launch_mixed<false>(p, config, stream);
   if (p.in_dtype == KSMM_F32) return tc_f32x3_launch(p, config, stream);
-  if (!last && p.d != 1) return config == 1 ? tc_bsfirst_dp_launch(p, stream) : tc_bsfirst_d_launch(p, stream);
+  if (!last && p.d != 1) {
+    if (p.d % 8 == 0) return tc_bsfirst_g_launch(p, stream);
+    return config == 1 ? tc_bsfirst_dp_launch(p, stream) : tc_bsfirst_d_launch(p, stream);
+  }
   if (p.out_regroup_d > 0 && !tc_can_regroup_output(p))
     return set_error(KSMM_ERR_UNSUPPORTED, "this factor cannot store a regrouped output");
   if (p.in_dtype == KSMM_F8E4M3) {

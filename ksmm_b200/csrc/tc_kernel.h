@@ -29,6 +29,10 @@ int tc_wait_probe(long long limit_cycles, int code, cudaStream_t stream);
 bool tc_bsfirst_d_supported(const Problem& p, bool check_pointers);
 int tc_bsfirst_d_launch(const Problem& p, cudaStream_t stream);
 
+// batch-first factors with d a multiple of 8 (tc_bsfirst_g.cu): groups of eight blocks per CTA
+bool tc_bsfirst_g_supported(const Problem& p, bool check_pointers);
+int tc_bsfirst_g_launch(const Problem& p, cudaStream_t stream);
+
 // batch-first factors with d = 2 or 4 through a regrouping pass and a kernel without the
 // transposer stage (tc_bsfirst_dp.cu); configuration 1 of such problems
 bool tc_bsfirst_dp_supported(const Problem& p, bool check_pointers);

@@ -120,13 +120,16 @@ def test_choice_cache_round_trip():
 
 def test_default_choice_reports_family_and_conversion_path():
     """What the automatic dispatch would run (no launch is made): fp32 and fp16 benchmark factors go
-    to the tensor-core family; a batch-first d = 16 factor goes through the layout conversion; a
-    block too small for the tensor cores stays on the FFMA family."""
+    to the tensor-core family; 16-bit batch-first factors have direct kernels for d = 2, 4 and
+    multiples of 8, other d and fp32 with d > 1 go through the layout conversion; a block too
+    small for the tensor cores stays on the FFMA family."""
     import torch
     import ksmm_b200 as kb
     assert kb.default_choice((1, 768, 192, 4), 4096, torch.float32, True)[::2] == ("tensor", False)
     assert kb.default_choice((1, 768, 192, 4), 4096, torch.float16, False)[::2] == ("tensor", False)
-    assert kb.default_choice((1, 64, 64, 16), 4096, torch.float16, False)[::2] == ("tensor", True)
+    assert kb.default_choice((1, 64, 64, 16), 4096, torch.float16, False)[::2] == ("tensor", False)
+    assert kb.default_choice((1, 64, 64, 12), 4096, torch.float16, False)[::2] == ("tensor", True)
+    assert kb.default_choice((1, 64, 64, 16), 4096, torch.float32, False)[::2] == ("tensor", True)
     assert kb.default_choice((4, 64, 64, 4), 4096, torch.float32, False)[::2] == ("ffma", False)
     assert kb.default_choice((1, 8, 8, 1), 4096, torch.float32, True)[::2] == ("ffma", False)
     assert kb.default_choice((1, 64, 2048, 1), 4096, torch.float32, True)[0] == "ffma"  # c > 1024

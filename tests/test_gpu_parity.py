@@ -222,10 +222,10 @@ def test_tc_family_batch_first_interleaved_blocks(dtype, config):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
 def test_batch_first_layout_conversion_path(dtype):
-    """Batch-first factors with a d that no direct kernel covers (here 16, 8, 3 x ...) run as
+    """Batch-first factors with a d that no direct kernel covers (12, 6: neither 2, 4 nor a multiple of 8) run as
     transpose -> batch-last kernel -> transpose, with bias and scale in the kernel's epilogue."""
     rng = np.random.RandomState(3)
-    for pi, pattern in enumerate([(1, 64, 64, 16), (2, 128, 32, 8), (1, 72, 48, 6)]):
+    for pi, pattern in enumerate([(1, 64, 64, 12), (2, 128, 32, 6), (1, 72, 48, 6)]):
         for batch in (40, 520):
             x, w = _inputs(pattern, batch, dtype, False, seed=500 + pi)
             a, b, c, d = pattern
@@ -830,7 +830,7 @@ def test_layout_scratch_from_the_caller_and_per_stream():
     descriptor the library allocates nothing; without it, calls on two streams get a buffer each
     and may overlap."""
     lib = _lib.load()
-    pattern, batch, dtype = (1, 64, 64, 16), 1000, torch.float16
+    pattern, batch, dtype = (1, 64, 64, 12), 1000, torch.float16
     a, b, c, d = pattern
     x, w = _inputs(pattern, batch, dtype, False, seed=35)
     ref = _oracle(x, w, False)
@@ -1179,4 +1179,32 @@ def test_residual_in_the_epilogue_and_as_a_pass():
         ref = ko.chain_apply(x.float().numpy(), [v.float().numpy() for v in wt], in_last)
         ref = (ref.T if in_last != out_last else ref) + res.float().numpy()
         assert ko.rel_fro_error(y.float().cpu().numpy(), ref) < 1e-2, (in_last, out_last)
+    kb.check_device()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_tc_family_batch_first_groups_of_eight_blocks(dtype):
+    """Batch-first with d a multiple of 8 and b <= 64 (tc_bsfirst_g.cu): eight blocks per CTA, 16-byte
+    pieces of l through TMA, 8 x 8 de-interleave in the transposer warps, interleaving epilogue.
+    One launch, every shape regime: several l groups, several block rows, ragged batch, b and c
+    that do not fill a tile, bias / scale / activation."""
+    pats = [(1, 64, 64, 16), (2, 64, 32, 8), (1, 64, 64, 8), (3, 48, 80, 24), (1, 56, 72, 32), (4, 64, 64, 64),
+            (1, 32, 40, 16), (2, 32, 16, 128), (1, 48, 192, 8),
+            (1, 136, 72, 32), (1, 768, 192, 8)]   # wider than one j tile: the default path converts the layout
+    rng = np.random.RandomState(1700)
+    for pi, pattern in enumerate(pats):
+        a, b, c, d = pattern
+        for batch in (8, 136, 520):
+            x, w = _inputs(pattern, batch, dtype, False, seed=1700 + pi)
+            before = kb.launch_count()
+            y = _run(x, w, pattern, False)
+            assert kb.launch_count() - before == (1 if b <= 64 else 3), pattern
+            assert not np.isnan(y).any(), (pattern, batch)
+            err = ko.rel_fro_error(y, _oracle(x, w, False))
+            assert err < TOL[dtype], (pattern, batch, err)
+        bias = torch.from_numpy(rng.standard_normal(a * b * d).astype(np.float32)).to(dtype)
+        x, w = _inputs(pattern, 200, dtype, False, seed=1750 + pi)
+        y = _run(x, w, pattern, False, bias=bias.to(DEV), alpha=0.5, activation="gelu")
+        ref = _act_ref(0.5 * _oracle(x, w, False) + bias.float().numpy()[None, :], "gelu")
+        assert ko.rel_fro_error(y, ref) < TOL[dtype], pattern
     kb.check_device()
