@@ -240,6 +240,43 @@ def workload_config():
 # ---------------------------------------------------------------------------
 # this library
 # ---------------------------------------------------------------------------
+def run_profile_case(name, local_rank):
+    """A few launches of one workload that `--only` cannot name (chains, backward), for a profiler
+    capture: no timing, nothing printed but the launch count."""
+    import ksmm_b200 as kb
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    gen = torch.Generator(device=dev).manual_seed(3)
+    before = kb.launch_count()
+    with torch.no_grad():
+        if name == "mlp_pair":
+            p1, p2 = [(4, 192, 192, 1), (1, 768, 192, 4)], [(1, 192, 768, 4), (4, 192, 192, 1)]
+            fc1 = kb.KSLinear(p1, bias=True, dtype=torch.float16, bs_last=False, device=dev, out_bs_last=True,
+                              activation="gelu")
+            fc2 = kb.KSLinear(p2, bias=True, dtype=torch.float16, bs_last=True, device=dev, out_bs_last=False)
+            x = torch.randn((BATCH, 768), device=dev, dtype=torch.float16, generator=gen)
+            for _ in range(3):
+                y = fc2(fc1(x))
+        elif name == "wgrad":
+            a, b, c, d = 1, 768, 192, 4
+            x = torch.randn((a * c * d, BATCH), device=dev, dtype=torch.float16, generator=gen)
+            g = torch.randn((a * b * d, BATCH), device=dev, dtype=torch.float16, generator=gen)
+            for _ in range(3):
+                y = kb.backward_weights(x, g, True, a, b, c, d)
+        elif name == "qkv":
+            layers = [kb.KSLinear([(1, 768, 768, 1)], bias=False, dtype=torch.float16, bs_last=False, device=dev)
+                      for _ in range(3)]
+            group = kb.KSLinearGroup(layers)
+            x = torch.randn((BATCH, 768), device=dev, dtype=torch.float16, generator=gen)
+            for _ in range(3):
+                y = group(x)
+        else:
+            raise SystemExit(f"unknown --profile-case {name}")
+    torch.cuda.synchronize()
+    kb.check_device()
+    print(json.dumps({"profile_case": name, "launches": kb.launch_count() - before}), flush=True)
+
+
 def run_ours(args, rank, world, local_rank):
     import ksmm_b200 as kb
     from ksmm_b200 import _lib
@@ -749,6 +786,8 @@ def main():
                     help="skip re-timing the fp32 cases on the FFMA family (the fp32_ffma_only line)")
     ap.add_argument("--sweep-configs", action="store_true",
                     help="also time every tile configuration of every case (printed to stderr)")
+    ap.add_argument("--profile-case", default=None, choices=["mlp_pair", "wgrad", "qkv"],
+                    help="run a few launches of a chain / backward / grouped workload and exit (profiler captures)")
     ap.add_argument("--only", default=None,
                     help='restrict the sweep: "dtype:layout:a,b,c,d", e.g. "fp16:bs_last:1,768,192,4"')
     args = ap.parse_args()
@@ -757,6 +796,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.profile_case:
+        run_profile_case(args.profile_case, local_rank)
         return
     if world > 1:
         torch.cuda.set_device(local_rank)
