@@ -595,20 +595,31 @@ struct ChainPlan {
 };
 
 static bool can_switch_layout(const int32_t* q, int64_t batch, int dtype) {
-  return (dtype == KSMM_F16 || dtype == KSMM_BF16) && q[3] == 1 && q[1] % 8 == 0 && q[2] % 8 == 0 &&
-         batch % 8 == 0 && q[1] >= 32 && q[2] >= 16;
+  if (q[3] != 1 || q[1] < 32 || q[2] < 16) return false;
+  if (dtype == KSMM_F32)  // the fp32 tensor kernel: 32-column atoms, c <= 1024
+    return q[1] % 32 == 0 && q[2] % 4 == 0 && q[2] <= 1024 && batch % 32 == 0;
+  return (dtype == KSMM_F16 || dtype == KSMM_BF16) && q[1] % 8 == 0 && q[2] % 8 == 0 && batch % 8 == 0;
 }
 
 static double step_cost(const int32_t* q, int64_t batch, int dtype, int in_last, int out_last) {
   const double bytes = static_cast<double>(dtype_size(dtype)) * q[0] * q[3] * (static_cast<double>(q[1]) + q[2]) * batch;
+  if (dtype == KSMM_F32) {
+    // The fp32 tensor kernel is compute-bound from blocks of about 64 x 64 on: its time is the larger
+    // of the bytes and the flops at about 35 flop per byte of bandwidth.  A batch-first factor with
+    // d > 1 pays a transpose on either side of it.
+    const double flops = 2.0 * q[0] * q[3] * static_cast<double>(q[1]) * q[2] * batch;
+    const double kernel = bytes > flops / 35.0 ? bytes : flops / 35.0;
+    if (in_last != out_last) return can_switch_layout(q, batch, dtype) ? 1.05 * kernel : -1.0;
+    if (in_last || q[3] == 1) return kernel;
+    return kernel + 1.5 * bytes;
+  }
   if (in_last != out_last) return can_switch_layout(q, batch, dtype) ? 1.05 * bytes : -1.0;
   if (in_last || q[3] == 1) return bytes;
-  const bool half = dtype == KSMM_F16 || dtype == KSMM_BF16;
-  if (half && (q[3] == 2 || q[3] == 4) && q[1] % 8 == 0 && (static_cast<int64_t>(q[2]) * q[3]) % 8 == 0)
+  if ((q[3] == 2 || q[3] == 4) && q[1] % 8 == 0 && (static_cast<int64_t>(q[2]) * q[3]) % 8 == 0)
     return 1.9 * bytes;   // in-kernel split of the interleaved blocks
-  if (half && q[3] % 8 == 0 && q[1] % 8 == 0 && q[1] >= 32 && q[1] <= 64 && q[2] >= 16)
+  if (q[3] % 8 == 0 && q[1] % 8 == 0 && q[1] >= 32 && q[1] <= 64 && q[2] >= 16)
     return 2.3 * bytes;   // groups of eight blocks, 16-byte pieces
-  return 2.6 * bytes;     // layout conversion around the batch-last kernel, or the strided FFMA kernel
+  return 2.6 * bytes;     // layout conversion around the batch-last kernel
 }
 
 static void plan_chain(int nfactors, const int32_t* patterns, int64_t batch, int dtype, int in_last,
@@ -617,8 +628,8 @@ static void plan_chain(int nfactors, const int32_t* patterns, int64_t batch, int
   for (int f = 0; f < nfactors && f < ChainPlan::kMax; ++f) plan->in_last[f] = plan->out_last[f] = in_last;
   plan->pre_transpose = false;
   plan->post_transpose = in_last != out_last;
-  const bool half = dtype == KSMM_F16 || dtype == KSMM_BF16;
-  if (!half || !allow_switch || nfactors > 8 || batch <= 0) return;
+  const bool planned = dtype == KSMM_F16 || dtype == KSMM_BF16 || dtype == KSMM_F32;
+  if (!planned || !allow_switch || nfactors > 8 || batch <= 0) return;
   const double es = dtype_size(dtype);
   const int32_t* p0 = patterns;
   const int32_t* pl = patterns + 4 * (nfactors - 1);
@@ -846,10 +857,16 @@ size_t ksmm_cu_chain_workspace_bytes_layouts(int nfactors, const int32_t* patter
   const void* dummy = nullptr;
   if (check_chain(nfactors, patterns, &dummy, dtype, 0) != KSMM_OK) return 0;
   const size_t inter = chain_intermediate_bytes(nfactors, patterns, batch, dtype);
+  // the larger of the two plans: with layout-changing factors (every pointer 16-byte aligned) and
+  // without them, so that the size holds whatever the pointers of the call turn out to be
   size_t scratch = 0;
-  if (chain_walk(false, nullptr, nullptr, nullptr, nullptr, nullptr, inter, nullptr, 0, 0, batch, nfactors,
-                 patterns, dtype, bs_last ? 1 : 0, out_bs_last ? 1 : 0, 0, nullptr, &scratch, 1) != KSMM_OK)
-    return 0;
+  for (int allow = 0; allow < 2; ++allow) {
+    size_t need = 0;
+    if (chain_walk(false, nullptr, nullptr, nullptr, nullptr, nullptr, inter, nullptr, 0, 0, batch, nfactors,
+                   patterns, dtype, bs_last ? 1 : 0, out_bs_last ? 1 : 0, 0, nullptr, &need, allow) != KSMM_OK)
+      return 0;
+    if (need > scratch) scratch = need;
+  }
   return inter + scratch;
 }
 

@@ -126,13 +126,16 @@ __device__ __forceinline__ uint32_t lo_part(uint32_t v) {
 // memory for all batch tiles of a block, and a stage is the raw input tile alone.
 constexpr int kMaxResident = 6;  // chunks of 32 k
 
-template <bool BS_LAST, int NJ_, int ST_, bool TS_, bool DIRECT_, bool WR_>
+// IN_LAST / BS_LAST: layout of the input / of the output.  The accumulator's rows are batch entries
+// in every form, so the input side (tensor map, producer, splitter, operand descriptors) and the
+// output side (epilogue, stores, bias index) combine freely; the two mixed forms need d = 1.
+template <bool IN_LAST, bool BS_LAST, int NJ_, int ST_, bool TS_, bool DIRECT_, bool WR_>
 struct CfgF {
   static constexpr int NJ = NJ_;                    // j columns per accumulator (64, 96 or 128)
   static constexpr int ST = ST_;
   static constexpr bool TS = TS_;
   static constexpr bool WR = WR_;
-  static_assert(!WR || (TS && BS_LAST && DIRECT_),
+  static_assert(!WR || (TS && BS_LAST && IN_LAST && DIRECT_),
                 "resident weights come with the tensor-memory input operand and direct stores");
   static constexpr int XT_BYTES = kKC * 128 * 4;    // 32 k x 128 batch entries (either order)
   static constexpr int WT_BYTES = kKC * NJ * 4;     // 32 k x NJ columns
@@ -164,12 +167,12 @@ struct CfgF {
   static_assert(8 * NBAR + 16 <= BAR_BYTES, "barrier area");
 };
 
-template <bool BS_LAST, int NJ_, int ST_, bool TS_, bool DIRECT_, bool WR_>
+template <bool IN_LAST, bool BS_LAST, int NJ_, int ST_, bool TS_, bool DIRECT_, bool WR_>
 __global__ void __launch_bounds__(kThreadsF, 1)
     ksmm_tc_f32x3_kernel(const __grid_constant__ CUtensorMap tmX,
                          const __grid_constant__ CUtensorMap tmW,
                          const __grid_constant__ CUtensorMap tmY, const ParamsF P) {
-  using C = CfgF<BS_LAST, NJ_, ST_, TS_, DIRECT_, WR_>;
+  using C = CfgF<IN_LAST, BS_LAST, NJ_, ST_, TS_, DIRECT_, WR_>;
   constexpr int ST = C::ST;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -262,7 +265,7 @@ __global__ void __launch_bounds__(kThreadsF, 1)
           KSMM_TRACE(0, 2);
           const uint32_t sb = stage0 + si * C::STAGE_BYTES;
           mbar_expect_tx(full_bar(si), C::XT_BYTES + (C::WR ? 0 : C::WT_BYTES));
-          if constexpr (BS_LAST) {
+          if constexpr (IN_LAST) {
             // (n % 32, k, n / 32, l, i): four atoms of 32 batch entries x 32 k rows
             tma_load_5d(sb, &tmX, full_bar(si), 0, qc * kKC, n0 / 32, blk % P.d, blk / P.d);
           } else {
@@ -321,7 +324,7 @@ __global__ void __launch_bounds__(kThreadsF, 1)
               continue;
             }
             uint64_t xhi, xlo;
-            if constexpr (BS_LAST) {
+            if constexpr (IN_LAST) {
               // MN-major, 32-byte atoms: 4 KB between the atoms of 32 batch entries, 512 bytes
               // between groups of 4 k rows; a k step of 8 is two groups
               xhi = make_desc(xb + ks * 1024, 4096, 512, 1);
@@ -384,7 +387,7 @@ __global__ void __launch_bounds__(kThreadsF, 1)
             if (++s2 == ST) { s2 = 0; ph2 ^= 1u; }
           }
           uint32_t v[kKC];
-          if constexpr (BS_LAST) {
+          if constexpr (IN_LAST) {
             // atom tr / 32 (32 batch entries x 32 k rows of 128 bytes), 32-byte piece p at p ^ (k % 4)
             const uint32_t ab0 = hb + (tr >> 5) * 4096 + (lane & 7) * 4;
 #pragma unroll
@@ -615,10 +618,10 @@ __global__ void __launch_bounds__(kThreadsF, 1)
   }
 }
 
-template <bool BS_LAST, int NJ_, int ST_, bool TS_, bool DIRECT_ = false, bool WR_ = false>
+template <bool IN_LAST, bool BS_LAST, int NJ_, int ST_, bool TS_, bool DIRECT_ = false, bool WR_ = false>
 static int launch_f(const Problem& p, cudaStream_t stream) {
-  using C = CfgF<BS_LAST, NJ_, ST_, TS_, DIRECT_, WR_>;
-  auto kern = ksmm_tc_f32x3_kernel<BS_LAST, NJ_, ST_, TS_, DIRECT_, WR_>;
+  using C = CfgF<IN_LAST, BS_LAST, NJ_, ST_, TS_, DIRECT_, WR_>;
+  auto kern = ksmm_tc_f32x3_kernel<IN_LAST, BS_LAST, NJ_, ST_, TS_, DIRECT_, WR_>;
   static std::atomic<bool> attr_set[64];  // zero-initialised; set once per device (a repeated set is harmless)
   int dev = 0;
   cudaGetDevice(&dev);
@@ -633,7 +636,7 @@ static int launch_f(const Problem& p, cudaStream_t stream) {
   const uint64_t a = p.a, b = p.b, c = p.c, d = p.d, B = p.batch;
   CUtensorMap tmX, tmW, tmY;
   int st;
-  if (BS_LAST) {
+  if (IN_LAST) {
     // input (a*c*d, batch), row (i*c + k)*d + l, seen as (n % 32, k, n / 32, l, i): one box is the
     // four atoms (32 batch entries x 32 k rows) of an MN-major operand tile
     const uint64_t dims[5] = {32, c, B / 32, d, a};
@@ -683,7 +686,7 @@ static int launch_f(const Problem& p, cudaStream_t stream) {
   if (!P.status) return set_error(KSMM_ERR_CUDA, "cannot resolve the device status word");
   // fp32 accumulate, tf32 operands, weights MN-major, batch-last input MN-major when it is read
   // from shared memory (an operand in tensor memory is K-major), M = 128
-  const uint32_t common = (1u << 4) | (2u << 7) | (2u << 10) | ((BS_LAST && !C::TS) ? (1u << 15) : 0u) | (1u << 16) |
+  const uint32_t common = (1u << 4) | (2u << 7) | (2u << 10) | ((IN_LAST && !C::TS) ? (1u << 15) : 0u) | (1u << 16) |
                           (static_cast<uint32_t>(128 >> 4) << 24);
   P.idesc = common | (static_cast<uint32_t>(C::NJ >> 3) << 17);
   P.idesc2 = common | (static_cast<uint32_t>(2 * C::NJ >> 3) << 17);
@@ -712,9 +715,12 @@ bool tc_f32x3_supported(const Problem& p, bool check_pointers) {
   if (p.batch <= 0 || p.batch > 0x7fffffffLL) return false;
   // the operand tiles are addressed in atoms of 32 columns; global strides are multiples of 16 bytes
   if (p.b % 32 != 0) return false;
-  if (p.bs_last) {
+  const bool out_last = p.out_bs_last < 0 ? p.bs_last != 0 : p.out_bs_last != 0;
+  if (out_last != (p.bs_last != 0) && (p.d != 1 || p.groups > 1)) return false;  // layout-changing factors
+  if (p.bs_last || out_last) {
     if (p.batch % 32 != 0) return false;
-  } else {
+  }
+  if (!p.bs_last) {
     if (p.d != 1 || p.c % 4 != 0) return false;
   }
   if (check_pointers) {
@@ -732,7 +738,7 @@ int tc_f32x3_launch(const Problem& p, int config, cudaStream_t stream) {
   // tensor memory); short blocks (batch-last, c <= 32 kMaxResident) have 96 columns with resident
   // weights (the weights of the j tile stay in shared memory and twelve warps store the
   // accumulator) at 0.6 against 0.45 for 64 columns.
-  const bool can_wr = p.bs_last && p.c <= 32 * tc::kMaxResident;
+  const bool can_wr = p.bs_last && p.out_bs_last != 0 && p.c <= 32 * tc::kMaxResident;
   int nj = 96;
   double best = 1e30;
   for (int cand : {128, 96, 64}) {
@@ -743,16 +749,26 @@ int tc_f32x3_launch(const Problem& p, int config, cudaStream_t stream) {
   if (config == 1) nj = 128;
   if (config == 2) nj = 96;
   if (config == 3) nj = 64;
-  if (p.bs_last) {
-    if (nj == 128) return tc::launch_f<true, 128, 3, false, true, false>(p, stream);
-    if (nj == 96)
-      return can_wr ? tc::launch_f<true, 96, 5, true, true, true>(p, stream)
-                    : tc::launch_f<true, 96, 5, true, true, false>(p, stream);
-    return tc::launch_f<true, 64, 6, true, false, false>(p, stream);
+  const bool out_last = p.out_bs_last < 0 ? p.bs_last != 0 : p.out_bs_last != 0;
+  if (out_last != (p.bs_last != 0)) {
+    // layout-changing factor (d = 1): the forms with the input operand in tensor memory
+    if (nj == 128) nj = 96;
+    if (p.bs_last)
+      return nj == 96 ? tc::launch_f<true, false, 96, 4, true, false, false>(p, stream)
+                      : tc::launch_f<true, false, 64, 6, true, false, false>(p, stream);
+    return nj == 96 ? tc::launch_f<false, true, 96, 5, true, true, false>(p, stream)
+                    : tc::launch_f<false, true, 64, 6, true, false, false>(p, stream);
   }
-  if (nj == 128) return tc::launch_f<false, 128, 3, false, false, false>(p, stream);
-  if (nj == 96) return tc::launch_f<false, 96, 4, true, false, false>(p, stream);
-  return tc::launch_f<false, 64, 6, true, false, false>(p, stream);
+  if (p.bs_last) {
+    if (nj == 128) return tc::launch_f<true, true, 128, 3, false, true, false>(p, stream);
+    if (nj == 96)
+      return can_wr ? tc::launch_f<true, true, 96, 5, true, true, true>(p, stream)
+                    : tc::launch_f<true, true, 96, 5, true, true, false>(p, stream);
+    return tc::launch_f<true, true, 64, 6, true, false, false>(p, stream);
+  }
+  if (nj == 128) return tc::launch_f<false, false, 128, 3, false, false, false>(p, stream);
+  if (nj == 96) return tc::launch_f<false, false, 96, 4, true, false, false>(p, stream);
+  return tc::launch_f<false, false, 64, 6, true, false, false>(p, stream);
 }
 
 }  // namespace ksmm

@@ -808,6 +808,7 @@ bool tc_config_supported(const Problem& p, int config, bool check_pointers) {
   if (out_last != (p.bs_last != 0)) {
     // a factor that changes the layout: 16-bit, d = 1, no groups, no regrouping
     if (p.d != 1 || p.groups > 1 || p.out_regroup_d || p.in_regrouped) return false;
+    if (p.in_dtype == KSMM_F32) return config >= 0 && config <= 3 && tc_f32x3_supported(p, check_pointers);
     if ((p.in_dtype != KSMM_F16 && p.in_dtype != KSMM_BF16) || p.out_dtype != p.in_dtype) return false;
     if (p.batch <= 0 || p.batch > 0x7fffffffLL) return false;
     if (p.b % 8 != 0 || p.c % 8 != 0 || p.batch % 8 != 0) return false;   // 16-byte strides on both sides
@@ -897,8 +898,8 @@ int tc_launch(const Problem& p, int config, cudaStream_t stream) {
                      p.a, p.b, p.c, p.d, static_cast<long long>(p.batch), p.in_dtype, p.bs_last);
   const bool last = p.bs_last != 0;
   const bool out_last = p.out_bs_last < 0 ? last : p.out_bs_last != 0;
-  if (out_last != last) return last ? tc::launch_mixed<true>(p, config, stream) : tc::launch_mixed<false>(p, config, stream);
   if (p.in_dtype == KSMM_F32) return tc_f32x3_launch(p, config, stream);
+  if (out_last != last) return last ? tc::launch_mixed<true>(p, config, stream) : tc::launch_mixed<false>(p, config, stream);
   if (!last && p.d != 1) {
     if (p.d % 8 == 0) return tc_bsfirst_g_launch(p, stream);
     return config == 1 ? tc_bsfirst_dp_launch(p, stream) : tc_bsfirst_d_launch(p, stream);

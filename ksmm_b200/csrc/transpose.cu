@@ -14,14 +14,15 @@ namespace ksmm {
 template <typename T>
 __global__ void __launch_bounds__(256)
     transpose_kernel(const T* __restrict__ in, T* __restrict__ out, int64_t rows, int64_t cols,
-                     int vec_ok) {
+                     int vec_ok, unsigned tiles_x) {
   constexpr int TILE = 64;
   constexpr int V = 16 / sizeof(T);            // elements per 16-byte vector
   // one extra 4-byte word per tile row keeps the column reads of a warp on distinct banks
   constexpr int PITCH = TILE + 4 / static_cast<int>(sizeof(T));
   __shared__ T tile[TILE][PITCH];
-  const int64_t r0 = static_cast<int64_t>(blockIdx.y) * TILE;
-  const int64_t c0 = static_cast<int64_t>(blockIdx.x) * TILE;
+  // tiles are numbered row-major in one grid dimension (either extent may exceed 65535 tiles)
+  const int64_t r0 = static_cast<int64_t>(blockIdx.x / tiles_x) * TILE;
+  const int64_t c0 = static_cast<int64_t>(blockIdx.x % tiles_x) * TILE;
   const int tid = threadIdx.x;
 
   // ---- load: rows r0.., columns c0.. --------------------------------------------
@@ -67,23 +68,23 @@ int launch_transpose(const void* in, void* out, int64_t rows, int64_t cols, int 
                      cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return KSMM_OK;
   const int64_t gx = (cols + 63) / 64, gy = (rows + 63) / 64;
-  if (gx > 0x7fffffffLL || gy > 65535)
+  if (gx * gy > 0x7fffffffLL)
     return set_error(KSMM_ERR_UNSUPPORTED, "transpose of %lld x %lld exceeds the grid limits",
                      static_cast<long long>(rows), static_cast<long long>(cols));
   const int V = 16 / es;
   const int vec_ok = (rows % V == 0) && (cols % V == 0) &&
                      reinterpret_cast<uintptr_t>(in) % 16 == 0 &&
                      reinterpret_cast<uintptr_t>(out) % 16 == 0;
-  dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
+  const unsigned grid = static_cast<unsigned>(gx * gy), tx = static_cast<unsigned>(gx);
   if (es == 4)
     transpose_kernel<uint32_t><<<grid, 256, 0, stream>>>(static_cast<const uint32_t*>(in),
-                                                         static_cast<uint32_t*>(out), rows, cols, vec_ok);
+                                                         static_cast<uint32_t*>(out), rows, cols, vec_ok, tx);
   else if (es == 2)
     transpose_kernel<uint16_t><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(in),
-                                                         static_cast<uint16_t*>(out), rows, cols, vec_ok);
+                                                         static_cast<uint16_t*>(out), rows, cols, vec_ok, tx);
   else
     transpose_kernel<uint8_t><<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(in),
-                                                        static_cast<uint8_t*>(out), rows, cols, vec_ok);
+                                                        static_cast<uint8_t*>(out), rows, cols, vec_ok, tx);
   count_launch();
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess)

@@ -1076,6 +1076,33 @@ def test_layout_changing_factor(dtype, in_last):
     kb.check_device()
 
 
+@pytest.mark.parametrize("in_last", [True, False])
+def test_layout_changing_factor_fp32(in_last):
+    """The fp32 tensor kernel's layout-changing forms (d = 1, b a multiple of 32, c of 4, batch of 32):
+    one launch, the 96- and 64-column tiles, blocks of one and of many 32-row chunks."""
+    pats = [(4, 192, 192, 1), (1, 768, 192, 1), (16, 64, 64, 1), (1, 64, 768, 1), (3, 32, 20, 1), (2, 160, 72, 1),
+            (1, 1024, 1024, 1)]
+    rng = np.random.RandomState(1450)
+    for pi, pattern in enumerate(pats):
+        a, b, c, d = pattern
+        for batch in (32, 160, 544, 4128):
+            x, w = _inputs(pattern, batch, torch.float32, in_last, seed=1450 + pi)
+            bias = torch.from_numpy(rng.standard_normal(a * b * d).astype(np.float32))
+            wk = kb.generate_factor(a, b, c, d, "kernel", w, torch.float32, DEV)
+            before = kb.launch_count()
+            y = kb.chain_forward(x.to(DEV), [wk], [pattern], in_last, bias=bias.to(DEV), out_bs_last=not in_last,
+                                 activation="relu")
+            assert kb.launch_count() - before == 1, (pattern, batch)
+            assert tuple(y.shape) == ((batch, a * b * d) if in_last else (a * b * d, batch))
+            ref = _oracle(x, w, in_last)
+            bf = bias.numpy()
+            ref = np.maximum(ref + (bf[:, None] if in_last else bf[None, :]), 0.0).T
+            yy = y.cpu().numpy()
+            assert not np.isnan(yy).any()
+            assert ko.rel_fro_error(yy, ref) < 1e-5, (pattern, batch)
+    kb.check_device()
+
+
 def test_planned_chains_mixed_layouts():
     """Chains whose output layout differs from the input's, and batch-first chains that run their
     d > 1 factors batch-last inside: KS-ViT-B's fc1 (batch-first tokens -> batch-last 3072 features,
@@ -1086,7 +1113,12 @@ def test_planned_chains_mixed_layouts():
              ([(1, 64, 64, 16), (4, 64, 64, 4), (16, 64, 64, 1)], torch.float16, False, False, None, 4),
              ([(1, 64, 64, 16), (4, 64, 64, 4), (16, 64, 64, 1)], torch.bfloat16, True, False, "relu", 3),
              ([(6, 64, 64, 1), (1, 768, 192, 2)], torch.float32, True, False, None, 3),
-             ([(2, 96, 48, 2)], torch.float16, False, True, None, 2)]
+             ([(2, 96, 48, 2)], torch.float16, False, True, None, 2),
+             # fp32: fc1 / fc2 of the KS-ViT-B MLP between batch-first tokens (first factor changes the
+             # layout, the d = 4 factor runs batch-last, one transpose at the end / at the start)
+             ([(4, 192, 192, 1), (1, 768, 192, 4)], torch.float32, False, False, "gelu", 3),
+             ([(1, 192, 768, 4), (4, 192, 192, 1)], torch.float32, False, False, None, 3),
+             ([(4, 192, 192, 1), (1, 768, 192, 4)], torch.float32, False, True, None, 2)]
     for ci, (pats, dtype, in_last, out_last, act, launches) in enumerate(cases):
         for batch in (520, 25088):
             rng = np.random.RandomState(1500 + ci)
