@@ -1107,7 +1107,7 @@ def test_planned_chains_mixed_layouts():
     """Chains whose output layout differs from the input's, and batch-first chains that run their
     d > 1 factors batch-last inside: KS-ViT-B's fc1 (batch-first tokens -> batch-last 3072 features,
     GELU fused), fc2 (back), the 3-factor chain (input transposed once, last factor writes
-    batch-first), and an fp32 chain (no layout-changing kernel: transposed at the end)."""
+    batch-first), and fp32 chains (a d = 2 factor last: transposed at the end; the MLP layers)."""
     cases = [([(4, 192, 192, 1), (1, 768, 192, 4)], torch.float16, False, True, "gelu", 2),
              ([(1, 192, 768, 4), (4, 192, 192, 1)], torch.float16, True, False, None, 2),
              ([(1, 64, 64, 16), (4, 64, 64, 4), (16, 64, 64, 1)], torch.float16, False, False, None, 4),
