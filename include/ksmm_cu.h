@@ -178,8 +178,9 @@ KSMM_API int ksmm_cu_chain_forward_act(const void* input, const void* const* val
  * while the network around them is batch-first (the reference fixes one
  * layout per layer, interface.py:134, 193-345, and pays for interleaved blocks
  * in every batch-first factor with d > 1).  The library plans a layout for
- * every intermediate: 16-bit factors with d = 1 read one layout and write the
- * other inside the kernel, at no cost; where no such factor exists the tensor
+ * every intermediate: 16-bit and fp32 factors with d = 1 read one layout and
+ * write the other inside the kernel, at no cost (fp32: b a multiple of 32, c
+ * of 4, batch of 32); where no such factor exists the tensor
  * at the chain's end is transposed.  ksmm_cu_chain_forward and
  * ksmm_cu_chain_forward_act are this call with out_bs_last = bs_last, and use
  * the same planner, so their intermediates may be batch-last inside a
