@@ -631,15 +631,17 @@ def run_ours(args, rank, world, local_rank):
     chains = None
     if not args.no_vit and not args.only:
         import math
-        chain_list = [("ks_vit_fc1", [(4, 192, 192, 1), (1, 768, 192, 4)]),
-                      ("ks_vit_fc2", [(1, 192, 768, 4), (4, 192, 192, 1)]),
-                      ("three_factor_1024", [(1, 64, 64, 16), (4, 64, 64, 4), (16, 64, 64, 1)])]
+        chain_list = [("ks_vit_fc1", [(4, 192, 192, 1), (1, 768, 192, 4)], torch.float16),
+                      ("ks_vit_fc2", [(1, 192, 768, 4), (4, 192, 192, 1)], torch.float16),
+                      ("three_factor_1024", [(1, 64, 64, 16), (4, 64, 64, 4), (16, 64, 64, 1)], torch.float16),
+                      ("ks_vit_fc1", [(4, 192, 192, 1), (1, 768, 192, 4)], torch.float32),
+                      ("three_factor_1024", [(1, 64, 64, 16), (4, 64, 64, 4), (16, 64, 64, 1)], torch.float32)]
         chains = []
-        for name, pats in chain_list:
+        for name, pats, cdt in chain_list:
             gen = torch.Generator(device=dev).manual_seed(11)
             n_in = pats[0][0] * pats[0][2] * pats[0][3]
-            xs = [torch.randn((BATCH, n_in), device=dev, dtype=torch.float16, generator=gen) for _ in range(4)]
-            layer = kb.KSLinear(pats, weights=None, bias=False, algo="kernel", dtype=torch.float16,
+            xs = [torch.randn((BATCH, n_in), device=dev, dtype=cdt, generator=gen) for _ in range(4)]
+            layer = kb.KSLinear(pats, weights=None, bias=False, algo="kernel", dtype=cdt,
                                 bs_last=False, device=dev)
 
             def run_chained(x):
@@ -671,7 +673,8 @@ def run_ours(args, rank, world, local_rank):
                     del g
                 ya, yb = run_chained(xs[0]).float(), run_per_factor(xs[0]).float()
                 rel = float((ya - yb).norm() / yb.norm())
-            chains.append({"chain": name, "patterns": [list(p_) for p_ in pats], "dtype": "fp16",
+            chains.append({"chain": name, "patterns": [list(p_) for p_ in pats],
+                           "dtype": "fp16" if cdt == torch.float16 else "fp32",
                            "layout": "bs_first", "ms_chained": round(res["chained"], 5),
                            "ms_per_factor": round(res["per_factor"], 5),
                            "speedup": round(res["per_factor"] / res["chained"], 3),
