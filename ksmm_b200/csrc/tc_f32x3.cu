@@ -732,17 +732,18 @@ bool tc_f32x3_supported(const Problem& p, bool check_pointers) {
 }
 
 int tc_f32x3_launch(const Problem& p, int config, cudaStream_t stream) {
-  // <batch-last, j tile, stages, input operand in tensor memory, direct stores, resident weights>.
-  // The j tile is the one with the least padded work.  Relative cost of a tile: 1 for 128 columns
-  // (input operand from shared memory), 0.65 and 0.55 for 96 and 64 columns (input operand in
-  // tensor memory); short blocks (batch-last, c <= 32 kMaxResident) have 96 columns with resident
-  // weights (the weights of the j tile stay in shared memory and twelve warps store the
-  // accumulator) at 0.6 against 0.45 for 64 columns.
+  // <input batch-last, output batch-last, j tile, stages, input operand in tensor memory, direct
+  // stores, resident weights>.  The j tile is the one with the least padded work.  Relative cost
+  // of a tile, from tuning runs at 25088 rows over benchmark and reference-list patterns: 1 for
+  // 128 columns (input operand from shared memory), 0.72 for 96 columns (input operand in tensor
+  // memory; with resident weights on short blocks, batch-last and c <= 32 kMaxResident, where twelve
+  // warps store the accumulator) and 0.55 for 64 columns.  E.g. b = 768: eight tiles of 96 (5.76)
+  // against six of 128 (6.0), measured level; b = 128, 256, 512: tiles of 128 win by 5 to 27 %.
   const bool can_wr = p.bs_last && p.out_bs_last != 0 && p.c <= 32 * tc::kMaxResident;
   int nj = 96;
   double best = 1e30;
   for (int cand : {128, 96, 64}) {
-    const double tile = cand == 128 ? 1.0 : (cand == 96 && can_wr ? 0.6 : (cand == 96 ? 0.65 : (can_wr ? 0.45 : 0.55)));
+    const double tile = cand == 128 ? 1.0 : (cand == 96 ? 0.72 : 0.55);
     const double cost = ((p.b + cand - 1) / cand) * tile;
     if (cost < best - 1e-9) { best = cost; nj = cand; }
   }

@@ -880,7 +880,14 @@ int tc_default_config(const Problem& p) {
   // against 85 us for (1,768,192,4) fp16); chains use its kernel when the previous factor can
   // store the intermediate regrouped for free.
   const bool out_last = p.out_bs_last < 0 ? p.bs_last != 0 : p.out_bs_last != 0;
-  if (out_last == (p.bs_last != 0) && !p.bs_last && p.d != 1) return 0;
+  if (out_last == (p.bs_last != 0) && !p.bs_last && p.d != 1) {
+    // The eight-block kernel moves 16-byte pieces that lie d elements apart: at d = 16 it beats the
+    // layout conversion (39 against 61 us for (1,64,64,16) fp16 at 25088 rows), at d = 24 the two
+    // are level, beyond that the conversion wins by far (299 against 734 us for (1,48,48,96)).
+    // It stays available as configuration 0 of the family.
+    if (p.d % 8 == 0 && p.d > 16) return -1;
+    return 0;
+  }
   // 64 x 64 blocks are copies with one MMA chunk per tile: two smaller CTAs per SM keep more loads
   // and stores in flight (configuration 5; tuned at batch 25088: 23.0 against 24.0 us batch-last,
   // 24.1 against 26.5 us batch-first for the 16-block patterns)

@@ -15,6 +15,7 @@ from __future__ import annotations
 import ctypes
 import json
 import math
+import os
 
 import torch
 
@@ -211,17 +212,23 @@ def _time_default(pattern, batch, dtype, bs_last, reps=30):
 
 
 def tune_set(patterns=BENCHMARK_PATTERNS, batch=25088, dtypes=(torch.float32, torch.float16, torch.bfloat16),
-             layouts=(True, False), min_gain=0.03, nrepeats=30):
+             layouts=(True, False), min_gain=0.03, nrepeats=30, time_budget_s=None, log=None):
     """Tune every (pattern, dtype, layout) and keep a choice only where it beats the heuristic by
     more than `min_gain` when both are timed the same way; everything else is left to the
     heuristic (a cached choice also switches off the layout fusion of chains for that factor, so
-    an entry has to earn its place).  Returns the kept entries."""
+    an entry has to earn its place).  Returns the kept entries.  With `time_budget_s` the loop
+    goes pattern by pattern (all types and layouts of one pattern together) and stops once the
+    budget is spent; `log` (a callable) receives one line per tuned case."""
+    import time
     lib = _lib.load()
     kept = []
-    for dtype in dtypes:
-        code = dtype_code(dtype)
-        for bs_last in layouts:
-            for pattern in patterns:
+    t_start = time.time()
+    for pattern in patterns:
+        if time_budget_s is not None and time.time() - t_start > time_budget_s:
+            break
+        for dtype in dtypes:
+            code = dtype_code(dtype)
+            for bs_last in layouts:
                 a, b, c, d = pattern
                 lib.ksmm_cu_clear_choice(batch, a, b, c, d, code, code, int(bs_last))
                 _table.pop(_key(batch, pattern, code, code, bs_last), None)
@@ -233,7 +240,12 @@ def tune_set(patterns=BENCHMARK_PATTERNS, batch=25088, dtypes=(torch.float32, to
                 entry["ms"], entry["ms_heuristic"] = t_tuned, t_default
                 same = (entry["family"] == "convert" and conv0) or \
                     (not conv0 and entry["family"] == fam0 and (entry["config"] == cfg0 or cfg0 < 0))
-                if not same and t_tuned < (1.0 - min_gain) * t_default:
+                keep = (not same) and t_tuned < (1.0 - min_gain) * t_default
+                if log is not None:
+                    log(f"{pattern} {str(dtype)[6:]} {'bs_last' if bs_last else 'bs_first'}: heuristic "
+                        f"{fam0}/{cfg0}{' via transposes' if conv0 else ''} {t_default * 1e3:.1f} us, tuned "
+                        f"{entry['family']}/{entry['config']} {t_tuned * 1e3:.1f} us{' KEPT' if keep else ''}")
+                if keep:
                     kept.append(entry)
                 else:
                     lib.ksmm_cu_clear_choice(batch, a, b, c, d, code, code, int(bs_last))
@@ -257,13 +269,21 @@ if __name__ == "__main__":
     ap.add_argument("--patterns-file", default=None,
                     help="text file with one a,b,c,d row per line (# comments allowed), tuned as well")
     ap.add_argument("--every", type=int, default=1, help="take every n-th row of --patterns-file")
+    ap.add_argument("--time-budget", type=float, default=None,
+                    help="stop after this many seconds and write what has been tuned so far")
+    ap.add_argument("--dtypes", default="fp32,fp16,bf16")
+    ap.add_argument("--keep-existing", action="store_true", help="start from the table already at --out")
     args = ap.parse_args()
     pats = list(BENCHMARK_PATTERNS)
     if args.patterns_file:
         rows = [tuple(int(v) for v in ln.split(",")) for ln in open(args.patterns_file)
                 if ln.strip() and not ln.startswith("#")]
         pats += [r for r in rows[::max(1, args.every)] if r not in pats]
-    for e in tune_set(patterns=pats, batch=args.batch):
+    names = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}
+    if args.keep_existing and os.path.exists(args.out):
+        load(args.out)
+    for e in tune_set(patterns=pats, batch=args.batch, dtypes=tuple(names[n] for n in args.dtypes.split(",")),
+                      time_budget_s=args.time_budget, log=lambda ln: print(ln, flush=True)):
         print(e)
     save(args.out)
     print(f"{len(entries())} entries -> {args.out}")
