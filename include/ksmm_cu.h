@@ -358,7 +358,11 @@ KSMM_API int ksmm_cu_host_wait(uint64_t ticket);
  * ksmm_cu_config_supported: 1 if (algo, config) can run this problem.
  * ksmm_cu_tune: times every supported candidate on the given buffers (which
  *   must be valid for the problem; output is overwritten), stores the winner
- *   in the in-process cache, and reports it.  best_ms may be NULL.
+ *   in the in-process cache, and reports it.  best_ms may be NULL.  Every
+ *   timed launch (nrepeats per candidate, at most 64) starts with a cold L2:
+ *   the call allocates a buffer of 1.5x the cache for its own duration and
+ *   overwrites it before each launch, outside the timed interval.  An
+ *   offline call: it allocates, synchronises the stream and frees.
  * ksmm_cu_set_choice / ksmm_cu_get_choice: write / read the cache directly,
  *   so that a saved table can be re-loaded without re-timing.
  * ksmm_cu_default_choice: what KSMM_ALGO_AUTO runs for this problem (a cached

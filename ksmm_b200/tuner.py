@@ -202,13 +202,17 @@ def _time_default(pattern, batch, dtype, bs_last, reps=30):
     y = torch.empty((a * b * d, batch) if bs_last else (batch, a * b * d), device=dev, dtype=dtype)
     for _ in range(3):
         forward_ex(x, w, bs_last, a, b, c, d, out=y)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(reps):
+    # every timed launch starts with a cold L2 (a buffer larger than the cache is overwritten
+    # before it, outside the timed interval), like ksmm_cu_tune's own timing
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+    for e0, e1 in pairs:
+        flush.zero_()
+        e0.record()
         forward_ex(x, w, bs_last, a, b, c, d, out=y)
-    e1.record()
-    e1.synchronize()
-    return e0.elapsed_time(e1) / reps
+        e1.record()
+    torch.cuda.synchronize()
+    return sum(e0.elapsed_time(e1) for e0, e1 in pairs) / reps
 
 
 def tune_set(patterns=BENCHMARK_PATTERNS, batch=25088, dtypes=(torch.float32, torch.float16, torch.bfloat16),
@@ -241,6 +245,15 @@ def tune_set(patterns=BENCHMARK_PATTERNS, batch=25088, dtypes=(torch.float32, to
                 same = (entry["family"] == "convert" and conv0) or \
                     (not conv0 and entry["family"] == fam0 and (entry["config"] == cfg0 or cfg0 < 0))
                 keep = (not same) and t_tuned < (1.0 - min_gain) * t_default
+                if keep:
+                    # a second look at both: single timings wander by several per cent
+                    lib.ksmm_cu_clear_choice(batch, a, b, c, d, code, code, int(bs_last))
+                    t_default = min(t_default, _time_default(pattern, batch, dtype, bs_last, nrepeats))
+                    lib.ksmm_cu_set_choice(batch, a, b, c, d, code, code, int(bs_last),
+                                           _ALGO_CODE[entry["family"]], entry["config"])
+                    t_tuned = max(t_tuned, _time_default(pattern, batch, dtype, bs_last, nrepeats))
+                    entry["ms"], entry["ms_heuristic"] = t_tuned, t_default
+                    keep = t_tuned < (1.0 - min_gain) * t_default
                 if log is not None:
                     log(f"{pattern} {str(dtype)[6:]} {'bs_last' if bs_last else 'bs_first'}: heuristic "
                         f"{fam0}/{cfg0}{' via transposes' if conv0 else ''} {t_default * 1e3:.1f} us, tuned "
