@@ -282,16 +282,17 @@ if __name__ == "__main__":
     ap.add_argument("--patterns-file", default=None,
                     help="text file with one a,b,c,d row per line (# comments allowed), tuned as well")
     ap.add_argument("--every", type=int, default=1, help="take every n-th row of --patterns-file")
+    ap.add_argument("--offset", type=int, default=0, help="first row of --patterns-file to take")
     ap.add_argument("--time-budget", type=float, default=None,
                     help="stop after this many seconds and write what has been tuned so far")
     ap.add_argument("--dtypes", default="fp32,fp16,bf16")
     ap.add_argument("--keep-existing", action="store_true", help="start from the table already at --out")
     args = ap.parse_args()
-    pats = list(BENCHMARK_PATTERNS)
+    pats = [] if args.patterns_file and args.offset else list(BENCHMARK_PATTERNS)
     if args.patterns_file:
         rows = [tuple(int(v) for v in ln.split(",")) for ln in open(args.patterns_file)
                 if ln.strip() and not ln.startswith("#")]
-        pats += [r for r in rows[::max(1, args.every)] if r not in pats]
+        pats += [r for r in rows[max(0, args.offset)::max(1, args.every)] if r not in pats]
     names = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}
     if args.keep_existing and os.path.exists(args.out):
         load(args.out)
