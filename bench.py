@@ -270,6 +270,14 @@ def run_profile_case(name, local_rank):
             x = torch.randn((BATCH, 768), device=dev, dtype=torch.float16, generator=gen)
             for _ in range(3):
                 y = group(x)
+        elif name == "chain_fp32":
+            # the fp32 three-factor chain on batch-first rows as the layout planner runs it: the input
+            # transposed once, two batch-last factors, the last factor writes batch-first rows
+            pats = [(1, 64, 64, 16), (4, 64, 64, 4), (16, 64, 64, 1)]
+            layer = kb.KSLinear(pats, bias=False, dtype=torch.float32, bs_last=False, device=dev)
+            x = torch.randn((BATCH, 1024), device=dev, generator=gen)
+            for _ in range(3):
+                y = layer(x)
         else:
             raise SystemExit(f"unknown --profile-case {name}")
     torch.cuda.synchronize()
@@ -789,7 +797,7 @@ def main():
                     help="skip re-timing the fp32 cases on the FFMA family (the fp32_ffma_only line)")
     ap.add_argument("--sweep-configs", action="store_true",
                     help="also time every tile configuration of every case (printed to stderr)")
-    ap.add_argument("--profile-case", default=None, choices=["mlp_pair", "wgrad", "qkv"],
+    ap.add_argument("--profile-case", default=None, choices=["mlp_pair", "wgrad", "qkv", "chain_fp32"],
                     help="run a few launches of a chain / backward / grouped workload and exit (profiler captures)")
     ap.add_argument("--only", default=None,
                     help='restrict the sweep: "dtype:layout:a,b,c,d", e.g. "fp16:bs_last:1,768,192,4"')
