@@ -406,7 +406,7 @@ KSMM_API uint64_t ksmm_cu_launch_count(void);
 
 /* Number of device allocations (cudaMalloc) the library itself has made in
  * this process: layout scratch, the staging buffers of the *_host calls, the
- * FFMA probe.  A caller that must not allocate at call time can assert that
+ * FFMA probe, the cache-flush buffer of ksmm_cu_tune.  A caller that must not allocate at call time can assert that
  * the count does not move across its calls. */
 KSMM_API uint64_t ksmm_cu_alloc_count(void);
 
